@@ -1,0 +1,341 @@
+// Fused attention for fp16 tensors with head_dim 64: O = softmax(scale * Q K^T + mask) V.
+//
+// One CTA per (batch, head, 128 query rows); two CTAs share an SM so that one CTA's softmax
+// overlaps the other's tensor-core work.  Per 128-key tile:
+//   warp 0   TMA loads of Q (once), K_j and V_j straight from the caller's strided tensors
+//            (so Q/K/V may live inside a packed [T, 3H] projection output - no head split);
+//   warp 1   tcgen05.mma S = Q K_j^T (128x128x64) into TMEM, later O_j = P_j V_j (128x64x128);
+//            V is consumed MN-major exactly as TMA lays it down - no transpose;
+//   warps 2-5  one query row per thread: read S from TMEM, online softmax in the log2 domain,
+//            write P_j (fp16) into shared memory in the 128-byte-swizzled K-major layout the MMA
+//            reads, then fold O_j into the fp32 running output held in registers.
+// The scores never touch HBM: traffic is Q, K, V in and O out.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "epilogue.cuh"
+#include <math.h>
+
+namespace b200ml {
+
+namespace {
+
+constexpr int AT_THREADS = 192;
+constexpr int QT = 128;   // query rows per CTA
+constexpr int KT = 128;   // keys per iteration
+constexpr int HD = 64;    // head dimension
+constexpr int TILE_BYTES = 128 * HD * 2;         // 16 KB: Q, K_j or V_j
+constexpr int P_BYTES = QT * KT * 2;             // 32 KB: two 64-column swizzle atoms
+constexpr int AT_SMEM = 3 * TILE_BYTES + P_BYTES + 256 + 1024;
+constexpr uint32_t AT_TMEM_COLS = 256;           // S: columns [0,128), O_j: [128,192)
+
+struct AttnArgs {
+    int32_t heads, seq_q, seq_kv, q_tiles;
+    int64_t o_stride_b, o_stride_h, o_stride_s;
+    float scale_log2;  // scale * log2(e)
+    __half* o;
+    const __half* mask;  // [batch, seq_kv] additive, or null
+    int32_t* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sq = smem;
+    uint8_t* sk = smem + TILE_BYTES;
+    uint8_t* sv = smem + 2 * TILE_BYTES;
+    uint8_t* sp = smem + 3 * TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES + P_BYTES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* v_full = bars + 2;
+    uint64_t* k_empty = bars + 3;
+    uint64_t* v_empty = bars + 4;
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_full = bars + 6;
+    uint64_t* o_full = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int qt = blockIdx.x % args.q_tiles;
+    const int bh = blockIdx.x / args.q_tiles;
+    const int head = bh % args.heads;
+    const int batch = bh / args.heads;
+    const int q0 = qt * QT;
+    const int n_kv = (args.seq_kv + KT - 1) / KT;
+
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_q);
+        ptx::prefetch_tensormap(&tmap_k);
+        ptx::prefetch_tensormap(&tmap_v);
+    }
+    if (warp == 1) {
+        if (lane == 0) {
+            ptx::mbar_init(q_full, 1);
+            ptx::mbar_init(k_full, 1);
+            ptx::mbar_init(v_full, 1);
+            ptx::mbar_init(k_empty, 1);
+            ptx::mbar_init(v_empty, 1);
+            ptx::mbar_init(s_full, 1);
+            ptx::mbar_init(p_full, 128);
+            ptx::mbar_init(o_full, 1);
+            ptx::fence_mbar_init();
+        }
+        __syncwarp();
+        ptx::tmem_alloc(tmem_slot, AT_TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;
+    const uint32_t tmem_o = tmem_base + 128;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (ptx::elect_one()) {
+            ptx::mbar_expect_tx(q_full, TILE_BYTES);
+            ptx::tma_load_4d(sq, &tmap_q, q_full, 0, q0, head, batch);
+            for (int j = 0; j < n_kv; ++j) {
+                const uint32_t par = j & 1;
+                if (!ptx::mbar_wait(k_empty, par ^ 1)) {
+                    atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                    break;
+                }
+                ptx::mbar_expect_tx(k_full, TILE_BYTES);
+                ptx::tma_load_4d(sk, &tmap_k, k_full, 0, j * KT, head, batch);
+                if (!ptx::mbar_wait(v_empty, par ^ 1)) {
+                    atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                    break;
+                }
+                ptx::mbar_expect_tx(v_full, TILE_BYTES);
+                ptx::tma_load_4d(sv, &tmap_v, v_full, 0, j * KT, head, batch);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (ptx::elect_one()) {
+            constexpr uint32_t IDESC_S = ptx::make_idesc_f16(128, KT, 0, 0);  // Q, K both K-major
+            constexpr uint32_t IDESC_O = ptx::make_idesc_f16(128, HD, 0, 1);  // P K-major, V MN-major
+            const uint32_t q_addr = ptx::smem_u32(sq), k_addr = ptx::smem_u32(sk), v_addr = ptx::smem_u32(sv),
+                           p_addr = ptx::smem_u32(sp);
+            bool ok = ptx::mbar_wait(q_full, 0);
+            if (!ok) atomicExch(args.status, DEV_TIMEOUT_ATTN);
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const uint32_t par = j & 1;
+                // S_j = Q K_j^T
+                if (!ptx::mbar_wait(k_full, par)) {
+                    atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                    break;
+                }
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t a = ptx::make_smem_desc_sw128(q_addr + kk * 32, 16, 1024);
+                    const uint64_t b = ptx::make_smem_desc_sw128(k_addr + kk * 32, 16, 1024);
+                    ptx::mma_f16_ss(tmem_s, a, b, IDESC_S, kk != 0 ? 1u : 0u);
+                }
+                ptx::mma_commit(s_full);
+                ptx::mma_commit(k_empty);
+                // O_j = P_j V_j
+                if (!ptx::mbar_wait(p_full, par) || !ptx::mbar_wait(v_full, par)) {
+                    atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                    break;
+                }
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < KT / 16; ++kk) {
+                    // P: atom kk / 4 (64 keys each, 16 KB apart), 32 bytes per step inside the atom
+                    const uint64_t a = ptx::make_smem_desc_sw128(p_addr + (kk >> 2) * (QT * 128) + (kk & 3) * 32, 16, 1024);
+                    // V: 16 key rows of 128 bytes per step; 8-row groups 1024 bytes apart
+                    const uint64_t b = ptx::make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024);
+                    ptx::mma_f16_ss(tmem_o, a, b, IDESC_O, kk != 0 ? 1u : 0u);
+                }
+                ptx::mma_commit(o_full);
+                ptx::mma_commit(v_empty);
+            }
+        }
+    } else {
+        // ------------------------------ softmax + output ------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;  // row of the query tile == TMEM lane
+        const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+        float acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;
+        const __half* mrow = args.mask ? args.mask + static_cast<int64_t>(batch) * args.seq_kv : nullptr;
+        constexpr float LOG2E = 1.44269504088896340736f;
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+            const uint32_t par = j & 1;
+            const int kv0 = j * KT;
+            if (!ptx::mbar_wait(s_full, par)) {
+                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            // pass 1: running maximum of the scaled, masked scores
+            float mx = m_run;
+#pragma unroll 1
+            for (int c = 0; c < KT / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int kv = kv0 + c * 32 + i;
+                    float t = __uint_as_float(r[i]) * args.scale_log2;
+                    if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
+                    if (kv >= args.seq_kv) t = -INFINITY;
+                    mx = fmaxf(mx, t);
+                }
+            }
+            const float m_safe = (mx == -INFINITY) ? 0.0f : mx;
+            const float alpha = ex2(m_run - m_safe);  // 0 on the first tile
+            // pass 2: P = exp2(t - m), row sum, fp16 P into swizzled shared memory
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < KT / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
+                ptx::tmem_ld_wait();
+                uint8_t* atom = sp + (c >> 1) * (QT * 128) + row * 128;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    float p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int kv = kv0 + c * 32 + g * 8 + i;
+                        float t = __uint_as_float(r[g * 8 + i]) * args.scale_log2;
+                        if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
+                        p[i] = kv < args.seq_kv ? ex2(t - m_safe) : 0.0f;
+                        sum += p[i];
+                    }
+                    const int chunk = (c & 1) * 4 + g;  // 16-byte chunk within the 128-byte row
+                    *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = pack8(p);
+                }
+            }
+            l_run = fmaf(l_run, alpha, sum);
+            m_run = mx;
+            ptx::fence_proxy_async_smem();  // P visible to the tensor core's shared-memory reads
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(p_full);
+            // fold O_j into the running output
+            if (!ptx::mbar_wait(o_full, par)) {
+                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_o + lane_off + c * 32, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[i]));
+            }
+            ptx::tc_fence_before();
+        }
+        const int q = q0 + row;
+        if (ok && q < args.seq_q) {
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            __half* op = args.o + batch * args.o_stride_b + head * args.o_stride_h + static_cast<int64_t>(q) * args.o_stride_s;
+            if ((reinterpret_cast<uintptr_t>(op) & 15) == 0) {
+#pragma unroll
+                for (int g = 0; g < HD / 8; ++g) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = acc[g * 8 + i] * inv;
+                    *reinterpret_cast<uint4*>(op + g * 8) = pack8(v);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < HD; ++i) op[i] = __float2half_rn(acc[i] * inv);
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        if (*reinterpret_cast<volatile int32_t*>(args.status) != DEV_OK) {
+            for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        }
+        ptx::tmem_dealloc(tmem_base, AT_TMEM_COLS);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// {head_dim, seq, heads, batch} with a 64 x 128 box, 128-byte swizzle.
+int make_qkv_tmap(const b200ml_ctx* ctx, CUtensorMap* out, const void* base, int64_t seq, int64_t heads, int64_t batch,
+                  int64_t ss, int64_t sh, int64_t sb, const char* what) {
+    if (!aligned16(base) || ss % 8 || (heads > 1 && sh % 8) || (batch > 1 && sb % 8))
+        return fail(B200ML_ERR_UNSUPPORTED, "attention: %s is not 16-byte aligned in every stride", what);
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!fn) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const uint64_t dummy = static_cast<uint64_t>(ss) * 2 * static_cast<uint64_t>(seq);
+    cuuint64_t dims[4] = {HD, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)ss * 2, heads > 1 ? (cuuint64_t)sh * 2 : dummy, batch > 1 ? (cuuint64_t)sb * 2 : dummy};
+    cuuint32_t box[4] = {HD, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+    return B200ML_OK;
+}
+
+}  // namespace
+
+int attention_f16(const b200ml_ctx* ctx, const b200ml_attention_params* p, cudaStream_t stream) {
+    if (p->head_dim != HD)
+        return fail(B200ML_ERR_UNSUPPORTED, "attention: head_dim %lld is not supported by the fused kernel (64 only)",
+                    (long long)p->head_dim);
+    if (p->mask && p->seq_kv >= (1ll << 31)) return fail(B200ML_ERR_INVALID, "attention: sequence too long");
+    CUtensorMap tq, tk, tv;
+    int rc = make_qkv_tmap(ctx, &tq, p->q, p->seq_q, p->heads, p->batch, p->q_stride_s, p->q_stride_h, p->q_stride_b, "Q");
+    if (rc) return rc;
+    rc = make_qkv_tmap(ctx, &tk, p->k, p->seq_kv, p->heads, p->batch, p->k_stride_s, p->k_stride_h, p->k_stride_b, "K");
+    if (rc) return rc;
+    rc = make_qkv_tmap(ctx, &tv, p->v, p->seq_kv, p->heads, p->batch, p->v_stride_s, p->v_stride_h, p->v_stride_b, "V");
+    if (rc) return rc;
+    AttnArgs a{};
+    a.heads = (int32_t)p->heads;
+    a.seq_q = (int32_t)p->seq_q;
+    a.seq_kv = (int32_t)p->seq_kv;
+    a.q_tiles = (int32_t)ceil_div(p->seq_q, QT);
+    a.o_stride_b = p->o_stride_b;
+    a.o_stride_h = p->o_stride_h;
+    a.o_stride_s = p->o_stride_s;
+    a.scale_log2 = p->scale * 1.44269504088896340736f;
+    a.o = static_cast<__half*>(p->o);
+    a.mask = static_cast<const __half*>(p->mask);
+    a.status = ctx->status_dev;
+    const int64_t grid = p->batch * p->heads * a.q_tiles;
+    B200ML_REQUIRE(grid < (1ll << 31), "attention: grid too large");
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        B200ML_CUDA(cudaFuncSetAttribute(attention_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
+        configured[ctx->device & 63] = true;
+    }
+    attention_f16_kernel<<<(unsigned)grid, AT_THREADS, AT_SMEM, stream>>>(tq, tk, tv, a);
+    return check_launch("attention_f16");
+}
+
+}  // namespace b200ml

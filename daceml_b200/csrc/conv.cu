@@ -1,0 +1,401 @@
+// ONNX Conv (NCHW cross-correlation) and squeeze-excite, FP32 FMA (rtol 1e-4 rules out TF32).
+//   * pointwise_x / pointwise_acc: 1x1 stride-1 convolutions as per-pixel small matrix products,
+//     four pixels per thread, weights broadcast from shared memory, one read of X and one write
+//     of Y; bias, Swish/ReLU, squeeze-excite gate on the input and the residual add are fused.
+//   * depthwise_plane: one (image, channel) plane per block staged in shared memory with its
+//     halo; bias + activation and the GlobalAveragePool of the result are fused.
+//   * direct: any stride / pad / dilation / group; accumulates in (c, i, j) order like the
+//     reference's 7-deep loop nest (daceml/onnx/op_implementations/img_op_implementations.py:263-288).
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace b200ml {
+
+int reduce(const b200ml_ctx* ctx, int dtype, int op, const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
+           cudaStream_t s);
+
+namespace {
+
+__device__ __forceinline__ float ldv(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float ldv(const __half* p) { return __half2float(__ldg(p)); }
+__device__ __forceinline__ void stv(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stv(__half* p, float v) { *p = __float2half_rn(v); }
+
+struct ConvGeom {
+    int32_t n, c, h, w, m, kh, kw, sh, sw, pt, pl, dh, dw, group, oh, ow, act;
+};
+
+// ---------------------------------------------------------------------------------------------
+// direct convolution: one thread = one output pixel x MT consecutive output channels
+// ---------------------------------------------------------------------------------------------
+constexpr int MT = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv_direct_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                          const T* __restrict__ bias, const T* __restrict__ gate,
+                                                          const T* __restrict__ residual, T* __restrict__ y,
+                                                          const ConvGeom g) {
+    const int cg = g.c / g.group;   // input channels per group
+    const int mg = g.m / g.group;   // output channels per group
+    const int mblocks = (mg + MT - 1) / MT;
+    const int grp = blockIdx.y / mblocks;
+    const int m0 = grp * mg + (blockIdx.y % mblocks) * MT;
+    const int mend = (grp + 1) * mg;
+    const int64_t pix = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t npix = static_cast<int64_t>(g.n) * g.oh * g.ow;
+    if (pix >= npix) return;
+    const int ox = pix % g.ow;
+    const int oy = (pix / g.ow) % g.oh;
+    const int b = pix / (static_cast<int64_t>(g.ow) * g.oh);
+    float acc[MT];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) acc[t] = (bias && m0 + t < mend) ? ldv(bias + m0 + t) : 0.0f;
+    const int64_t wstride = static_cast<int64_t>(cg) * g.kh * g.kw;
+    for (int c = 0; c < cg; ++c) {
+        const int ci = grp * cg + c;
+        const T* xp = x + (static_cast<int64_t>(b) * g.c + ci) * g.h * g.w;
+        const float gt = gate ? ldv(gate + static_cast<int64_t>(b) * g.c + ci) : 1.0f;
+        for (int i = 0; i < g.kh; ++i) {
+            const int iy = oy * g.sh - g.pt + i * g.dh;
+            if (iy < 0 || iy >= g.h) continue;
+            for (int j = 0; j < g.kw; ++j) {
+                const int ix = ox * g.sw - g.pl + j * g.dw;
+                if (ix < 0 || ix >= g.w) continue;
+                const float xv = ldv(xp + static_cast<int64_t>(iy) * g.w + ix) * gt;
+                const T* wp = w + static_cast<int64_t>(m0) * wstride + (static_cast<int64_t>(c) * g.kh + i) * g.kw + j;
+#pragma unroll
+                for (int t = 0; t < MT; ++t)
+                    if (m0 + t < mend) acc[t] = fmaf(ldv(wp + t * wstride), xv, acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+        if (m0 + t < mend) {
+            const int64_t o = ((static_cast<int64_t>(b) * g.m + m0 + t) * g.oh + oy) * g.ow + ox;
+            float v = apply_act(acc[t], g.act);
+            if (residual) v += ldv(residual + o);
+            stv(y + o, v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 1x1 convolution, few input channels (C <= 32): X held in registers, loop over output channels
+// ---------------------------------------------------------------------------------------------
+template <int CP>  // C padded to a multiple of 4
+__global__ void __launch_bounds__(128) pointwise_x_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                          const float* __restrict__ bias, const float* __restrict__ gate,
+                                                          const float* __restrict__ residual, float* __restrict__ y,
+                                                          int64_t total4, int p4, int c, int m, int act) {
+    extern __shared__ float wsm[];  // [m][CP], zero-padded
+    for (int i = threadIdx.x; i < m * CP; i += blockDim.x) {
+        const int mm = i / CP, cc = i % CP;
+        wsm[i] = cc < c ? __ldg(w + mm * c + cc) : 0.0f;
+    }
+    __syncthreads();
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int64_t img = idx / p4;
+    const int q = idx % p4;
+    const float4* xp = reinterpret_cast<const float4*>(x) + img * c * p4 + q;
+    float4 xv[CP];
+#pragma unroll
+    for (int cc = 0; cc < CP; ++cc) {
+        if (cc < c) {
+            xv[cc] = __ldg(xp + static_cast<int64_t>(cc) * p4);
+            if (gate) {
+                const float gt = __ldg(gate + img * c + cc);
+                xv[cc].x *= gt, xv[cc].y *= gt, xv[cc].z *= gt, xv[cc].w *= gt;
+            }
+        } else {
+            xv[cc] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    float4* yp = reinterpret_cast<float4*>(y) + img * m * p4 + q;
+    const float4* rp = residual ? reinterpret_cast<const float4*>(residual) + img * m * p4 + q : nullptr;
+    for (int mm = 0; mm < m; ++mm) {
+        const float b = bias ? __ldg(bias + mm) : 0.0f;
+        float4 acc = make_float4(b, b, b, b);
+        const float4* wr = reinterpret_cast<const float4*>(wsm + mm * CP);
+#pragma unroll
+        for (int c4 = 0; c4 < CP / 4; ++c4) {
+            const float4 wv = wr[c4];
+            const float ws[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float4 xx = xv[c4 * 4 + t];
+                acc.x = fmaf(ws[t], xx.x, acc.x);
+                acc.y = fmaf(ws[t], xx.y, acc.y);
+                acc.z = fmaf(ws[t], xx.z, acc.z);
+                acc.w = fmaf(ws[t], xx.w, acc.w);
+            }
+        }
+        acc.x = apply_act(acc.x, act), acc.y = apply_act(acc.y, act);
+        acc.z = apply_act(acc.z, act), acc.w = apply_act(acc.w, act);
+        if (rp) {
+            const float4 r = __ldg(rp + static_cast<int64_t>(mm) * p4);
+            acc.x += r.x, acc.y += r.y, acc.z += r.z, acc.w += r.w;
+        }
+        yp[static_cast<int64_t>(mm) * p4] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 1x1 convolution, few output channels per pass (MP <= 32): accumulators in registers, loop over C
+// ---------------------------------------------------------------------------------------------
+template <int MP>  // output channels per pass, multiple of 4
+__global__ void __launch_bounds__(128) pointwise_acc_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                            const float* __restrict__ bias,
+                                                            const float* __restrict__ gate,
+                                                            const float* __restrict__ residual, float* __restrict__ y,
+                                                            int64_t total4, int p4, int c, int m, int act) {
+    extern __shared__ float wsm[];  // [c][MP]: the MP weights of one input channel are contiguous
+    const int m0 = blockIdx.y * MP;
+    for (int i = threadIdx.x; i < c * MP; i += blockDim.x) {
+        const int cc = i / MP, mm = i % MP;
+        wsm[i] = (m0 + mm < m) ? __ldg(w + static_cast<int64_t>(m0 + mm) * c + cc) : 0.0f;
+    }
+    __syncthreads();
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int64_t img = idx / p4;
+    const int q = idx % p4;
+    const float4* xp = reinterpret_cast<const float4*>(x) + img * c * p4 + q;
+    const float* gp = gate ? gate + img * c : nullptr;
+    float4 acc[MP];
+#pragma unroll
+    for (int mm = 0; mm < MP; ++mm) {
+        const float b = (bias && m0 + mm < m) ? __ldg(bias + m0 + mm) : 0.0f;
+        acc[mm] = make_float4(b, b, b, b);
+    }
+#pragma unroll 2
+    for (int cc = 0; cc < c; ++cc) {
+        float4 xx = __ldg(xp + static_cast<int64_t>(cc) * p4);
+        if (gp) {
+            const float gt = __ldg(gp + cc);
+            xx.x *= gt, xx.y *= gt, xx.z *= gt, xx.w *= gt;
+        }
+        const float4* wr = reinterpret_cast<const float4*>(wsm + cc * MP);
+#pragma unroll
+        for (int m4 = 0; m4 < MP / 4; ++m4) {
+            const float4 wv = wr[m4];
+            const float ws[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                float4& a = acc[m4 * 4 + t];
+                a.x = fmaf(ws[t], xx.x, a.x);
+                a.y = fmaf(ws[t], xx.y, a.y);
+                a.z = fmaf(ws[t], xx.z, a.z);
+                a.w = fmaf(ws[t], xx.w, a.w);
+            }
+        }
+    }
+    float4* yp = reinterpret_cast<float4*>(y) + img * m * p4 + q;
+    const float4* rp = residual ? reinterpret_cast<const float4*>(residual) + img * m * p4 + q : nullptr;
+#pragma unroll
+    for (int mm = 0; mm < MP; ++mm) {
+        if (m0 + mm < m) {
+            float4 a = acc[mm];
+            a.x = apply_act(a.x, act), a.y = apply_act(a.y, act), a.z = apply_act(a.z, act), a.w = apply_act(a.w, act);
+            if (rp) {
+                const float4 r = __ldg(rp + static_cast<int64_t>(m0 + mm) * p4);
+                a.x += r.x, a.y += r.y, a.z += r.z, a.w += r.w;
+            }
+            yp[static_cast<int64_t>(m0 + mm) * p4] = a;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// depthwise convolution, stride 1: one (image, channel) plane per block
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                              const float* __restrict__ bias, float* __restrict__ y,
+                                                              float* __restrict__ pool_mean, const ConvGeom g) {
+    extern __shared__ float plane[];  // (h + kh - 1 ... ) padded input plane
+    __shared__ float red[8];
+    __shared__ float wk[64];
+    const int ch = blockIdx.x % g.c;
+    const int64_t img = blockIdx.x / g.c;
+    const int ph = g.oh + g.kh - 1, pw = g.ow + g.kw - 1;  // padded plane extents actually read
+    const float* xp = x + (img * g.c + ch) * static_cast<int64_t>(g.h) * g.w;
+    for (int i = threadIdx.x; i < ph * pw; i += blockDim.x) {
+        const int py = i / pw, px = i % pw;
+        const int iy = py - g.pt, ix = px - g.pl;
+        plane[i] = (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) ? __ldg(xp + iy * g.w + ix) : 0.0f;
+    }
+    if (threadIdx.x < g.kh * g.kw) wk[threadIdx.x] = __ldg(w + ch * g.kh * g.kw + threadIdx.x);
+    __syncthreads();
+    const float b = bias ? __ldg(bias + ch) : 0.0f;
+    float* yp = y + (img * g.m + ch) * static_cast<int64_t>(g.oh) * g.ow;
+    float local = 0.0f;
+    for (int o = threadIdx.x; o < g.oh * g.ow; o += blockDim.x) {
+        const int oy = o / g.ow, ox = o % g.ow;
+        float acc = b;
+        for (int i = 0; i < g.kh; ++i)
+            for (int j = 0; j < g.kw; ++j) acc = fmaf(wk[i * g.kw + j], plane[(oy + i) * pw + ox + j], acc);
+        acc = apply_act(acc, g.act);
+        yp[o] = acc;
+        local += acc;
+    }
+    if (pool_mean) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (int i = 0; i < 8; ++i) t += red[i];
+            pool_mean[img * g.m + ch] = t / (g.oh * g.ow);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// squeeze-excite gate: one block per image
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) se_gate_kernel(const T* __restrict__ pooled, const T* __restrict__ w1,
+                                                      const T* __restrict__ b1, const T* __restrict__ w2,
+                                                      const T* __restrict__ b2, T* __restrict__ gate, int c, int r) {
+    extern __shared__ float sm[];  // pooled[c] then hidden[r]
+    float* ps = sm;
+    float* hs = sm + c;
+    const int64_t img = blockIdx.x;
+    for (int i = threadIdx.x; i < c; i += blockDim.x) ps[i] = ldv(pooled + img * c + i);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int rr = warp; rr < r; rr += nw) {
+        float s = 0.0f;
+        for (int i = lane; i < c; i += 32) s = fmaf(ldv(w1 + static_cast<int64_t>(rr) * c + i), ps[i], s);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) {
+            s += b1 ? ldv(b1 + rr) : 0.0f;
+            hs[rr] = s * sigmoidf_(s);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < c; i += blockDim.x) {
+        float s = b2 ? ldv(b2 + i) : 0.0f;
+        for (int rr = 0; rr < r; ++rr) s = fmaf(ldv(w2 + static_cast<int64_t>(i) * r + rr), hs[rr], s);
+        stv(gate + img * c + i, sigmoidf_(s));
+    }
+}
+
+template <typename T>
+int launch_direct(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s) {
+    const int mg = g.m / g.group;
+    const int64_t npix = static_cast<int64_t>(g.n) * g.oh * g.ow;
+    const int64_t gy = static_cast<int64_t>(g.group) * ceil_div(mg, MT);
+    B200ML_REQUIRE(gy <= 65535, "conv: too many output-channel blocks");
+    conv_direct_kernel<T><<<dim3((unsigned)ceil_div(npix, 256), (unsigned)gy), 256, 0, s>>>(
+        (const T*)p->x, (const T*)p->weight, (const T*)p->bias, (const T*)p->gate, (const T*)p->residual, (T*)p->y, g);
+    return check_launch("conv_direct");
+}
+
+}  // namespace
+
+// Tries the specialised kernels; *launched says whether one ran, *pooled whether it also wrote the pool.
+static int conv2d_fast(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched, bool* pooled) {
+    *launched = false;
+    *pooled = false;
+    if (p->dtype != B200ML_F32) return B200ML_OK;
+    const bool unit = p->stride_h == 1 && p->stride_w == 1 && p->dil_h == 1 && p->dil_w == 1;
+    const bool nopad = !p->pad_top && !p->pad_left && !p->pad_bottom && !p->pad_right;
+    const int64_t hw = p->h * p->w;
+    const float *x = (const float*)p->x, *w = (const float*)p->weight, *b = (const float*)p->bias,
+                *gt = (const float*)p->gate, *r = (const float*)p->residual;
+    float* y = (float*)p->y;
+    if (unit && nopad && p->group == 1 && p->kh == 1 && p->kw == 1 && hw % 4 == 0 && aligned16(x) && aligned16(y) &&
+        (!r || aligned16(r))) {
+        const int p4 = (int)(hw / 4);
+        const int64_t total4 = p->n * (int64_t)p4;
+        const int64_t gx64 = ceil_div(total4, 128);
+        if (gx64 < (1ll << 31)) {
+            const unsigned gx = (unsigned)gx64;
+            const int c = (int)p->c, m = (int)p->m;
+            if (c <= 32) {
+                const int cp = c <= 4 ? 4 : (c <= 8 ? 8 : (c <= 16 ? 16 : (c <= 24 ? 24 : 32)));
+                const size_t sm = (size_t)m * cp * sizeof(float);
+                if (sm <= 48 * 1024) {
+                    switch (cp) {
+                        case 4: pointwise_x_kernel<4><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 8: pointwise_x_kernel<8><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 16: pointwise_x_kernel<16><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 24: pointwise_x_kernel<24><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        default: pointwise_x_kernel<32><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                    }
+                    *launched = true;
+                    return check_launch("pointwise_x");
+                }
+            }
+            const int mp = m <= 8 ? 8 : (m <= 16 ? 16 : (m <= 24 ? 24 : 32));
+            const size_t sm = (size_t)c * mp * sizeof(float);
+            if (sm <= 48 * 1024) {
+                const dim3 grid(gx, (unsigned)ceil_div(m, mp));
+                switch (mp) {
+                    case 8: pointwise_acc_kernel<8><<<grid, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                    case 16: pointwise_acc_kernel<16><<<grid, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                    case 24: pointwise_acc_kernel<24><<<grid, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                    default: pointwise_acc_kernel<32><<<grid, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                }
+                *launched = true;
+                return check_launch("pointwise_acc");
+            }
+        }
+    }
+    if (unit && p->group == p->c && p->m == p->c && !gt && !r && p->kh * p->kw <= 64) {
+        const size_t sm = (size_t)(g.oh + p->kh - 1) * (g.ow + p->kw - 1) * sizeof(float);
+        if (sm <= 40 * 1024 && p->n * p->c < (1ll << 31)) {
+            depthwise_plane_kernel<<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
+            *launched = true;
+            *pooled = true;
+            return check_launch("depthwise_plane");
+        }
+    }
+    return B200ML_OK;
+}
+
+int conv2d(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t s) {
+    B200ML_REQUIRE(p->group >= 1 && p->c % p->group == 0 && p->m % p->group == 0, "conv: channels not divisible by group");
+    B200ML_REQUIRE(p->stride_h >= 1 && p->stride_w >= 1 && p->dil_h >= 1 && p->dil_w >= 1, "conv: bad stride or dilation");
+    B200ML_REQUIRE(p->kh >= 1 && p->kw >= 1, "conv: empty kernel");
+    const int64_t eh = p->h + p->pad_top + p->pad_bottom - p->dil_h * (p->kh - 1) - 1;
+    const int64_t ew = p->w + p->pad_left + p->pad_right - p->dil_w * (p->kw - 1) - 1;
+    B200ML_REQUIRE(eh >= 0 && ew >= 0, "conv: kernel larger than the padded input");
+    const int64_t oh = eh / p->stride_h + 1, ow = ew / p->stride_w + 1;
+    if (p->n == 0 || p->m == 0) return B200ML_OK;
+    ConvGeom g{(int32_t)p->n, (int32_t)p->c, (int32_t)p->h, (int32_t)p->w, (int32_t)p->m, (int32_t)p->kh,
+               (int32_t)p->kw, (int32_t)p->stride_h, (int32_t)p->stride_w, (int32_t)p->pad_top, (int32_t)p->pad_left,
+               (int32_t)p->dil_h, (int32_t)p->dil_w, (int32_t)p->group, (int32_t)oh, (int32_t)ow, p->act};
+    bool launched = false, pooled = false;
+    int rc = conv2d_fast(p, g, s, &launched, &pooled);
+    if (rc) return rc;
+    if (!launched) {
+        rc = p->dtype == B200ML_F32 ? launch_direct<float>(p, g, s) : launch_direct<__half>(p, g, s);
+        if (rc) return rc;
+    }
+    if (p->pool_sum && !pooled) {
+        B200ML_REQUIRE(p->dtype == B200ML_F32, "conv: fused GlobalAveragePool needs fp32 tensors");
+        return reduce(ctx, B200ML_F32, B200ML_RED_MEAN, p->y, p->pool_sum, p->n * p->m, oh * ow, 1, s);
+    }
+    return B200ML_OK;
+}
+
+int se_gate(const b200ml_ctx*, int dtype, const void* pooled, const void* w1, const void* b1, const void* w2,
+            const void* b2, void* gate, int64_t n, int64_t c, int64_t r, cudaStream_t s) {
+    if (n == 0 || c == 0) return B200ML_OK;
+    const size_t sm = (size_t)(c + r) * sizeof(float);
+    B200ML_REQUIRE(sm <= 48 * 1024, "se_gate: too many channels");
+    if (dtype == B200ML_F16)
+        se_gate_kernel<__half><<<(unsigned)n, 256, sm, s>>>((const __half*)pooled, (const __half*)w1, (const __half*)b1,
+                                                           (const __half*)w2, (const __half*)b2, (__half*)gate, (int)c, (int)r);
+    else
+        se_gate_kernel<float><<<(unsigned)n, 256, sm, s>>>((const float*)pooled, (const float*)w1, (const float*)b1,
+                                                          (const float*)w2, (const float*)b2, (float*)gate, (int)c, (int)r);
+    return check_launch("se_gate");
+}
+
+}  // namespace b200ml

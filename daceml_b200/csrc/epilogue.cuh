@@ -1,0 +1,88 @@
+// The element-wise tail shared by the GEMM and convolution kernels:
+//   out = act(alpha * acc + bias_scale * bias[n]) + residual_scale * residual[m, n]
+// All math is fp32; erf / exp are the full-precision libm versions (the reference strips
+// --use_fast_math because it produced NaNs in BERT, daceml/__init__.py:13-19).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/daceml_b200.h"
+
+namespace b200ml {
+
+struct EpilogueParams {
+    int32_t flags;
+    float alpha, bias_scale, residual_scale;
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ float apply_act(float v, int32_t flags) {
+    if (flags & B200ML_EPI_RELU) v = fmaxf(v, 0.0f);
+    if (flags & B200ML_EPI_GELU) v = gelu_erf(v);
+    if (flags & B200ML_EPI_SWISH) v = v * sigmoidf_(v);
+    return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 q;
+    __half2* h = reinterpret_cast<__half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return q;
+}
+
+// Finishes 32 consecutive columns [col0, col0 + 32) of one output row held as raw fp32 bits in r.
+__device__ __forceinline__ void epilogue_store_32(const EpilogueParams& ep, const uint32_t (&r)[32], __half* c_row,
+                                                  const __half* r_row, const __half* bias, int col0, int n, bool vec) {
+    const int valid = n - col0 < 32 ? n - col0 : 32;
+    const bool has_bias = (ep.flags & B200ML_EPI_BIAS) && bias != nullptr;
+    const bool has_res = (ep.flags & B200ML_EPI_RESIDUAL) && r_row != nullptr;
+    if (vec && valid == 32) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = ep.alpha * __uint_as_float(r[g * 8 + j]);
+            if (has_bias) {
+                float b[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8)), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = fmaf(ep.bias_scale, b[j], v[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], ep.flags);
+            if (has_res) {
+                float q[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8)), q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = fmaf(ep.residual_scale, q[j], v[j]);
+            }
+            *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(v);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (j < valid) {
+                float v = ep.alpha * __uint_as_float(r[j]);
+                if (has_bias) v = fmaf(ep.bias_scale, __half2float(bias[col0 + j]), v);
+                v = apply_act(v, ep.flags);
+                if (has_res) v = fmaf(ep.residual_scale, __half2float(r_row[col0 + j]), v);
+                c_row[col0 + j] = __float2half_rn(v);
+            }
+        }
+    }
+}
+
+}  // namespace b200ml

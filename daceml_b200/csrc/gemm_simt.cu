@@ -1,0 +1,174 @@
+// FP32-FMA GEMM for the fp32 configurations (rtol 1e-4 rules out single-pass TF32) and for fp16
+// operands whose layout the tensor-core kernel cannot address (unaligned leading dimensions,
+// transposed A, tiny outputs).  Arbitrary row/column strides, two batch loops, same epilogue.
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace b200ml {
+
+namespace {
+
+constexpr int SBM = 64, SBN = 64, SBK = 16, STHREADS = 256;
+
+template <typename T>
+struct SimtArgs {
+    int32_t m, n, k, batch_inner;
+    int64_t a_rs, a_cs, a_so, a_si;  // A(m,k) = a[m*a_rs + k*a_cs]
+    int64_t b_rs, b_cs, b_so, b_si;  // B(k,n) = b[k*b_rs + n*b_cs]
+    int64_t ldc, c_so, c_si;
+    int64_t ldr, r_so, r_si;
+    EpilogueParams ep;
+    const T* a;
+    const T* b;
+    const T* bias;
+    const T* residual;
+    T* c;
+};
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(const SimtArgs<T> g) {
+    __shared__ float As[SBK][SBM + 4];
+    __shared__ float Bs[SBK][SBN + 4];
+    const int tid = threadIdx.x;
+    const int batch = blockIdx.z;
+    const int bi = batch % g.batch_inner, bo = batch / g.batch_inner;
+    const int m0 = blockIdx.y * SBM, n0 = blockIdx.x * SBN;
+    const T* a = g.a + bo * g.a_so + bi * g.a_si;
+    const T* b = g.b + bo * g.b_so + bi * g.b_si;
+
+    // Thread-to-element maps for the tile loads: the contiguous axis of each operand goes to
+    // consecutive threads.
+    const bool a_k_contig = g.a_cs == 1;
+    const bool b_n_contig = g.b_cs == 1;
+
+    const int tx = tid & 15, ty = tid >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < g.k; k0 += SBK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int mm, kk;
+            if (a_k_contig) {
+                kk = tid & 15;
+                mm = (tid >> 4) + 16 * i;
+            } else {
+                mm = tid & 63;
+                kk = (tid >> 6) + 4 * i;
+            }
+            const int gm = m0 + mm, gk = k0 + kk;
+            As[kk][mm] = (gm < g.m && gk < g.k) ? to_f(a[gm * g.a_rs + gk * g.a_cs]) : 0.0f;
+            int nn, kb;
+            if (b_n_contig) {
+                nn = tid & 63;
+                kb = (tid >> 6) + 4 * i;
+            } else {
+                kb = tid & 15;
+                nn = (tid >> 4) + 16 * i;
+            }
+            const int gn = n0 + nn, gkb = k0 + kb;
+            Bs[kb][nn] = (gn < g.n && gkb < g.k) ? to_f(b[gkb * g.b_rs + gn * g.b_cs]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < SBK; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+            const float aa[4] = {av.x, av.y, av.z, av.w};
+            const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(aa[i], bb[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+    T* c = g.c + bo * g.c_so + bi * g.c_si;
+    const T* res = g.residual ? g.residual + bo * g.r_so + bi * g.r_si : nullptr;
+    const bool has_bias = (g.ep.flags & B200ML_EPI_BIAS) && g.bias;
+    const bool has_res = (g.ep.flags & B200ML_EPI_RESIDUAL) && res;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + ty * 4 + i;
+        if (gm >= g.m) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= g.n) continue;
+            float v = g.ep.alpha * acc[i][j];
+            if (has_bias) v = fmaf(g.ep.bias_scale, to_f(g.bias[gn]), v);
+            v = apply_act(v, g.ep.flags);
+            if (has_res) v = fmaf(g.ep.residual_scale, to_f(res[gm * g.ldr + gn]), v);
+            c[gm * g.ldc + gn] = from_f<T>(v);
+        }
+    }
+}
+
+template <typename T>
+int launch_simt(const b200ml_gemm_params* p, cudaStream_t stream) {
+    SimtArgs<T> g{};
+    g.m = (int32_t)p->m;
+    g.n = (int32_t)p->n;
+    g.k = (int32_t)p->k;
+    g.batch_inner = (int32_t)p->batch_inner;
+    if (p->a_layout == 0) {
+        g.a_rs = p->lda;
+        g.a_cs = 1;
+    } else {
+        g.a_rs = 1;
+        g.a_cs = p->lda;
+    }
+    if (p->b_layout == 0) {
+        g.b_rs = p->ldb;
+        g.b_cs = 1;
+    } else {
+        g.b_rs = 1;
+        g.b_cs = p->ldb;
+    }
+    g.a_so = p->a_stride_outer;
+    g.a_si = p->a_stride_inner;
+    g.b_so = p->b_stride_outer;
+    g.b_si = p->b_stride_inner;
+    g.ldc = p->ldc;
+    g.c_so = p->c_stride_outer;
+    g.c_si = p->c_stride_inner;
+    g.ldr = p->ldr;
+    g.r_so = p->r_stride_outer;
+    g.r_si = p->r_stride_inner;
+    g.ep.flags = p->epilogue;
+    g.ep.alpha = p->alpha;
+    g.ep.bias_scale = p->bias_scale;
+    g.ep.residual_scale = p->residual_scale;
+    g.a = static_cast<const T*>(p->a);
+    g.b = static_cast<const T*>(p->b);
+    g.bias = static_cast<const T*>(p->bias);
+    g.residual = static_cast<const T*>(p->residual);
+    g.c = static_cast<T*>(p->c);
+    const int64_t batches = p->batch_outer * p->batch_inner;
+    B200ML_REQUIRE(batches <= 65535 && ceil_div(p->m, SBM) <= 65535, "gemm: grid too large for the FP32-FMA kernel");
+    dim3 grid((unsigned)ceil_div(p->n, SBN), (unsigned)ceil_div(p->m, SBM), (unsigned)batches);
+    gemm_simt_kernel<T><<<grid, STHREADS, 0, stream>>>(g);
+    return check_launch("gemm_simt");
+}
+
+}  // namespace
+
+int gemm_f32(const b200ml_ctx*, const b200ml_gemm_params* p, cudaStream_t stream) { return launch_simt<float>(p, stream); }
+int gemm_f16_simt(const b200ml_ctx*, const b200ml_gemm_params* p, cudaStream_t stream) {
+    return launch_simt<__half>(p, stream);
+}
+
+}  // namespace b200ml

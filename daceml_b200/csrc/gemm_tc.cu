@@ -1,0 +1,391 @@
+// fp16 GEMM on the 5th-generation tensor cores: C[M,N] = epilogue(alpha * A[M,K] . B), fp32 accumulate.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: streams 128x64 A tiles and BNx64 B tiles (128-byte swizzle) through a
+//               ring of shared-memory stages, completion signalled on "full" mbarriers;
+//   warp 1      owns the TMEM allocation and issues tcgen05.mma (128 x BN x 16) from one elected
+//               thread; tcgen05.commit releases each stage ("empty") and publishes each finished
+//               accumulator ("tmem_full");
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (one TMEM lane = one output row per
+//               thread), apply alpha / bias / activation / residual, convert to fp16 and store.
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
+// the main loop of tile i+1.
+//
+// A is K-major ([M,K] row-major).  B is either K-major ([N,K] row-major, an nn.Linear weight or a
+// Gemm with transB=1) or MN-major ([K,N] row-major, the ONNX MatMul operand); both are fed to the
+// MMA directly, so no Transpose node has to run.  Two batch loops are folded into the TMA
+// coordinates, which lets attention read Q, K, V per head straight out of a packed [T, 3H] buffer.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "epilogue.cuh"
+
+namespace b200ml {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 fp16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmArgs {
+    int32_t m, n, k;
+    int32_t tiles_m, tiles_n, num_tiles;
+    int32_t batch_inner;
+    int32_t epilogue;
+    // 0 when the operand is broadcast over that batch loop (its TMA coordinate stays 0)
+    int32_t a_use_inner, a_use_outer, b_use_inner, b_use_outer;
+    int64_t ldc, c_so, c_si;
+    int64_t ldr, r_so, r_si;
+    float alpha, bias_scale, residual_scale;
+    int32_t vec_ok;  // C (and residual) rows are 16-byte aligned
+    __half* c;
+    const __half* bias;
+    const __half* residual;
+    int32_t* status;
+};
+
+template <int BN>
+struct GemmSmem {
+    static constexpr int B_TILE_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
+};
+
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmArgs args) {
+    using S = GemmSmem<BN>;
+    constexpr int STAGES = S::STAGES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;  // 128, 256 or 512: a power of two
+    constexpr uint32_t IDESC = ptx::make_idesc_f16(BM, BN, 0, B_MN ? 1 : 0);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full_bar = empty_bar + STAGES;
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_kb = (args.k + BK - 1) / BK;
+
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        if (lane == 0) {
+            for (int s = 0; s < STAGES; ++s) {
+                ptx::mbar_init(&full_bar[s], 1);
+                ptx::mbar_init(&empty_bar[s], 1);
+            }
+            for (int a = 0; a < 2; ++a) {
+                ptx::mbar_init(&tmem_full_bar[a], 1);
+                ptx::mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+            }
+            ptx::fence_mbar_init();
+        }
+        __syncwarp();
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
+                const int mt = tile % args.tiles_m;
+                const int rest = tile / args.tiles_m;
+                const int nt = rest % args.tiles_n;
+                const int batch = rest / args.tiles_n;
+                const int bi = batch % args.batch_inner;
+                const int bo = batch / args.batch_inner;
+                const int m0 = mt * BM, n0 = nt * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+                        atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + stage * S::STAGE_BYTES;
+                    uint8_t* sb = sa + A_TILE_BYTES;
+                    ptx::mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+                    ptx::tma_load_4d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, bi * args.a_use_inner,
+                                     bo * args.a_use_outer);
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + j * 64, kb * BK,
+                                             bi * args.b_use_inner, bo * args.b_use_outer);
+                    } else {
+                        ptx::tma_load_4d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, bi * args.b_use_inner,
+                                         bo * args.b_use_outer);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
+                if (!ptx::mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1)) {
+                    atomicExch(args.status, DEV_TIMEOUT_MMA);
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+                        atomicExch(args.status, DEV_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(smem + stage * S::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t a_desc = ptx::make_smem_desc_sw128(a_addr + kk * (UMMA_K * 2), 16, 1024);
+                        const uint64_t b_desc =
+                            B_MN ? ptx::make_smem_desc_sw128(b_addr + kk * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                 : ptx::make_smem_desc_sw128(b_addr + kk * (UMMA_K * 2), 16, 1024);
+                        ptx::mma_f16_ss(d_tmem, a_desc, b_desc, IDESC, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    ptx::mma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                ptx::mma_commit(&tmem_full_bar[acc]);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        EpilogueParams ep;
+        ep.flags = args.epilogue;
+        ep.alpha = args.alpha;
+        ep.bias_scale = args.bias_scale;
+        ep.residual_scale = args.residual_scale;
+        for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
+            const int mt = tile % args.tiles_m;
+            const int rest = tile / args.tiles_m;
+            const int nt = rest % args.tiles_n;
+            const int batch = rest / args.tiles_n;
+            const int bi = batch % args.batch_inner;
+            const int bo = batch / args.batch_inner;
+            const int row = mt * BM + row_in_tile;
+            const int n0 = nt * BN;
+            if (!ptx::mbar_wait(&tmem_full_bar[acc], acc_phase)) {
+                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                break;
+            }
+            ptx::tc_fence_after();
+            __half* c_row = args.c + bo * args.c_so + bi * args.c_si + static_cast<int64_t>(row) * args.ldc;
+            const __half* r_row = args.residual
+                                      ? args.residual + bo * args.r_so + bi * args.r_si + static_cast<int64_t>(row) * args.ldr
+                                      : nullptr;
+            const bool row_ok = row < args.m;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= args.n) break;  // warp-uniform
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
+                ptx::tmem_ld_wait();
+                if (row_ok) epilogue_store_32(ep, r, c_row, r_row, args.bias, col0, args.n, args.vec_ok != 0);
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        if (*reinterpret_cast<volatile int32_t*>(args.status) != DEV_OK) {
+            // A wait gave up: give copies and MMAs still in flight time to land before the
+            // tensor memory and shared memory are released.
+            for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        }
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// rank-4 fp16 tensor map {inner, rows, batch_inner, batch_outer} with a 128-byte-swizzled box.
+int make_tmap(const b200ml_ctx* ctx, CUtensorMap* out, const void* base, int64_t inner, int64_t rows, int64_t ld,
+              int64_t n_inner, int64_t s_inner, int64_t n_outer, int64_t s_outer, int box_inner, int box_rows,
+              const char* what) {
+    if (!aligned16(base)) return fail(B200ML_ERR_UNSUPPORTED, "gemm f16: %s base is not 16-byte aligned", what);
+    if (ld % 8 != 0) return fail(B200ML_ERR_UNSUPPORTED, "gemm f16: %s leading dimension %lld is not a multiple of 8", what, (long long)ld);
+    const bool use_i = n_inner > 1 && s_inner != 0;
+    const bool use_o = n_outer > 1 && s_outer != 0;
+    if ((use_i && s_inner % 8 != 0) || (use_o && s_outer % 8 != 0))
+        return fail(B200ML_ERR_UNSUPPORTED, "gemm f16: %s batch stride is not a multiple of 8 elements", what);
+    const uint64_t row_bytes = static_cast<uint64_t>(ld) * 2;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(use_i ? n_inner : 1), static_cast<cuuint64_t>(use_o ? n_outer : 1)};
+    // A size-1 dimension still needs a legal stride (non-zero multiple of 16 bytes).
+    const uint64_t dummy = row_bytes * static_cast<uint64_t>(rows);
+    cuuint64_t strides[3] = {row_bytes, use_i ? static_cast<uint64_t>(s_inner) * 2 : dummy,
+                             use_o ? static_cast<uint64_t>(s_outer) * 2 : dummy};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows), 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!fn) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d (dims %llu x %llu, ld %lld)", what,
+                    (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (long long)ld);
+    return B200ML_OK;
+}
+
+template <int BN, bool B_MN>
+int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, cudaStream_t stream) {
+    using S = GemmSmem<BN>;
+    auto kernel = gemm_f16_tc_kernel<BN, B_MN>;
+    static bool configured[64] = {};  // per instantiation and device
+    if (!configured[ctx->device & 63]) {
+        B200ML_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        configured[ctx->device & 63] = true;
+    }
+    const int grid = args.num_tiles < ctx->sm_count ? args.num_tiles : ctx->sm_count;
+    kernel<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, args);
+    return check_launch("gemm_f16_tc");
+}
+
+}  // namespace
+
+int gemm_f16_simt(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
+
+// Tile width: the widest N tile whose wave count does not waste more of the machine than a
+// narrower one would.  Time is proportional to waves * BN.
+static int pick_bn(int64_t m, int64_t n, int64_t batches, int sms) {
+    if (n <= 64) return 64;
+    if (n <= 128) return 128;
+    const int64_t tm = ceil_div(m, BM);
+    int best = 256;
+    int64_t best_cost = INT64_MAX;
+    const int cand[3] = {256, 128, 64};
+    for (int i = 0; i < 2; ++i) {  // 64-wide tiles only for narrow outputs
+        const int bn = cand[i];
+        const int64_t tiles = tm * ceil_div(n, bn) * batches;
+        const int64_t cost = ceil_div(tiles, sms) * bn + (bn == 128 ? bn / 8 : 0);  // mild preference for 256
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream) {
+    const int64_t batches = p->batch_outer * p->batch_inner;
+    // Operand layouts the tensor-core kernel cannot address go to the FP32-FMA kernel instead.
+    const bool a_ok = p->a_layout == 0 && aligned16(p->a) && p->lda % 8 == 0 && p->a_stride_inner % 8 == 0 &&
+                      p->a_stride_outer % 8 == 0;
+    const bool b_ok = aligned16(p->b) && p->ldb % 8 == 0 && p->b_stride_inner % 8 == 0 && p->b_stride_outer % 8 == 0;
+    if (!a_ok || !b_ok || p->m * p->n * batches < 64 * 64) return gemm_f16_simt(ctx, p, stream);
+
+    const int bn = pick_bn(p->m, p->n, batches, ctx->sm_count);
+    GemmArgs args{};
+    args.m = (int32_t)p->m;
+    args.n = (int32_t)p->n;
+    args.k = (int32_t)p->k;
+    args.tiles_m = (int32_t)ceil_div(p->m, BM);
+    args.tiles_n = (int32_t)ceil_div(p->n, bn);
+    const int64_t tiles = (int64_t)args.tiles_m * args.tiles_n * batches;
+    B200ML_REQUIRE(tiles < (1ll << 31), "gemm f16: too many tiles");
+    args.num_tiles = (int32_t)tiles;
+    args.batch_inner = (int32_t)p->batch_inner;
+    args.epilogue = p->epilogue;
+    args.a_use_inner = (p->batch_inner > 1 && p->a_stride_inner != 0) ? 1 : 0;
+    args.a_use_outer = (p->batch_outer > 1 && p->a_stride_outer != 0) ? 1 : 0;
+    args.b_use_inner = (p->batch_inner > 1 && p->b_stride_inner != 0) ? 1 : 0;
+    args.b_use_outer = (p->batch_outer > 1 && p->b_stride_outer != 0) ? 1 : 0;
+    args.ldc = p->ldc;
+    args.c_so = p->c_stride_outer;
+    args.c_si = p->c_stride_inner;
+    args.ldr = p->ldr;
+    args.r_so = p->r_stride_outer;
+    args.r_si = p->r_stride_inner;
+    args.alpha = p->alpha;
+    args.bias_scale = p->bias_scale;
+    args.residual_scale = p->residual_scale;
+    args.c = static_cast<__half*>(p->c);
+    args.bias = static_cast<const __half*>(p->bias);
+    args.residual = static_cast<const __half*>(p->residual);
+    args.status = ctx->status_dev;
+    bool vec = aligned16(p->c) && p->ldc % 8 == 0 && p->c_stride_inner % 8 == 0 && p->c_stride_outer % 8 == 0;
+    if (p->residual)
+        vec = vec && aligned16(p->residual) && p->ldr % 8 == 0 && p->r_stride_inner % 8 == 0 && p->r_stride_outer % 8 == 0;
+    if (p->bias) vec = vec && aligned16(p->bias);
+    args.vec_ok = vec ? 1 : 0;
+
+    CUtensorMap ta, tb;
+    int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, p->batch_inner, p->a_stride_inner, p->batch_outer,
+                       p->a_stride_outer, BK, BM, "A");
+    if (rc) return rc;
+    if (p->b_layout == 1) {
+        rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, p->batch_inner, p->b_stride_inner, p->batch_outer,
+                       p->b_stride_outer, BK, bn, "B");
+        if (rc) return rc;
+        switch (bn) {
+            case 256: return launch<256, false>(ctx, ta, tb, args, stream);
+            case 128: return launch<128, false>(ctx, ta, tb, args, stream);
+            default: return launch<64, false>(ctx, ta, tb, args, stream);
+        }
+    } else {
+        rc = make_tmap(ctx, &tb, p->b, p->n, p->k, p->ldb, p->batch_inner, p->b_stride_inner, p->batch_outer,
+                       p->b_stride_outer, 64, BK, "B");
+        if (rc) return rc;
+        switch (bn) {
+            case 256: return launch<256, true>(ctx, ta, tb, args, stream);
+            case 128: return launch<128, true>(ctx, ta, tb, args, stream);
+            default: return launch<64, true>(ctx, ta, tb, args, stream);
+        }
+    }
+}
+
+}  // namespace b200ml

@@ -1,0 +1,506 @@
+// Bandwidth-bound row kernels: (scale + mask +) Softmax / LogSoftmax, (residual + bias +) LayerNorm
+// and the Reduce* family.  A row lives in one warp's registers whenever it fits: 128-bit coalesced
+// loads, fp32 math, warp-shuffle reductions, one read and one write of HBM per element.
+#include "common.cuh"
+#include "epilogue.cuh"
+#include <float.h>
+
+namespace b200ml {
+
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(FULL, v, o));
+    return v;
+}
+
+// A 16-byte packet of T: 8 halves or 4 floats.
+template <typename T>
+struct Vec;
+template <>
+struct Vec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __half* p, float (&f)[8]) {
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p)), f);
+    }
+    static __device__ __forceinline__ void store(__half* p, const float (&f)[8]) {
+        *reinterpret_cast<uint4*>(p) = pack8(f);
+    }
+};
+template <>
+struct Vec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+        f[0] = q.x, f[1] = q.y, f[2] = q.z, f[3] = q.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&f)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    }
+};
+
+__device__ __forceinline__ float ld1(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float ld1(const __half* p) { return __half2float(__ldg(p)); }
+__device__ __forceinline__ void st1(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st1(__half* p, float v) { *p = __float2half_rn(v); }
+
+// exp for the softmax numerator.  fp16 outputs carry 11 significant bits, so exp2f on a
+// pre-scaled argument is ample there; fp32 outputs use expf.
+template <typename T>
+__device__ __forceinline__ float softmax_exp(float d);
+template <>
+__device__ __forceinline__ float softmax_exp<__half>(float d) { return exp2f(d * 1.44269504088896340736f); }
+template <>
+__device__ __forceinline__ float softmax_exp<float>(float d) { return expf(d); }
+
+// ---------------------------------------------------------------------------------------------
+// Softmax: one warp per row, the row held in registers (ITERS packets per lane).
+// ---------------------------------------------------------------------------------------------
+template <typename T, int ITERS>
+__global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__ x, const T* __restrict__ mask,
+                                                           T* __restrict__ y, int64_t rows, int cols,
+                                                           int64_t mask_row_div, float scale, int is_log) {
+    constexpr int V = Vec<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const T* xr = x + row * cols;
+    const T* mr = mask ? mask + (row / mask_row_div) * cols : nullptr;
+    float v[ITERS][V];
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < cols) {
+            Vec<T>::load(xr + c, v[it]);
+            if (mr) {
+                float mv[V];
+                Vec<T>::load(mr + c, mv);
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[it][j] = fmaf(v[it][j], scale, mv[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[it][j] *= scale;
+            }
+#pragma unroll
+            for (int j = 0; j < V; ++j) mx = fmaxf(mx, v[it][j]);
+        }
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < cols) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const float d = v[it][j] - mx;
+                const float e = softmax_exp<T>(d);
+                sum += e;
+                v[it][j] = is_log ? d : e;
+            }
+        }
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    const float lse = logf(sum);
+    T* yr = y + row * cols;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < cols) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[it][j] = is_log ? v[it][j] - lse : v[it][j] * inv;
+            Vec<T>::store(yr + c, v[it]);
+        }
+    }
+}
+
+// Any row length / alignment: one block per row, three passes over the row (it stays in L1/L2).
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_block_kernel(const T* __restrict__ x, const T* __restrict__ mask,
+                                                            T* __restrict__ y, int64_t cols, int64_t mask_row_div,
+                                                            float scale, int is_log) {
+    __shared__ float red[8];
+    __shared__ float bcast;
+    const int64_t row = blockIdx.x;
+    const T* xr = x + row * cols;
+    const T* mr = mask ? mask + (row / mask_row_div) * cols : nullptr;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float mx = -FLT_MAX;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = ld1(xr + c) * scale + (mr ? ld1(mr + c) : 0.0f);
+        mx = fmaxf(mx, v);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = red[0];
+        for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+        bcast = m;
+    }
+    __syncthreads();
+    mx = bcast;
+    float sum = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float v = ld1(xr + c) * scale + (mr ? ld1(mr + c) : 0.0f);
+        sum += softmax_exp<T>(v - mx);
+    }
+    sum = warp_sum(sum);
+    __syncthreads();
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        for (int i = 0; i < 8; ++i) s += red[i];
+        bcast = s;
+    }
+    __syncthreads();
+    sum = bcast;
+    const float inv = 1.0f / sum, lse = logf(sum);
+    T* yr = y + row * cols;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float d = ld1(xr + c) * scale + (mr ? ld1(mr + c) : 0.0f) - mx;
+        st1(yr + c, is_log ? d - lse : softmax_exp<T>(d) * inv);
+    }
+}
+
+template <typename T>
+int softmax_t(const T* x, const T* mask, T* y, int64_t rows, int64_t cols, int64_t mask_row_div, float scale,
+              int is_log, cudaStream_t stream) {
+    constexpr int V = Vec<T>::N;
+    const bool vec = cols % V == 0 && aligned16(x) && aligned16(y) && (!mask || aligned16(mask));
+    const int64_t packets = cols / V;
+    if (vec && packets <= 32 * 8) {
+        const int warps = 8;
+        const int64_t blocks = ceil_div(rows, warps);
+        B200ML_REQUIRE(blocks < (1ll << 31), "softmax: too many rows");
+        const int iters = (int)ceil_div(packets, 32);
+#define SM_LAUNCH(I)                                                                                          \
+    softmax_warp_kernel<T, I><<<(unsigned)blocks, warps * 32, 0, stream>>>(x, mask, y, rows, (int)cols, mask_row_div, \
+                                                                         scale, is_log)
+        if (iters <= 1) SM_LAUNCH(1);
+        else if (iters <= 2) SM_LAUNCH(2);
+        else if (iters <= 4) SM_LAUNCH(4);
+        else SM_LAUNCH(8);
+#undef SM_LAUNCH
+        return check_launch("softmax_warp");
+    }
+    B200ML_REQUIRE(rows < (1ll << 31), "softmax: too many rows");
+    softmax_block_kernel<T><<<(unsigned)rows, 256, 0, stream>>>(x, mask, y, cols, mask_row_div, scale, is_log);
+    return check_launch("softmax_block");
+}
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm over the last axis of v = x (+ residual) (+ bias): mean, then the mean of squared
+// deviations (two passes over registers, as the ReduceMean/Sub/Pow/ReduceMean chain does),
+// eps added in fp32 (1e-12 underflows in fp16).
+// ---------------------------------------------------------------------------------------------
+template <typename T, int ITERS>
+__global__ void __launch_bounds__(128) layernorm_warp_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                                                             const T* __restrict__ bias, const T* __restrict__ gamma,
+                                                             const T* __restrict__ beta, T* __restrict__ y,
+                                                             int64_t rows, int cols, float eps) {
+    constexpr int V = Vec<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const T* xr = x + row * cols;
+    const T* rr = residual ? residual + row * cols : nullptr;
+    float v[ITERS][V];
+    float sum = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < cols) {
+            Vec<T>::load(xr + c, v[it]);
+            if (rr) {
+                float t[V];
+                Vec<T>::load(rr + c, t);
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[it][j] += t[j];
+            }
+            if (bias) {
+                float t[V];
+                Vec<T>::load(bias + c, t);
+#pragma unroll
+                for (int j = 0; j < V; ++j) v[it][j] += t[j];
+            }
+#pragma unroll
+            for (int j = 0; j < V; ++j) sum += v[it][j];
+        }
+    }
+    const float mean = warp_sum(sum) / cols;
+    float sq = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < cols) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                v[it][j] -= mean;
+                sq = fmaf(v[it][j], v[it][j], sq);
+            }
+        }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / cols + eps);
+    T* yr = y + row * cols;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * 32 + lane) * V;
+        if (c < cols) {
+            float gm[V], bt[V];
+            if (gamma) Vec<T>::load(gamma + c, gm);
+            if (beta) Vec<T>::load(beta + c, bt);
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                float o = v[it][j] * rstd;
+                if (gamma) o *= gm[j];
+                if (beta) o += bt[j];
+                v[it][j] = o;
+            }
+            Vec<T>::store(yr + c, v[it]);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_block_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                                                              const T* __restrict__ bias, const T* __restrict__ gamma,
+                                                              const T* __restrict__ beta, T* __restrict__ y,
+                                                              int64_t cols, float eps) {
+    __shared__ float red[8];
+    __shared__ float bcast;
+    const int64_t row = blockIdx.x;
+    const T* xr = x + row * cols;
+    const T* rr = residual ? residual + row * cols : nullptr;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    auto value = [&](int64_t c) { return ld1(xr + c) + (rr ? ld1(rr + c) : 0.0f) + (bias ? ld1(bias + c) : 0.0f); };
+    float s = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += value(c);
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < 8; ++i) t += red[i];
+        bcast = t / cols;
+    }
+    __syncthreads();
+    const float mean = bcast;
+    float sq = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float d = value(c) - mean;
+        sq = fmaf(d, d, sq);
+    }
+    sq = warp_sum(sq);
+    __syncthreads();
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < 8; ++i) t += red[i];
+        bcast = 1.0f / sqrtf(t / cols + eps);
+    }
+    __syncthreads();
+    const float rstd = bcast;
+    T* yr = y + row * cols;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        float o = (value(c) - mean) * rstd;
+        if (gamma) o *= ld1(gamma + c);
+        if (beta) o += ld1(beta + c);
+        st1(yr + c, o);
+    }
+}
+
+template <typename T>
+int layernorm_t(const T* x, const T* residual, const T* bias, const T* gamma, const T* beta, T* y, int64_t rows,
+                int64_t cols, float eps, cudaStream_t stream) {
+    constexpr int V = Vec<T>::N;
+    const bool vec = cols % V == 0 && aligned16(x) && aligned16(y) && (!residual || aligned16(residual)) &&
+                     (!bias || aligned16(bias)) && (!gamma || aligned16(gamma)) && (!beta || aligned16(beta));
+    const int64_t packets = cols / V;
+    if (vec && packets <= 32 * 8) {
+        const int warps = 4;
+        const int64_t blocks = ceil_div(rows, warps);
+        B200ML_REQUIRE(blocks < (1ll << 31), "layernorm: too many rows");
+        const int iters = (int)ceil_div(packets, 32);
+#define LN_LAUNCH(I)                                                                                               \
+    layernorm_warp_kernel<T, I><<<(unsigned)blocks, warps * 32, 0, stream>>>(x, residual, bias, gamma, beta, y, rows, \
+                                                                           (int)cols, eps)
+        if (iters <= 1) LN_LAUNCH(1);
+        else if (iters <= 2) LN_LAUNCH(2);
+        else if (iters <= 4) LN_LAUNCH(4);
+        else LN_LAUNCH(8);
+#undef LN_LAUNCH
+        return check_launch("layernorm_warp");
+    }
+    B200ML_REQUIRE(rows < (1ll << 31), "layernorm: too many rows");
+    layernorm_block_kernel<T><<<(unsigned)rows, 256, 0, stream>>>(x, residual, bias, gamma, beta, y, cols, eps);
+    return check_launch("layernorm_block");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Reduce over the middle extent of [outer, reduce, inner]
+// ---------------------------------------------------------------------------------------------
+struct RedOp {
+    int op;
+    __device__ __forceinline__ float init() const {
+        return op == B200ML_RED_MAX ? -FLT_MAX : (op == B200ML_RED_MIN ? FLT_MAX : 0.0f);
+    }
+    __device__ __forceinline__ float combine(float a, float b) const {
+        return op == B200ML_RED_MAX ? fmaxf(a, b) : (op == B200ML_RED_MIN ? fminf(a, b) : a + b);
+    }
+    __device__ __forceinline__ float warp(float v) const {
+        return op == B200ML_RED_MAX ? warp_max(v) : (op == B200ML_RED_MIN ? warp_min(v) : warp_sum(v));
+    }
+    __device__ __forceinline__ float finish(float v, int64_t n) const { return op == B200ML_RED_MEAN ? v / n : v; }
+};
+
+// inner == 1: contiguous rows.  One block per (row, slice); slices > 1 writes partials to scratch.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                          float* __restrict__ partial, int64_t reduce, int slices,
+                                                          RedOp op) {
+    __shared__ float red[8];
+    const int64_t row = blockIdx.x;
+    const int slice = blockIdx.y;
+    const int64_t per = (reduce + slices - 1) / slices;
+    const int64_t lo = slice * per, hi = lo + per < reduce ? lo + per : reduce;
+    const T* xr = x + row * reduce;
+    float v = op.init();
+    for (int64_t c = lo + threadIdx.x; c < hi; c += blockDim.x) v = op.combine(v, ld1(xr + c));
+    v = op.warp(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = red[0];
+        for (int i = 1; i < (int)(blockDim.x >> 5); ++i) t = op.combine(t, red[i]);
+        if (slices == 1) st1(y + row, op.finish(t, reduce));
+        else partial[row * slices + slice] = t;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_finish_kernel(const float* __restrict__ partial, T* __restrict__ y,
+                                                            int64_t rows, int slices, int64_t reduce, RedOp op) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float v = op.init();
+    for (int s = lane; s < slices; s += 32) v = op.combine(v, partial[row * slices + s]);
+    v = op.warp(v);
+    if (lane == 0) st1(y + row, op.finish(v, reduce));
+}
+
+// One warp per short contiguous row (GlobalAveragePool: rows of H*W).
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_rows_warp_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                               int64_t rows, int64_t reduce, RedOp op) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const T* xr = x + row * reduce;
+    float v = op.init();
+    for (int64_t c = lane; c < reduce; c += 32) v = op.combine(v, ld1(xr + c));
+    v = op.warp(v);
+    if (lane == 0) st1(y + row, op.finish(v, reduce));
+}
+
+// inner > 1: thread per (outer, inner) column, coalesced across inner.
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_cols_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t outer,
+                                                          int64_t reduce, int64_t inner, RedOp op) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= outer * inner) return;
+    const int64_t o = idx / inner, i = idx % inner;
+    const T* p = x + o * reduce * inner + i;
+    float v = op.init();
+    for (int64_t r = 0; r < reduce; ++r) v = op.combine(v, ld1(p + r * inner));
+    st1(y + idx, op.finish(v, reduce));
+}
+
+template <typename T>
+int reduce_t(const b200ml_ctx* ctx, int opcode, const T* x, T* y, int64_t outer, int64_t reduce, int64_t inner,
+             cudaStream_t stream) {
+    RedOp op{opcode};
+    if (outer * inner == 0) return B200ML_OK;
+    B200ML_REQUIRE(reduce > 0, "reduce: empty reduction extent");
+    if (inner == 1) {
+        if (reduce <= 4096) {
+            const int64_t blocks = ceil_div(outer, 8);
+            B200ML_REQUIRE(blocks < (1ll << 31), "reduce: too many rows");
+            reduce_rows_warp_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(x, y, outer, reduce, op);
+            return check_launch("reduce_rows_warp");
+        }
+        // Long rows: cut each row into slices so that a full-tensor reduction still fills the GPU.
+        int slices = 1;
+        const int64_t want = 4ll * ctx->sm_count;
+        if (outer < want) {
+            slices = (int)((want + outer - 1) / outer);
+            const int64_t max_by_len = reduce / 2048 > 0 ? reduce / 2048 : 1;
+            if (slices > max_by_len) slices = (int)max_by_len;
+            if (slices > 1024) slices = 1024;
+        }
+        B200ML_REQUIRE(outer < (1ll << 31), "reduce: too many rows");
+        if (slices == 1) {
+            reduce_rows_kernel<T><<<dim3((unsigned)outer, 1), 256, 0, stream>>>(x, y, nullptr, reduce, 1, op);
+            return check_launch("reduce_rows");
+        }
+        const int64_t need = outer * slices * (int64_t)sizeof(float);
+        if (need > ctx->workspace_bytes)
+            return fail(B200ML_ERR_WORKSPACE, "reduce: needs %lld bytes of scratch, the context has %lld",
+                        (long long)need, (long long)ctx->workspace_bytes);
+        float* partial = static_cast<float*>(ctx->workspace);
+        reduce_rows_kernel<T><<<dim3((unsigned)outer, (unsigned)slices), 256, 0, stream>>>(x, y, partial, reduce, slices, op);
+        int rc = check_launch("reduce_rows");
+        if (rc) return rc;
+        reduce_finish_kernel<T><<<(unsigned)ceil_div(outer, 8), 256, 0, stream>>>(partial, y, outer, slices, reduce, op);
+        return check_launch("reduce_finish");
+    }
+    const int64_t blocks = ceil_div(outer * inner, 256);
+    B200ML_REQUIRE(blocks < (1ll << 31), "reduce: too many outputs");
+    reduce_cols_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(x, y, outer, reduce, inner, op);
+    return check_launch("reduce_cols");
+}
+
+}  // namespace
+
+int softmax(int dtype, const void* x, const void* mask, void* y, int64_t rows, int64_t cols, int64_t mask_row_div,
+            float scale, int is_log, cudaStream_t s) {
+    if (dtype == B200ML_F16)
+        return softmax_t<__half>((const __half*)x, (const __half*)mask, (__half*)y, rows, cols, mask_row_div, scale, is_log, s);
+    return softmax_t<float>((const float*)x, (const float*)mask, (float*)y, rows, cols, mask_row_div, scale, is_log, s);
+}
+
+int layernorm(int dtype, const void* x, const void* residual, const void* bias, const void* gamma, const void* beta,
+              void* y, int64_t rows, int64_t cols, float eps, cudaStream_t s) {
+    if (dtype == B200ML_F16)
+        return layernorm_t<__half>((const __half*)x, (const __half*)residual, (const __half*)bias, (const __half*)gamma,
+                                   (const __half*)beta, (__half*)y, rows, cols, eps, s);
+    return layernorm_t<float>((const float*)x, (const float*)residual, (const float*)bias, (const float*)gamma,
+                              (const float*)beta, (float*)y, rows, cols, eps, s);
+}
+
+int reduce(const b200ml_ctx* ctx, int dtype, int op, const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
+           cudaStream_t s) {
+    if (dtype == B200ML_F16) return reduce_t<__half>(ctx, op, (const __half*)x, (__half*)y, outer, red, inner, s);
+    return reduce_t<float>(ctx, op, (const float*)x, (float*)y, outer, red, inner, s);
+}
+
+}  // namespace b200ml

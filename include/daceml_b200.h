@@ -1,0 +1,256 @@
+/*
+ * daceml_b200.h -- C ABI of libdaceml_b200.so
+ *
+ * A B200 (sm_100a) implementation of the forward path of DaCeML's ONNX operator
+ * library nodes.  Every entry point below is what a DaCeML expansion
+ * (an ONNXForward subclass registered with @op_implementation) binds instead of
+ * returning a nested SDFG: the expansion hands over raw device pointers, extents
+ * and attributes, exactly as the reference's generated tasklets hand them to
+ * cuDNN or ONNX Runtime.
+ *
+ * Conventions (borrowed from the reference where it has one):
+ *   - Tensors are C-contiguous unless a stride argument says otherwise; the
+ *     caller owns all memory and pre-allocates outputs
+ *     (daceml/onnx/onnx_importer.py:585-590, daceml/torch/dispatchers/ctypes_module.py:58-67).
+ *   - One context per (process, device), the analogue of
+ *     daceml::cudnn::CudnnHandle::Get(device) (daceml/onnx/include/daceml_cudnn.h:41-62).
+ *     A context is not thread-safe.
+ *   - Kernels are enqueued on the stream passed in and never synchronise the host
+ *     (the reference sets state.nosync, daceml/torch/dispatchers/cpp_torch_extension.py:474-475).
+ *   - Every function returns 0 on success or a negative b200ml_status; the message
+ *     is available from b200ml_last_error().  Nothing prints-and-exits as
+ *     __ort_check_status does (daceml/onnx/include/dace_onnx.h:7-15).
+ *   - Device-side waits are bounded.  A kernel that gave up records a code in the
+ *     context's status word, readable with b200ml_ctx_device_status() after the
+ *     stream has been synchronised.
+ */
+#ifndef DACEML_B200_H
+#define DACEML_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200ml_ctx b200ml_ctx;
+typedef void* b200ml_stream; /* a cudaStream_t */
+
+typedef enum {
+    B200ML_OK = 0,
+    B200ML_ERR_INVALID = -1,     /* bad argument (null pointer, negative extent, misaligned) */
+    B200ML_ERR_UNSUPPORTED = -2, /* valid ONNX, but no kernel here: the expansion must say "cannot be applied" */
+    B200ML_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
+    B200ML_ERR_DEVICE = -4,      /* a kernel recorded a device-side error (bounded wait ran out) */
+    B200ML_ERR_WORKSPACE = -5    /* the context's scratch buffer is too small */
+} b200ml_status;
+
+typedef enum { B200ML_F16 = 0, B200ML_F32 = 1 } b200ml_dtype;
+
+/* ------------------------------------------------------------------------- */
+/* Context and errors                                                         */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces CudnnHandle::Get(device) (daceml/onnx/include/daceml_cudnn.h:41-62) and the
+ * per-SDFG init code of daceml/onnx/environments/cudnn.py:33-49.  Allocates the
+ * context's scratch buffer (workspace_bytes, may be 0) and its status word. */
+int b200ml_ctx_create(int device, int64_t workspace_bytes, b200ml_ctx** out);
+int b200ml_ctx_destroy(b200ml_ctx* ctx);
+/* Reads (and clears) the device status word.  Call after synchronising the stream. */
+int b200ml_ctx_device_status(b200ml_ctx* ctx, int32_t* status);
+int64_t b200ml_ctx_workspace_bytes(const b200ml_ctx* ctx);
+/* Replaces __ort_check_status / CheckCudnnError (dace_onnx.h:7-15, daceml_cudnn.h:17-24). */
+const char* b200ml_last_error(void);
+int b200ml_version(void);
+/* Number of kernels this library has launched in the calling process (all contexts). */
+int64_t b200ml_launch_count(void);
+
+/* ------------------------------------------------------------------------- */
+/* MatMul / Gemm / Einsum-as-matmul                                           */
+/* ------------------------------------------------------------------------- */
+
+/* Epilogue: out = act(alpha * (A.B) + bias_scale * bias[n]) + residual_scale * residual[m, n] */
+enum {
+    B200ML_EPI_BIAS = 1,
+    B200ML_EPI_RELU = 2,
+    B200ML_EPI_GELU = 4, /* 0.5 x (1 + erf(x / sqrt 2)), the Div/Erf/Add/Mul/Mul chain */
+    B200ML_EPI_RESIDUAL = 8,
+    B200ML_EPI_SWISH = 16 /* x * sigmoid(x), the Sigmoid/Mul pair */
+};
+
+typedef struct {
+    int32_t dtype;    /* B200ML_F16: tcgen05 tensor cores, fp32 accumulate, fp16 in/out.
+                         B200ML_F32: FP32 FMA (no TF32 rounding). */
+    int32_t a_layout; /* 0: A is [M,K] row-major. 1: A is stored [K,M] (Gemm transA=1); F32 only. */
+    int32_t b_layout; /* 0: B is [K,N] row-major (ONNX MatMul). 1: B is stored [N,K] (Gemm transB=1, nn.Linear weight). */
+    int32_t epilogue; /* B200ML_EPI_* flags */
+    int64_t m, n, k;
+    int64_t batch_outer, batch_inner; /* two batch loops (e.g. B and heads); 1 when unused */
+    /* element strides: leading dimension, then per batch loop (0 broadcasts an operand) */
+    int64_t lda, a_stride_outer, a_stride_inner;
+    int64_t ldb, b_stride_outer, b_stride_inner;
+    int64_t ldc, c_stride_outer, c_stride_inner;
+    int64_t ldr, r_stride_outer, r_stride_inner;
+    float alpha, bias_scale, residual_scale;
+    int32_t reserved;
+    const void* a;
+    const void* b;
+    const void* bias;     /* [N] or null */
+    const void* residual; /* [M,N] with ldr, or null */
+    void* c;
+} b200ml_gemm_params;
+
+/* Replaces PureMatMul / PureEinsum / PureGemm and the BLAS library node they lower to
+ * (daceml/onnx/op_implementations/pure_implementations.py:111-252, 380-553). */
+int b200ml_gemm(b200ml_ctx* ctx, const b200ml_gemm_params* p, b200ml_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Row-wise kernels                                                           */
+/* ------------------------------------------------------------------------- */
+
+/* y[r,:] = softmax(scale * x[r,:] + mask[r / mask_row_div, :]) over contiguous rows
+ * (log_softmax when is_log != 0).  mask may be null.  Replaces Softmax / LogSoftmax
+ * (pure_implementations.py:309-319, 649-656) and the Mul(0.125) / Add(mask) nodes in front. */
+int b200ml_softmax(b200ml_ctx* ctx, int32_t dtype, const void* x, const void* mask, void* y,
+                   int64_t rows, int64_t cols, int64_t mask_row_div, float scale, int32_t is_log,
+                   b200ml_stream stream);
+
+/* y = (v - mean(v)) / sqrt(mean((v-mean)^2) + eps) * gamma + beta with v = x (+ residual) (+ bias[cols]).
+ * Replaces the ReduceMean/Sub/Pow/ReduceMean/Add/Sqrt/Div/Mul/Add chain
+ * (pure_implementations.py:34-41, 76-103) and the residual Add in front of it. */
+int b200ml_layernorm(b200ml_ctx* ctx, int32_t dtype, const void* x, const void* residual,
+                     const void* bias, const void* gamma, const void* beta, void* y, int64_t rows,
+                     int64_t cols, float eps, b200ml_stream stream);
+
+typedef enum { B200ML_RED_SUM = 0, B200ML_RED_MEAN = 1, B200ML_RED_MAX = 2, B200ML_RED_MIN = 3 } b200ml_reduce_op;
+
+/* x viewed as [outer, reduce, inner]; y[outer, inner] = op over the middle extent.
+ * Replaces ReduceSum/Mean/Max/Min (pure_implementations.py:101-103, 294-306) and
+ * GlobalAveragePool (img_op_implementations.py:415-526). */
+int b200ml_reduce(b200ml_ctx* ctx, int32_t dtype, int32_t op, const void* x, void* y, int64_t outer,
+                  int64_t reduce, int64_t inner, b200ml_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Element-wise kernels                                                       */
+/* ------------------------------------------------------------------------- */
+
+typedef enum {
+    B200ML_UN_COPY = 0,
+    B200ML_UN_RELU = 1,
+    B200ML_UN_SIGMOID = 2,
+    B200ML_UN_ERF = 3,
+    B200ML_UN_SQRT = 4,
+    B200ML_UN_EXP = 5,
+    B200ML_UN_LOG = 6,
+    B200ML_UN_TANH = 7,
+    B200ML_UN_SWISH = 8,      /* x * sigmoid(x) */
+    B200ML_UN_GELU = 9,       /* erf form */
+    B200ML_UN_RECIPROCAL = 10,
+    B200ML_UN_LEAKYRELU = 11, /* max(x,0) + p0 * min(x,0) */
+    B200ML_UN_AFFINE = 12,    /* p0 * x + p1 */
+    B200ML_UN_POWS = 13,      /* x ** p0 */
+    B200ML_UN_SOFTPLUS = 14,
+    B200ML_UN_CLIP = 15,      /* min(max(x, p0), p1) */
+    B200ML_UN_NEG = 16,
+    B200ML_UN_ABS = 17
+} b200ml_unary_op;
+
+/* Replaces the dace.elementwise bodies of pure_implementations.py:24-36, 106-108, 283-291,
+ * 556-568, 736-743. */
+int b200ml_unary(b200ml_ctx* ctx, int32_t dtype, int32_t op, const void* x, void* y, int64_t n,
+                 float p0, float p1, b200ml_stream stream);
+
+typedef enum {
+    B200ML_BIN_ADD = 0,
+    B200ML_BIN_SUB = 1,
+    B200ML_BIN_MUL = 2,
+    B200ML_BIN_DIV = 3,
+    B200ML_BIN_POW = 4,
+    B200ML_BIN_MAX = 5,
+    B200ML_BIN_MIN = 6
+} b200ml_binary_op;
+
+/* Numpy-broadcast binary op.  shape is the output shape (rank <= 6); a_strides / b_strides are
+ * element strides of the operands in that shape, 0 on broadcast dimensions.  Replaces
+ * Add/Sub/Mul/Div/Pow (pure_implementations.py:39-41, 76-93). */
+int b200ml_binary(b200ml_ctx* ctx, int32_t dtype, int32_t op, const void* a, const void* b, void* y,
+                  int32_t rank, const int64_t* shape, const int64_t* a_strides,
+                  const int64_t* b_strides, b200ml_stream stream);
+
+/* y[r,c] = act(x[r,c] + bias[c]) (+ residual[r,c]); act is a B200ML_EPI_* activation flag or 0.
+ * The stand-alone form of the GEMM epilogue (bias Add followed by Relu / the GELU chain). */
+int b200ml_bias_act(b200ml_ctx* ctx, int32_t dtype, const void* x, const void* bias,
+                    const void* residual, void* y, int64_t rows, int64_t cols, int32_t act,
+                    b200ml_stream stream);
+
+/* y = permute(x, perm) for elements of elem_bytes (2 or 4), rank <= 6.  Replaces Transpose and
+ * EinsumTranspose (pure_implementations.py:322-326, 746-778). */
+int b200ml_transpose(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void* y, int32_t rank,
+                     const int64_t* shape, const int32_t* perm, b200ml_stream stream);
+
+/* Replaces Cast (pure_implementations.py:329-377) for the two floating types used here. */
+int b200ml_cast(b200ml_ctx* ctx, int32_t src_dtype, int32_t dst_dtype, const void* x, void* y,
+                int64_t n, b200ml_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Convolution and squeeze-excite                                             */
+/* ------------------------------------------------------------------------- */
+
+typedef struct {
+    int32_t dtype; /* B200ML_F32 (B200ML_F16 storage with fp32 accumulate also accepted) */
+    int32_t act;   /* 0, B200ML_EPI_RELU or B200ML_EPI_SWISH applied after bias */
+    int64_t n, c, h, w;  /* X is [n, c, h, w] */
+    int64_t m, kh, kw;   /* W is [m, c / group, kh, kw] */
+    int64_t stride_h, stride_w;
+    int64_t pad_top, pad_left, pad_bottom, pad_right;
+    int64_t dil_h, dil_w;
+    int64_t group;
+    const void* x;
+    const void* weight;   /* [m, c / group, kh, kw] */
+    const void* bias;     /* [m] or null */
+    const void* gate;     /* [n, c] or null: X is multiplied by gate[n, c] on load (squeeze-excite) */
+    const void* residual; /* [n, m, oh, ow] or null, added after act */
+    void* y;              /* [n, m, oh, ow] */
+    float* pool_sum;      /* [n, m] or null: receives the mean of y over (oh, ow) (GlobalAveragePool fused) */
+} b200ml_conv_params;
+
+/* ONNX Conv (cross-correlation, NCHW).  Replaces PureConv2D (img_op_implementations.py:164-330)
+ * for stride 1 / no pad / group 1, and CudnnConvolution (cudnn_implementations.py:123-410) for
+ * strided, padded and grouped convolutions. */
+int b200ml_conv2d(b200ml_ctx* ctx, const b200ml_conv_params* p, b200ml_stream stream);
+
+/* gate[n, c] = sigmoid(W2 . swish(W1 . pooled[n, :] + b1) + b2): the two 1x1 convolutions of a
+ * squeeze-excite block on a [n, c, 1, 1] tensor.  w1 is [r, c], w2 is [c, r]. */
+int b200ml_se_gate(b200ml_ctx* ctx, int32_t dtype, const void* pooled, const void* w1,
+                   const void* b1, const void* w2, const void* b2, void* gate, int64_t n, int64_t c,
+                   int64_t r, b200ml_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Fused attention                                                            */
+/* ------------------------------------------------------------------------- */
+
+typedef struct {
+    int64_t batch, heads, seq_q, seq_kv, head_dim;
+    /* element strides of q, k, v, o per (batch, head, position); head_dim is contiguous */
+    int64_t q_stride_b, q_stride_h, q_stride_s;
+    int64_t k_stride_b, k_stride_h, k_stride_s;
+    int64_t v_stride_b, v_stride_h, v_stride_s;
+    int64_t o_stride_b, o_stride_h, o_stride_s;
+    float scale;
+    int32_t reserved;
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* mask; /* additive [batch, seq_kv] fp16 or null */
+    void* o;
+} b200ml_attention_params;
+
+/* softmax(scale * Q K^T + mask) V in one kernel, fp16 in/out, fp32 accumulate.  Replaces the
+ * MatMul -> Mul -> (Add) -> Softmax -> MatMul sub-graph and the head split / merge Transposes
+ * around it (pure_implementations.py:111-216, 309-326). */
+int b200ml_attention_f16(b200ml_ctx* ctx, const b200ml_attention_params* p, b200ml_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DACEML_B200_H */
