@@ -185,45 +185,89 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 break;
             }
             ptx::tc_fence_after();
-            // pass 1: running maximum of the scaled, masked scores
+            // A tile is "plain" when every key is in range and there is no additive mask: the
+            // scale then commutes with the maximum and each score costs one FMNMX in pass 1 and
+            // one FFMA + one MUFU.EX2 + one FADD in pass 2.
+            const bool plain = (kv0 + KT <= args.seq_kv) && mrow == nullptr && args.scale_log2 > 0.0f;
+            // pass 1: running maximum of the scaled, masked scores (log2 domain)
             float mx = m_run;
+            if (plain) {
+                float raw = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < KT / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
-                ptx::tmem_ld_wait();
+                for (int c = 0; c < KT / 32; c += 2) {
+                    uint32_t r0[32], r1[32];
+                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r0);
+                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32 + 32, r1);
+                    ptx::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int kv = kv0 + c * 32 + i;
-                    float t = __uint_as_float(r[i]) * args.scale_log2;
-                    if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
-                    if (kv >= args.seq_kv) t = -INFINITY;
-                    mx = fmaxf(mx, t);
+                    for (int i = 0; i < 32; ++i) raw = fmaxf(raw, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+                }
+                mx = fmaxf(mx, raw * args.scale_log2);
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < KT / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int kv = kv0 + c * 32 + i;
+                        float t = __uint_as_float(r[i]) * args.scale_log2;
+                        if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
+                        if (kv >= args.seq_kv) t = -INFINITY;
+                        mx = fmaxf(mx, t);
+                    }
                 }
             }
             const float m_safe = (mx == -INFINITY) ? 0.0f : mx;
             const float alpha = ex2(m_run - m_safe);  // 0 on the first tile
             // pass 2: P = exp2(t - m), row sum, fp16 P into swizzled shared memory
             float sum = 0.0f;
+            if (plain) {
+                const float neg_m = -m_safe;
 #pragma unroll 1
-            for (int c = 0; c < KT / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
-                ptx::tmem_ld_wait();
-                uint8_t* atom = sp + (c >> 1) * (QT * 128) + row * 128;
+                for (int c = 0; c < KT / 32; c += 2) {
+                    uint32_t r[2][32];
+                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r[0]);
+                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32 + 32, r[1]);
+                    ptx::tmem_ld_wait();
+                    uint8_t* atom = sp + (c >> 1) * (QT * 128) + row * 128;  // chunks c, c+1 = one 64-key atom
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float p[8];
+                    for (int u = 0; u < 2; ++u) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int kv = kv0 + c * 32 + g * 8 + i;
-                        float t = __uint_as_float(r[g * 8 + i]) * args.scale_log2;
-                        if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
-                        p[i] = kv < args.seq_kv ? ex2(t - m_safe) : 0.0f;
-                        sum += p[i];
+                        for (int g = 0; g < 4; ++g) {
+                            float p[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                p[i] = ex2(fmaf(__uint_as_float(r[u][g * 8 + i]), args.scale_log2, neg_m));
+                                sum += p[i];
+                            }
+                            const int chunk = u * 4 + g;  // 16-byte chunk within the 128-byte row
+                            *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = pack8(p);
+                        }
                     }
-                    const int chunk = (c & 1) * 4 + g;  // 16-byte chunk within the 128-byte row
-                    *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = pack8(p);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < KT / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    uint8_t* atom = sp + (c >> 1) * (QT * 128) + row * 128;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float p[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int kv = kv0 + c * 32 + g * 8 + i;
+                            float t = __uint_as_float(r[g * 8 + i]) * args.scale_log2;
+                            if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
+                            p[i] = kv < args.seq_kv ? ex2(t - m_safe) : 0.0f;
+                            sum += p[i];
+                        }
+                        const int chunk = (c & 1) * 4 + g;  // 16-byte chunk within the 128-byte row
+                        *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = pack8(p);
+                    }
                 }
             }
             l_run = fmaf(l_run, alpha, sum);

@@ -43,33 +43,91 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return q;
 }
 
+// GELU (erf form) for fp16 outputs: Phi is evaluated through erfc(|z|) = 2^(-q(|z|)), q a fitted
+// degree-5 polynomial (|erf error| < 7e-7, no cancellation on the negative side), one MUFU.EX2.
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+    const float z = fabsf(x) * 0.70710678118654752440f;
+    float q = fmaf(z, 0.0029446918051689863f, -0.02959194779396057f);
+    q = fmaf(z, q, 0.1486678570508957f);
+    q = fmaf(z, q, 0.9185084104537964f);
+    q = fmaf(z, q, 1.6278891563415527f);
+    q *= z;
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-q));
+    const float phi2 = x < 0.0f ? e : 2.0f - e;
+    return (0.5f * x) * phi2;
+}
+
+// Residual / bias packets of one 32-column chunk, fetched before the accumulator arrives.
+struct EpiloguePrefetch {
+    uint4 res[4];
+    uint4 bias[4];
+};
+
+__device__ __forceinline__ void epilogue_prefetch_32(const EpilogueParams& ep, EpiloguePrefetch& pf, const __half* r_row,
+                                                     const __half* bias, int col0, int n, bool vec) {
+    if (!(vec && n - col0 >= 32)) return;
+    if ((ep.flags & B200ML_EPI_RESIDUAL) && r_row != nullptr) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) pf.res[g] = __ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8));
+    }
+    if ((ep.flags & B200ML_EPI_BIAS) && bias != nullptr) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) pf.bias[g] = __ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8));
+    }
+}
+
 // Finishes 32 consecutive columns [col0, col0 + 32) of one output row held as raw fp32 bits in r.
-__device__ __forceinline__ void epilogue_store_32(const EpilogueParams& ep, const uint32_t (&r)[32], __half* c_row,
-                                                  const __half* r_row, const __half* bias, int col0, int n, bool vec) {
+// Every branch on ep.flags is warp-uniform; the per-element work is alpha, bias, activation,
+// residual, one fp16 conversion.
+__device__ __forceinline__ void epilogue_store_32(const EpilogueParams& ep, const uint32_t (&r)[32],
+                                                  const EpiloguePrefetch& pf, __half* c_row, const __half* r_row,
+                                                  const __half* bias, int col0, int n, bool vec) {
     const int valid = n - col0 < 32 ? n - col0 : 32;
     const bool has_bias = (ep.flags & B200ML_EPI_BIAS) && bias != nullptr;
     const bool has_res = (ep.flags & B200ML_EPI_RESIDUAL) && r_row != nullptr;
     if (vec && valid == 32) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (ep.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= ep.alpha;
+        }
+        if (has_bias) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                float b[8];
+                unpack8(pf.bias[g], b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[g * 8 + j] = fmaf(ep.bias_scale, b[j], v[g * 8 + j]);
+            }
+        }
+        if (ep.flags & B200ML_EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf_fast(v[j]);
+        } else if (ep.flags & B200ML_EPI_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+        } else if (ep.flags & B200ML_EPI_SWISH) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoidf_(v[j]);
+        }
+        if (has_res) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                float q[8];
+                unpack8(pf.res[g], q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[g * 8 + j] = fmaf(ep.residual_scale, q[j], v[g * 8 + j]);
+            }
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            float v[8];
+            float o[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = ep.alpha * __uint_as_float(r[g * 8 + j]);
-            if (has_bias) {
-                float b[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col0 + g * 8)), b);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = fmaf(ep.bias_scale, b[j], v[j]);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], ep.flags);
-            if (has_res) {
-                float q[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8)), q);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = fmaf(ep.residual_scale, q[j], v[j]);
-            }
-            *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(v);
+            for (int j = 0; j < 8; ++j) o[j] = v[g * 8 + j];
+            *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(o);
         }
     } else {
 #pragma unroll

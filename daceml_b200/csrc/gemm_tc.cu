@@ -27,7 +27,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 fp16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int A_TILE_BYTES = BM * BK * 2;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;  // two per TMEM lane quarter, each taking half of the tile's columns
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 
 struct GemmArgs {
     int32_t m, n, k;
@@ -44,7 +45,16 @@ struct GemmArgs {
     const __half* bias;
     const __half* residual;
     int32_t* status;
+    long long* trace;  // per-CTA cycle counters, only written when built with B200ML_TRACE
 };
+
+#ifdef B200ML_TRACE
+#define TRACE_T0() const long long _t0 = clock64()
+#define TRACE_ADD(var) var += clock64() - _t0
+#else
+#define TRACE_T0()
+#define TRACE_ADD(var)
+#endif
 
 template <int BN>
 struct GemmSmem {
@@ -88,7 +98,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
             for (int a = 0; a < 2; ++a) {
                 ptx::mbar_init(&tmem_full_bar[a], 1);
-                ptx::mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+                ptx::mbar_init(&tmem_empty_bar[a], EPI_WARPS);  // one arrival per epilogue warp
             }
             ptx::fence_mbar_init();
         }
@@ -107,6 +117,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            long long tr_wait = 0;
+            const long long tr_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
                 const int mt = tile % args.tiles_m;
                 const int rest = tile / args.tiles_m;
@@ -116,11 +128,13 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 const int bo = batch / args.batch_inner;
                 const int m0 = mt * BM, n0 = nt * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    TRACE_T0();
                     if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
                         atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
                         ok = false;
                         break;
                     }
+                    TRACE_ADD(tr_wait);
                     uint8_t* sa = smem + stage * S::STAGE_BYTES;
                     uint8_t* sb = sa + A_TILE_BYTES;
                     ptx::mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
@@ -141,6 +155,10 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     }
                 }
             }
+#ifdef B200ML_TRACE
+            args.trace[blockIdx.x * 16 + 0] = tr_wait;
+            args.trace[blockIdx.x * 16 + 1] = clock64() - tr_begin;
+#endif
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
@@ -150,18 +168,28 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            long long tr_wait_acc = 0, tr_wait_full = 0;
+            const long long tr_begin = clock64();
             for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
-                if (!ptx::mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1)) {
-                    atomicExch(args.status, DEV_TIMEOUT_MMA);
-                    break;
+                {
+                    TRACE_T0();
+                    if (!ptx::mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1)) {
+                        atomicExch(args.status, DEV_TIMEOUT_MMA);
+                        break;
+                    }
+                    TRACE_ADD(tr_wait_acc);
                 }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!ptx::mbar_wait(&full_bar[stage], phase)) {
-                        atomicExch(args.status, DEV_TIMEOUT_MMA);
-                        ok = false;
-                        break;
+                    {
+                        TRACE_T0();
+                        if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+                            atomicExch(args.status, DEV_TIMEOUT_MMA);
+                            ok = false;
+                            break;
+                        }
+                        TRACE_ADD(tr_wait_full);
                     }
                     ptx::tc_fence_after();
                     const uint32_t a_addr = ptx::smem_u32(smem + stage * S::STAGE_BYTES);
@@ -185,10 +213,19 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1;
             }
+#ifdef B200ML_TRACE
+            args.trace[blockIdx.x * 16 + 2] = tr_wait_acc;
+            args.trace[blockIdx.x * 16 + 3] = tr_wait_full;
+            args.trace[blockIdx.x * 16 + 4] = clock64() - tr_begin;
+#endif
         }
     } else {
         // ------------------------------ epilogue ------------------------------
-        const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+        const int quarter = warp & 3;         // the TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp finishes
+        constexpr int WCOLS = BN / 2;         // columns per warp
+        constexpr int CHUNKS = WCOLS / 32;    // 32-column chunks per warp: 1, 2 or 4
+        constexpr int GROUP = CHUNKS >= 2 ? 2 : 1;  // chunks fetched per tcgen05.wait::ld
         const int row_in_tile = quarter * 32 + lane;
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -197,6 +234,9 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         ep.alpha = args.alpha;
         ep.bias_scale = args.bias_scale;
         ep.residual_scale = args.residual_scale;
+        long long tr_wait_epi = 0, tr_ld = 0;
+        const long long tr_begin = clock64();
+        (void)tr_wait_epi, (void)tr_ld, (void)tr_begin;
         for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
             const int mt = tile % args.tiles_m;
             const int rest = tile / args.tiles_m;
@@ -205,10 +245,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const int bi = batch % args.batch_inner;
             const int bo = batch / args.batch_inner;
             const int row = mt * BM + row_in_tile;
-            const int n0 = nt * BN;
-            if (!ptx::mbar_wait(&tmem_full_bar[acc], acc_phase)) {
-                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
-                break;
+            const int n0 = nt * BN + half * WCOLS;
+            {
+                TRACE_T0();
+                if (!ptx::mbar_wait(&tmem_full_bar[acc], acc_phase)) {
+                    if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                    break;
+                }
+                TRACE_ADD(tr_wait_epi);
             }
             ptx::tc_fence_after();
             __half* c_row = args.c + bo * args.c_so + bi * args.c_si + static_cast<int64_t>(row) * args.ldc;
@@ -216,14 +260,33 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                                       ? args.residual + bo * args.r_so + bi * args.r_si + static_cast<int64_t>(row) * args.ldr
                                       : nullptr;
             const bool row_ok = row < args.m;
+            const bool vec = args.vec_ok != 0;
+            const uint32_t t_base = tmem_base + acc * BN + half * WCOLS + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < CHUNKS; c += GROUP) {
                 const int col0 = n0 + c * 32;
                 if (col0 >= args.n) break;  // warp-uniform
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
-                ptx::tmem_ld_wait();
-                if (row_ok) epilogue_store_32(ep, r, c_row, r_row, args.bias, col0, args.n, args.vec_ok != 0);
+                uint32_t r[GROUP][32];
+                EpiloguePrefetch pf[GROUP];
+                {
+                    TRACE_T0();
+#pragma unroll
+                    for (int u = 0; u < GROUP; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
+                    if (row_ok) {
+#pragma unroll
+                        for (int u = 0; u < GROUP; ++u)
+                            epilogue_prefetch_32(ep, pf[u], r_row, args.bias, col0 + u * 32, args.n, vec);
+                    }
+                    ptx::tmem_ld_wait();
+                    TRACE_ADD(tr_ld);
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int u = 0; u < GROUP; ++u) {
+                        if (col0 + u * 32 < args.n)
+                            epilogue_store_32(ep, r[u], pf[u], c_row, r_row, args.bias, col0 + u * 32, args.n, vec);
+                    }
+                }
             }
             ptx::tc_fence_before();
             __syncwarp();
@@ -231,6 +294,13 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
+#ifdef B200ML_TRACE
+        if (threadIdx.x == 64) {
+            args.trace[blockIdx.x * 16 + 5] = tr_wait_epi;
+            args.trace[blockIdx.x * 16 + 6] = tr_ld;
+            args.trace[blockIdx.x * 16 + 7] = clock64() - tr_begin;
+        }
+#endif
     }
 
     // ------------------------------ teardown ------------------------------
@@ -299,26 +369,10 @@ int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, 
 
 int gemm_f16_simt(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
 
-// Tile width: the widest N tile whose wave count does not waste more of the machine than a
-// narrower one would.  Time is proportional to waves * BN.
-static int pick_bn(int64_t m, int64_t n, int64_t batches, int sms) {
-    if (n <= 64) return 64;
-    if (n <= 128) return 128;
-    const int64_t tm = ceil_div(m, BM);
-    int best = 256;
-    int64_t best_cost = INT64_MAX;
-    const int cand[3] = {256, 128, 64};
-    for (int i = 0; i < 2; ++i) {  // 64-wide tiles only for narrow outputs
-        const int bn = cand[i];
-        const int64_t tiles = tm * ceil_div(n, bn) * batches;
-        const int64_t cost = ceil_div(tiles, sms) * bn + (bn == 128 ? bn / 8 : 0);  // mild preference for 256
-        if (cost < best_cost) {
-            best_cost = cost;
-            best = bn;
-        }
-    }
-    return best;
-}
+// Tile width.  The main loop of a 128 x 256 tile needs 48 KB per 64-deep k-block, which is what one
+// SM can pull from L2 in the time the tensor core takes; narrower tiles are load-bound, so they
+// are used only for narrow outputs.
+static int pick_bn(int64_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
 int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream) {
     const int64_t batches = p->batch_outer * p->batch_inner;
@@ -328,7 +382,7 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
     const bool b_ok = aligned16(p->b) && p->ldb % 8 == 0 && p->b_stride_inner % 8 == 0 && p->b_stride_outer % 8 == 0;
     if (!a_ok || !b_ok || p->m * p->n * batches < 64 * 64) return gemm_f16_simt(ctx, p, stream);
 
-    const int bn = pick_bn(p->m, p->n, batches, ctx->sm_count);
+    const int bn = pick_bn(p->n);
     GemmArgs args{};
     args.m = (int32_t)p->m;
     args.n = (int32_t)p->n;
@@ -357,6 +411,7 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
     args.bias = static_cast<const __half*>(p->bias);
     args.residual = static_cast<const __half*>(p->residual);
     args.status = ctx->status_dev;
+    args.trace = static_cast<long long*>(ctx->workspace);
     bool vec = aligned16(p->c) && p->ldc % 8 == 0 && p->c_stride_inner % 8 == 0 && p->c_stride_outer % 8 == 0;
     if (p->residual)
         vec = vec && aligned16(p->residual) && p->ldr % 8 == 0 && p->r_stride_inner % 8 == 0 && p->r_stride_outer % 8 == 0;

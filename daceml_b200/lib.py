@@ -12,7 +12,8 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libdaceml_b200.so")
+# DACEML_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("DACEML_B200_LIB") or os.path.join(_HERE, "lib", "libdaceml_b200.so")
 
 # status codes / enums (mirrors of the header)
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
