@@ -1,0 +1,74 @@
+"""Batch-sharded inference across the GPUs of one box.
+
+The reference has no multi-device path at all.  Every operator on the path is independent across
+the batch dimension, so each rank (one process per GPU, ``torch.distributed``) runs the whole
+layer stack on its own samples with replicated weights and no per-layer collective; the outputs
+are gathered once at the end (NCCL over NVLink / NVSwitch on GPUs, gloo in the CPU tests).
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def init_from_env(backend=None, timeout_s=120):
+    """Joins the process group described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT.
+
+    Returns ``(rank, world_size, local_rank)``; a single process without those variables is rank 0 of 1."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world > 1 and not dist.is_initialized():
+        import datetime
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        if backend == "nccl":
+            torch.cuda.set_device(local_rank)
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend=backend, rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s))
+    return rank, world, local_rank
+
+
+def shard_bounds(global_batch, rank, world):
+    """Rank r of R takes the contiguous samples [lo, hi); the batch must split evenly."""
+    if global_batch % world != 0:
+        raise ValueError("global batch {} does not split evenly over {} ranks".format(global_batch, world))
+    per = global_batch // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_batch(x_global, rank, world):
+    lo, hi = shard_bounds(x_global.shape[0], rank, world)
+    return x_global[lo:hi]
+
+
+def gather_outputs(y_local, out=None, group=None):
+    """All-gathers the per-rank outputs along the batch dimension, in rank order."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        if out is None:
+            return y_local
+        out.copy_(y_local)
+        return out
+    if out is None:
+        out = torch.empty((world * y_local.shape[0], ) + tuple(y_local.shape[1:]), dtype=y_local.dtype,
+                          device=y_local.device)
+    y_local = y_local.contiguous()
+    if hasattr(dist, "all_gather_into_tensor") and (y_local.is_cuda or dist.get_backend(group) != "gloo"):
+        dist.all_gather_into_tensor(out, y_local, group=group)
+    else:
+        parts = list(out.chunk(world, dim=0))
+        dist.all_gather(parts, y_local, group=group)
+    return out
+
+
+class ShardedEncoder:
+    """Wraps a per-rank model (``model(x_shard) -> y_shard``) with the batch split and the final gather."""
+
+    def __init__(self, model, rank, world, group=None):
+        self.model, self.rank, self.world, self.group = model, rank, world, group
+
+    def __call__(self, x_global, gather=True):
+        y = self.model(shard_batch(x_global, self.rank, self.world))
+        return gather_outputs(y, group=self.group) if gather else y

@@ -1,0 +1,1 @@
+from .onnx_op import *  # noqa: F401,F403

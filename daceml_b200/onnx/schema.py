@@ -1,0 +1,90 @@
+"""Operator schemas for the ONNX opset-12 operators on the hot path.
+
+The reference mirrors ``onnx.defs`` schemas at import time (``daceml/onnx/schema.py``,
+``daceml/onnx/nodes/onnx_op.py:510-556``).  The ``onnx`` package is not a dependency here, so the
+connector names, their kinds and the attribute defaults of the operators this library implements
+are written out; they are the names an expansion sees (``A, B, Y``; ``X, W, B, Y``;
+``Inputs__0 ...``, ``Output``; ``data, reduced``).
+
+Four fused operators that opset 12 does not have (``LayerNormalization`` and ``Gelu`` exist in
+later opsets; ``FusedMatMul`` and ``Attention`` are the usual contrib names) are declared with
+``fused=True``: they are what the fusion pass rewrites exported sub-graphs into.
+"""
+from collections import namedtuple
+
+SINGLE, OPTIONAL, VARIADIC = "single", "optional", "variadic"
+
+Param = namedtuple("Param", ["name", "kind"])
+
+
+class ONNXSchema:
+    def __init__(self, name, inputs, outputs, attributes=None, fused=False, doc=""):
+        self.name = name
+        self.inputs = [Param(*p) if isinstance(p, tuple) else Param(p, SINGLE) for p in inputs]
+        self.outputs = [Param(*p) if isinstance(p, tuple) else Param(p, SINGLE) for p in outputs]
+        self.attributes = dict(attributes or {})
+        self.fused = fused
+        self.doc = doc
+
+    def non_variadic_inputs(self):
+        return [p.name for p in self.inputs if p.kind != VARIADIC]
+
+    def variadic_inputs(self):
+        return [p.name for p in self.inputs if p.kind == VARIADIC]
+
+    def non_variadic_outputs(self):
+        return [p.name for p in self.outputs if p.kind != VARIADIC]
+
+    def variadic_outputs(self):
+        return [p.name for p in self.outputs if p.kind == VARIADIC]
+
+
+def _unary(name, i="X", o="Y", **attrs):
+    return ONNXSchema(name, [i], [o], attrs)
+
+
+_S = [
+    ONNXSchema("MatMul", ["A", "B"], ["Y"]),
+    ONNXSchema("Gemm", ["A", "B", ("C", OPTIONAL)], ["Y"], dict(alpha=1.0, beta=1.0, transA=0, transB=0)),
+    ONNXSchema("Einsum", [("Inputs", VARIADIC)], ["Output"], dict(equation=None)),
+    ONNXSchema("Softmax", ["input"], ["output"], dict(axis=1)),
+    ONNXSchema("LogSoftmax", ["input"], ["output"], dict(axis=1)),
+    ONNXSchema("Add", ["A", "B"], ["C"]),
+    ONNXSchema("Sub", ["A", "B"], ["C"]),
+    ONNXSchema("Mul", ["A", "B"], ["C"]),
+    ONNXSchema("Div", ["A", "B"], ["C"]),
+    ONNXSchema("Pow", ["X", "Y"], ["Z"]),
+    _unary("Sqrt"), _unary("Relu"), _unary("Sigmoid"), _unary("Reciprocal"), _unary("Softplus"),
+    _unary("LeakyRelu", alpha=0.01),
+    _unary("Erf", "input", "output"), _unary("Exp", "input", "output"), _unary("Log", "input", "output"),
+    _unary("Tanh", "input", "output"), _unary("Identity", "input", "output"),
+    ONNXSchema("Clip", ["input", ("min", OPTIONAL), ("max", OPTIONAL)], ["output"]),
+    ONNXSchema("Cast", ["input"], ["output"], dict(to=None)),
+    ONNXSchema("ReduceMean", ["data"], ["reduced"], dict(axes=None, keepdims=1)),
+    ONNXSchema("ReduceSum", ["data"], ["reduced"], dict(axes=None, keepdims=1)),
+    ONNXSchema("ReduceMax", ["data"], ["reduced"], dict(axes=None, keepdims=1)),
+    ONNXSchema("ReduceMin", ["data"], ["reduced"], dict(axes=None, keepdims=1)),
+    ONNXSchema("Transpose", ["data"], ["transposed"], dict(perm=None)),
+    ONNXSchema("Reshape", ["data", ("shape", OPTIONAL)], ["reshaped"]),
+    ONNXSchema("Flatten", ["input"], ["output"], dict(axis=1)),
+    ONNXSchema("Unsqueeze", ["data"], ["expanded"], dict(axes=None)),
+    ONNXSchema("Squeeze", ["data"], ["squeezed"], dict(axes=None)),
+    ONNXSchema("Sum", [("data_0", VARIADIC)], ["sum"]),
+    ONNXSchema("Conv", ["X", "W", ("B", OPTIONAL)], ["Y"],
+               dict(auto_pad="NOTSET", dilations=None, group=1, kernel_shape=None, pads=None, strides=None)),
+    ONNXSchema("GlobalAveragePool", ["X"], ["Y"]),
+    # fused operators (targets of the fusion pass)
+    ONNXSchema("LayerNormalization", ["X", ("Scale", OPTIONAL), ("B", OPTIONAL), ("Residual", OPTIONAL)], ["Y"],
+               dict(axis=-1, epsilon=1e-5), fused=True),
+    ONNXSchema("Gelu", ["X"], ["Y"], fused=True),
+    ONNXSchema("Swish", ["X"], ["Y"], fused=True),
+    ONNXSchema("FusedMatMul", ["A", "B", ("Bias", OPTIONAL), ("Residual", OPTIONAL)], ["Y"],
+               dict(alpha=1.0, transB=0, activation=""), fused=True),
+    ONNXSchema("Attention", ["Q", ("K", OPTIONAL), ("V", OPTIONAL), ("Mask", OPTIONAL)], ["Y"], dict(num_heads=1, scale=None), fused=True),
+    ONNXSchema("FusedConv", ["X", "W", ("B", OPTIONAL), ("Gate", OPTIONAL), ("Residual", OPTIONAL)],
+               ["Y", ("Pool", OPTIONAL)],
+               dict(dilations=None, group=1, kernel_shape=None, pads=None, strides=None, activation=""), fused=True),
+    ONNXSchema("SqueezeExcite", ["X", "W1", ("B1", OPTIONAL), "W2", ("B2", OPTIONAL)], ["Y"], fused=True),
+]
+
+SCHEMAS = {s.name: s for s in _S}

@@ -1,0 +1,84 @@
+"""Helpers with the reference's names and meaning (``daceml/util/utils.py:34-95, 156-235``)."""
+import logging
+from typing import Callable, Optional
+
+from daceml_b200 import sdfg as sd
+
+log = logging.getLogger(__name__)
+
+__all__ = ["in_desc_with_name", "out_desc_with_name", "in_edge_with_name", "out_edge_with_name", "expand_onnx_nodes",
+           "expand_nodes", "auto_optimize", "is_desc_contiguous", "prod"]
+
+
+def prod(sequence):
+    out = 1
+    for s in sequence:
+        out *= s
+    return out
+
+
+def is_desc_contiguous(desc) -> bool:
+    return True  # descriptors of this build are always C-contiguous
+
+
+def in_edge_with_name(node, state, name):
+    """ Find the edge that connects to input connector `name` on `node`. """
+    cands = list(state.in_edges_by_connector(node, name))
+    if len(cands) != 1:
+        raise ValueError("Expected to find exactly one edge with name '{}', found {}".format(name, len(cands)))
+    return cands[0]
+
+
+def out_edge_with_name(node, state, name):
+    """ Find the edge that connects to output connector `name` on `node`. """
+    cands = list(state.out_edges_by_connector(node, name))
+    if len(cands) != 1:
+        raise ValueError("Expected to find exactly one edge with name '{}', found {}".format(name, len(cands)))
+    return cands[0]
+
+
+def in_desc_with_name(node, state, sdfg, name):
+    """ Find the descriptor of the data that connects to input connector `name`. """
+    return sdfg.arrays[in_edge_with_name(node, state, name).data.data]
+
+
+def out_desc_with_name(node, state, sdfg, name):
+    """ Find the descriptor of the data that connects to output connector `name`. """
+    return sdfg.arrays[out_edge_with_name(node, state, name).data.data]
+
+
+def expand_nodes(sdfg, predicate: Callable[[sd.Node], bool]):
+    """ Expand library nodes in the SDFG using a given predicate, until none is left. """
+    from daceml_b200.onnx.nodes.onnx_op import ONNXOp
+    states = list(sdfg.states())
+    while states:
+        state = states.pop()
+        expanded_something = False
+        for node in state.nodes():
+            if isinstance(node, ONNXOp) and predicate(node):
+                impl_name = node.expand(sdfg, state)
+                log.debug('Expanded library node "%s" with implementation "%s".', node, impl_name)
+                expanded_something = True
+        if expanded_something:
+            states.append(state)
+
+
+def expand_onnx_nodes(sdfg, predicate: Optional[Callable[[sd.Node], bool]] = None):
+    """ Recursively expand all onnx library nodes in the SDFG. """
+    expand_nodes(sdfg, (lambda n: True) if predicate is None else predicate)
+
+
+def auto_optimize(sdfg, cuda=True, simplify=False, fold_constants=True, fuse=True):
+    """ Automatically optimize ``sdfg``: fuse exported sub-graphs into the fused operators this
+        library has kernels for, then expand every ONNX node.
+
+        The reference's function of the same name folds constants, expands the nodes and picks
+        fast BLAS implementations (``daceml/util/utils.py:205-235``); the fusion step takes the
+        place of constant folding and BLAS selection here.
+    """
+    if not cuda:
+        raise ValueError("daceml_b200 has no CPU path")
+    if fuse:
+        from daceml_b200.transformation import fuse_subgraphs
+        fuse_subgraphs(sdfg)
+    expand_onnx_nodes(sdfg)

@@ -1,0 +1,262 @@
+"""Whole-graph parity on the B200 for the five benchmark configurations (small golden versions and the
+full sizes), fused against unfused, and properties that do not need an oracle at full size."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from daceml_b200 import graphs, kernels as K, lib as L, runner
+from oracle import ops
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def gold(name):
+    return np.load(os.path.join(GOLD, name + ".npz"))
+
+
+def t(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dtype)
+
+
+def status_ok():
+    torch.cuda.synchronize()
+    assert L.get_context(0).device_status() == 0
+
+
+def bert_params(rng, hidden, ffn, scale=0.02, zero_bias=False):
+    def w(*s):
+        return torch.from_numpy((rng.standard_normal(s) * scale).astype(np.float32))
+    z = (lambda n: torch.zeros(n)) if zero_bias else (lambda n: w(n))
+    return dict(wq=w(hidden, hidden), bq=z(hidden), wk=w(hidden, hidden), bk=z(hidden), wv=w(hidden, hidden), bv=z(hidden),
+                wo=w(hidden, hidden), bo=z(hidden), ln1_g=torch.ones(hidden), ln1_b=torch.zeros(hidden), w1=w(ffn, hidden),
+                b1=z(ffn), w2=w(hidden, ffn), b2=z(hidden), ln2_g=torch.ones(hidden), ln2_b=torch.zeros(hidden))
+
+
+# ------------------------------------------------------------------------------------------------
+# config 2: MLP
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("fused", [True, False])
+def test_mlp_golden(fused):
+    g = gold("mlp")
+    p = {k: t(g[k]) for k in ("w1", "b1", "w2", "b2", "w3", "b3")}
+    y = graphs.mlp_sdfg(p, g["x"].shape[0], fused=fused)(input=t(g["x"]).cuda())
+    assert_close(y, g["y"], what="mlp golden")
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_mlp_config2_full_size(fused):
+    """Linear 784->120, ReLU, 120->32, ReLU, 32->10, LogSoftmax; batch 4096; PyTorch default init from a fixed seed."""
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(784, 120), torch.nn.ReLU(), torch.nn.Linear(120, 32), torch.nn.ReLU(),
+                              torch.nn.Linear(32, 10), torch.nn.LogSoftmax(dim=-1))
+    x = torch.randn(4096, 784)
+    p = dict(w1=net[0].weight, b1=net[0].bias, w2=net[2].weight, b2=net[2].bias, w3=net[4].weight, b3=net[4].bias)
+    p = {k: v.detach() for k, v in p.items()}
+    y = graphs.mlp_sdfg(p, 4096, fused=fused)(input=x.cuda())
+    ref = ops.mlp(x.numpy(), {k: v.numpy() for k, v in p.items()})
+    assert_close(y, ref, what="config 2 vs oracle")
+    with torch.no_grad():
+        assert_close(y, net(x), rtol=1e-4, atol=1e-5, what="config 2 vs torch module")
+    status_ok()
+
+
+# ------------------------------------------------------------------------------------------------
+# config 3: BERT encoder layer
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("fused", [True, False])
+def test_bert_layer_golden_fp16(fused):
+    g = gold("bert_layer")
+    p = {k: t(g[k]) for k in g.files if k not in ("x", "y_fp32", "y_fp16")}
+    s = graphs.bert_layer_sdfg(p, 2, 40, 2, fused=fused)
+    y = s(input=t(g["x"], torch.float16).cuda())
+    # the oracle computed in fp32 from fp16-rounded inputs and weights
+    p16 = {k: v.half().float().numpy() for k, v in p.items()}
+    ref = ops.bert_layer(t(g["x"]).half().float().numpy(), p16, heads=2, store=np.float32)
+    assert_close(y, ref, torch.float16, atol=1e-2, what="bert layer (small) vs fp32 oracle")
+    assert_close(y, g["y_fp16"], torch.float16, atol=1e-2, what="bert layer (small) vs fp16-storage oracle")
+    status_ok()
+
+
+def test_bert_layer_with_attention_mask():
+    g = gold("bert_layer")
+    p = {k: t(g[k]) for k in g.files if k not in ("x", "y_fp32", "y_fp16")}
+    mask = torch.zeros(2, 40)
+    mask[0, 30:] = -10000.0
+    mask[1, 17:] = -10000.0
+    p["mask"] = mask
+    x16 = t(g["x"], torch.float16)
+    yf = graphs.bert_layer_sdfg(p, 2, 40, 2, fused=True)(input=x16.cuda())
+    yu = graphs.bert_layer_sdfg(p, 2, 40, 2, fused=False)(input=x16.cuda())
+    pn = {k: v.half().float().numpy() for k, v in p.items()}
+    ref = ops.bert_layer(x16.float().numpy(), pn, heads=2, store=np.float32)
+    assert_close(yf, ref, torch.float16, atol=1e-2, what="masked, fused")
+    assert_close(yu, ref, torch.float16, atol=1e-2, what="masked, unfused")
+
+
+def test_bert_layer_config3_full_size():
+    """B=8, S=512, hidden 1024, 16 heads, FFN 4096, weights ~ N(0, 0.02), biases 0, gamma 1, beta 0."""
+    rng = np.random.default_rng(3)
+    p = bert_params(rng, 1024, 4096, zero_bias=True)
+    x = torch.from_numpy(rng.standard_normal((8, 512, 1024)).astype(np.float32)).half()
+    y = graphs.bert_layer_sdfg(p, 8, 512, 16, fused=True)(input=x.cuda())
+    status_ok()
+    pn = {k: v.half().float().numpy() for k, v in p.items()}
+    inter = {}
+    ref = ops.bert_layer(x.float().numpy(), pn, heads=16, store=np.float32, intermediates=inter)
+    assert_close(y, ref, torch.float16, atol=1e-2, what="config 3 vs oracle")
+    # second witness: HuggingFace BertLayer (the model tests/torch/test_bert_encoder.py:11-33 uses), fp32 on the CPU
+    from transformers import BertConfig
+    from transformers.models.bert.modeling_bert import BertLayer
+    cfg = BertConfig(hidden_size=1024, num_attention_heads=16, intermediate_size=4096)
+    cfg._attn_implementation = "eager"
+    m = BertLayer(cfg).eval()
+    sd = m.state_dict()
+    names = {"attention.self.query": ("wq", "bq"), "attention.self.key": ("wk", "bk"), "attention.self.value": ("wv", "bv"),
+             "attention.output.dense": ("wo", "bo"), "intermediate.dense": ("w1", "b1"), "output.dense": ("w2", "b2")}
+    for k, (w, b) in names.items():
+        sd[k + ".weight"], sd[k + ".bias"] = p[w].half().float(), p[b].half().float()
+    sd["attention.output.LayerNorm.weight"], sd["attention.output.LayerNorm.bias"] = p["ln1_g"], p["ln1_b"]
+    sd["output.LayerNorm.weight"], sd["output.LayerNorm.bias"] = p["ln2_g"], p["ln2_b"]
+    m.load_state_dict(sd)
+    with torch.no_grad():
+        hf = m(x.float())
+    hf = hf[0] if isinstance(hf, tuple) else hf
+    assert_close(y, hf, torch.float16, atol=1e-2, what="config 3 vs HuggingFace BertLayer")
+
+
+def test_fused_equals_unfused_full_size():
+    rng = np.random.default_rng(5)
+    p = bert_params(rng, 1024, 4096)
+    x = torch.from_numpy(rng.standard_normal((8, 512, 1024)).astype(np.float32)).half().cuda()
+    yf = graphs.bert_layer_sdfg(p, 8, 512, 16, fused=True)(input=x)
+    yu = graphs.bert_layer_sdfg(p, 8, 512, 16, fused=False)(input=x)
+    assert_close(yf, yu, torch.float16, atol=1e-2, what="fused vs node-by-node")
+    status_ok()
+
+
+def test_layer_is_deterministic_and_respects_guard_bands():
+    rng = np.random.default_rng(7)
+    p = bert_params(rng, 1024, 4096)
+    s = graphs.bert_layer_sdfg(p, 8, 512, 16, fused=True).compile()
+    x = torch.from_numpy(rng.standard_normal((8, 512, 1024)).astype(np.float32)).half().cuda()
+    # output placed between two poisoned bands
+    n = 8 * 512 * 1024
+    slab = torch.full((n + 2 * 4096, ), 777.0, dtype=torch.float16, device="cuda")
+    out = slab[4096:4096 + n].view(8, 512, 1024)
+    s(**{"input": x, "__return": out})
+    first = out.clone()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        s(**{"input": x, "__return": out})
+    side.synchronize()
+    assert torch.equal(first, out), "two runs (two streams) differ bit-wise"
+    assert bool((slab[:4096] == 777.0).all()) and bool((slab[4096 + n:] == 777.0).all()), "guard band overwritten"
+    assert torch.isfinite(out).all()
+    status_ok()
+
+
+# ------------------------------------------------------------------------------------------------
+# config 5: stack of layers (the per-GPU part)
+# ------------------------------------------------------------------------------------------------
+def test_encoder_stack_small():
+    rng = np.random.default_rng(11)
+    params = [bert_params(rng, 128, 256, scale=0.05) for _ in range(3)]
+    enc = runner.BertEncoder(params, batch=2, seq=48, heads=2, cuda_graph=True)
+    x = torch.from_numpy(rng.standard_normal((2, 48, 128)).astype(np.float32)).half()
+    y = enc(x.cuda()).clone()
+    ref = x.float().numpy()
+    for p in params:
+        ref = ops.bert_layer(ref, {k: v.half().float().numpy() for k, v in p.items()}, heads=2, store=np.float16).astype(np.float32)
+    assert_close(y, ref, torch.float16, atol=2e-2, what="3-layer stack")
+    assert enc.launches_per_forward == 21
+    y2 = enc(x.cuda())
+    assert torch.equal(y, y2)
+    status_ok()
+
+
+# ------------------------------------------------------------------------------------------------
+# config 4: MBConv block
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("fused", [True, False])
+def test_mbconv_golden(fused):
+    g = gold("mbconv")
+    p = {k: t(g[k]) for k in g.files if k not in ("x", "y")}
+    y = graphs.mbconv_sdfg(p, g["x"].shape, fused=fused)(input=t(g["x"]).cuda())
+    assert_close(y, g["y"], what="mbconv golden")
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_mbconv_config4_full_size(fused):
+    """Input [128,24,56,56] ~ N(0,1); 1x1 24->144 + Swish; depthwise 3x3 pad 1 + Swish; SE with 6 channels;
+    1x1 144->24 + residual; weights ~ N(0, 0.05); folded-BatchNorm biases ~ N(0, 0.05)."""
+    rng = np.random.default_rng(4)
+
+    def w(*s):
+        return torch.from_numpy((rng.standard_normal(s) * 0.05).astype(np.float32))
+    p = dict(w_exp=w(144, 24, 1, 1), b_exp=w(144), w_dw=w(144, 1, 3, 3), b_dw=w(144), w_se1=w(6, 144, 1, 1), b_se1=w(6),
+             w_se2=w(144, 6, 1, 1), b_se2=w(144), w_proj=w(24, 144, 1, 1), b_proj=w(24))
+    x = torch.from_numpy(rng.standard_normal((128, 24, 56, 56)).astype(np.float32))
+    y = graphs.mbconv_sdfg(p, tuple(x.shape), fused=fused)(input=x.cuda())
+    status_ok()
+    import torch.nn.functional as F
+    h = F.silu(F.conv2d(x, p["w_exp"], p["b_exp"]))
+    h = F.silu(F.conv2d(h, p["w_dw"], p["b_dw"], padding=1, groups=144))
+    s = h.mean((2, 3), keepdim=True)
+    s = torch.sigmoid(F.conv2d(F.silu(F.conv2d(s, p["w_se1"], p["b_se1"])), p["w_se2"], p["b_se2"]))
+    ref = F.conv2d(s * h, p["w_proj"], p["b_proj"]) + x
+    assert_close(y, ref, rtol=1e-4, atol=1e-5, what="config 4 vs torch fp32 (CPU)")
+    sub = ops.mbconv_block(x[:2].numpy(), {k: v.numpy() for k, v in p.items()})
+    assert_close(y[:2], sub, what="config 4 vs oracle (first two images)")
+
+
+# ------------------------------------------------------------------------------------------------
+# properties at full size
+# ------------------------------------------------------------------------------------------------
+def test_softmax_rows_sum_to_one_full_size():
+    x = torch.randn(8, 16, 512, 512, device="cuda", generator=torch.Generator("cuda").manual_seed(1)).half()
+    y = torch.empty_like(x)
+    K.softmax(x, y, rows=8 * 16 * 512, cols=512, scale=0.125)
+    sums = y.float().sum(-1)
+    assert float((sums - 1).abs().max()) < 4e-3
+    assert float(y.min()) >= 0.0
+
+
+def test_gemm_linearity_full_size():
+    gen = torch.Generator("cuda").manual_seed(2)
+    a1 = torch.randn(4096, 1024, device="cuda", generator=gen).half()
+    a2 = torch.randn(4096, 1024, device="cuda", generator=gen).half()
+    w = (torch.randn(4096, 1024, device="cuda", generator=gen) * 0.02).half()
+    y1, y2, y12 = (torch.empty(4096, 4096, dtype=torch.float16, device="cuda") for _ in range(3))
+    K.gemm(a1, w, y1, b_layout=1)
+    K.gemm(a2, w, y2, b_layout=1)
+    a12 = (a1.float() + a2.float()).half()
+    K.gemm(a12, w, y12, b_layout=1)
+    ref = y1.float() + y2.float()
+    assert float((y12.float() - ref).abs().max()) < 2e-2 * float(ref.abs().max())
+    # the transposed operand layout gives the same product
+    y_mn = torch.empty_like(y1)
+    K.gemm(a1, w.t().contiguous(), y_mn, b_layout=0)
+    assert float((y_mn.float() - y1.float()).abs().max()) <= 2e-3 * float(y1.float().abs().max())
+
+
+def test_attention_matches_unfused_kernels_full_size():
+    gen = torch.Generator("cuda").manual_seed(3)
+    B, h, S, d = 8, 16, 512, 64
+    qkv = torch.randn(B * S, 3 * h * d, device="cuda", generator=gen).half()
+    H = h * d
+    q = qkv[:, :H].view(B, S, h, d).permute(0, 2, 1, 3)
+    k = qkv[:, H:2 * H].view(B, S, h, d).permute(0, 2, 1, 3)
+    v = qkv[:, 2 * H:].view(B, S, h, d).permute(0, 2, 1, 3)
+    o = torch.empty(B, S, h, d, dtype=torch.float16, device="cuda")
+    K.attention(q, k, v, o.permute(0, 2, 1, 3), scale=0.125)
+    scores = torch.empty(B, h, S, S, dtype=torch.float16, device="cuda")
+    K.gemm_batched(q, k, scores, b_layout=1, alpha=0.125)
+    K.softmax(scores, scores, rows=B * h * S, cols=S)
+    o2 = torch.empty_like(o)
+    K.gemm_batched(scores, v, o2.permute(0, 2, 1, 3), b_layout=0)
+    assert_close(o, o2, torch.float16, atol=3e-3, what="fused attention vs QK^T / softmax / PV kernels")
+    status_ok()

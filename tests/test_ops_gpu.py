@@ -1,0 +1,364 @@
+"""Per-operator parity on the B200: the CUDA path (through the donnx frontend and the C ABI) against
+the CPU oracle and the committed golden vectors.  Shapes follow the reference's own tests
+(tests/pure_expansions/test_expansions.py, test_conv_expansion.py) plus ragged and empty cases."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import daceml_b200.onnx as donnx
+from daceml_b200 import kernels as K, lib as L, sdfg as sd
+from oracle import ops
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+DTYPES = [torch.float32, torch.float16]
+
+
+def gold(name):
+    return np.load(os.path.join(GOLD, name + ".npz"))
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dtype).cuda()
+
+
+def rounded(a, dtype):
+    """The oracle sees inputs already rounded to the storage type."""
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dtype).float().numpy()
+
+
+def empty(shape, dtype):
+    return torch.empty(shape, dtype=dtype, device="cuda")
+
+
+def status_ok():
+    torch.cuda.synchronize()
+    assert L.get_context(0).device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------
+# MatMul / Gemm / Einsum
+# ------------------------------------------------------------------------------------------------
+def test_matmul_expansion_reference_test():
+    """tests/pure_expansions/test_expansions.py:23-63, written against the same SDFG API."""
+    g = gold("matmul")
+    X, Z = g["a"], g["b"]
+    sdfg = sd.SDFG("matmul_expansion")
+    sdfg.add_array("X", X.shape, np.float32)
+    sdfg.add_array("Z", Z.shape, np.float32)
+    sdfg.add_array("__return", g["y"].shape, np.float32)
+    state = sdfg.add_state()
+    access_X, access_Z, access_result = state.add_access("X"), state.add_access("Z"), state.add_access("__return")
+    op_node = donnx.ONNXMatMul("Matmul")
+    state.add_node(op_node)
+    state.add_edge(access_X, None, op_node, "A", sdfg.make_array_memlet("X"))
+    state.add_edge(access_Z, None, op_node, "B", sdfg.make_array_memlet("Z"))
+    state.add_edge(op_node, "Y", access_result, None, sdfg.make_array_memlet("__return"))
+    sdfg.expand_library_nodes()
+    assert any(isinstance(n, sd.KernelTasklet) for n, _ in sdfg.all_nodes_recursive())
+    result = sdfg(X=X, Z=Z)
+    assert_close(result, g["y"], torch.float32, what="matmul golden")
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("a_shape, b_shape", [((2, 4), (4, 3)), ((3, 5, 8), (8, 6)), ((2, 3, 16, 8), (2, 3, 8, 24)),
+                                              ((130, 72), (72, 136)), ((8, 64, 256), (256, 512)), ((2, 4, 128, 64), (2, 4, 64, 128)),
+                                              ((5, 40), (3, 40, 24)), ((1, 8), (8, 1))])
+def test_matmul_shapes(dtype, a_shape, b_shape, rng):
+    a, b = rng.standard_normal(a_shape).astype(np.float32), rng.standard_normal(b_shape).astype(np.float32) * 0.2
+    ref = ops.matmul(rounded(a, dtype), rounded(b, dtype))
+    y = empty(ref.shape, dtype)
+    donnx.ONNXMatMul(A=dev(a, dtype), B=dev(b, dtype), Y=y)
+    assert_close(y, ref, dtype, what=f"matmul {a_shape}x{b_shape}")
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m, n, k", [(256, 512, 1024), (4096, 256, 64), (1000, 520, 264), (128, 64, 512), (300, 3072, 128)])
+def test_matmul_tensor_core_shapes(dtype, m, n, k, rng):
+    """Sizes that take the tcgen05 path in fp16 (all three tile widths, ragged edges, K not a multiple of 64)."""
+    a, b = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32) * 0.05
+    ref = ops.matmul(rounded(a, dtype), rounded(b, dtype))
+    y = empty((m, n), dtype)
+    donnx.ONNXMatMul(A=dev(a, dtype), B=dev(b, dtype), Y=y)
+    assert_close(y, ref, dtype, what=f"matmul {m}x{n}x{k}")
+    status_ok()
+
+
+def test_gemm_golden_and_rules():
+    g = gold("gemm")
+    y = empty((7, 5), torch.float32)
+    donnx.ONNXGemm(A=dev(g["a"]), B=dev(g["b"]), C=dev(g["c"]), Y=y, alpha=0.5, beta=2.0, transB=1)
+    assert_close(y, g["y"], what="gemm alpha/beta/transB")
+    donnx.ONNXGemm(A=dev(g["at"]), B=dev(g["bt"]), C=dev(g["c2"]), Y=y, transA=1)
+    assert_close(y, g["y2"], what="gemm transA, full C")
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_linear_export(dtype, rng):
+    """nn.Linear as exported: Gemm(alpha=1, beta=1, transB=1) with C[N]."""
+    a, w, c = (rng.standard_normal((512, 784)).astype(np.float32), rng.standard_normal((120, 784)).astype(np.float32) * 0.05,
+               rng.standard_normal(120).astype(np.float32))
+    ref = ops.gemm(rounded(a, dtype), rounded(w, dtype), rounded(c, dtype), trans_b=1)
+    y = empty((512, 120), dtype)
+    donnx.ONNXGemm(A=dev(a, dtype), B=dev(w, dtype), C=dev(c, dtype), Y=y, transB=1)
+    assert_close(y, ref, dtype, what="gemm linear")
+
+
+def test_einsum_reference_test():
+    """tests/pure_expansions/test_expansions.py:387-405 ('bij, jk -> bik')."""
+    g = gold("einsum")
+    y = empty(g["y"].shape, torch.float32)
+    donnx.ONNXEinsum(Inputs__0=dev(g["a"]), Inputs__1=dev(g["b"]), Output=y, equation="bij, jk -> bik")
+    assert_close(y, g["y"], what="einsum bij,jk->bik")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("eq, shapes", [("bik,bjk->bij", [(4, 160, 64), (4, 96, 64)]), ("ki,kj->ij", [(64, 40), (64, 24)]),
+                                        ("abcd->acbd", [(2, 3, 4, 5)]), ("yzik,yzkj->yzij", [(2, 3, 16, 8), (2, 3, 8, 24)])])
+def test_einsum_forms(dtype, eq, shapes, rng):
+    arrs = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+    ref = ops.einsum(eq, *[rounded(a, dtype) for a in arrs])
+    y = empty(ref.shape, dtype)
+    kwargs = {"Inputs__%d" % i: dev(a, dtype) for i, a in enumerate(arrs)}
+    donnx.ONNXEinsum(Output=y, equation=eq, **kwargs)
+    assert_close(y, ref, dtype, what=eq)
+
+
+# ------------------------------------------------------------------------------------------------
+# Softmax / reductions / element-wise
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_softmax_golden_axes(dtype):
+    g = gold("softmax")
+    x = g["x"]
+    for axis, key in ((3, "softmax_axis3"), (1, "softmax_axis1"), (-1, "softmax_axis3")):
+        y = empty(x.shape, dtype)
+        donnx.ONNXSoftmax(input=dev(x, dtype), output=y, axis=axis)
+        ref = ops.softmax(rounded(x, dtype), axis)
+        assert_close(y, ref, dtype, what=f"softmax axis {axis}")
+        if dtype == torch.float32:
+            assert_close(y, g[key], dtype, what=f"softmax golden axis {axis}")
+    y = empty((5, 16), dtype)
+    donnx.ONNXLogSoftmax(input=dev(x[0, 0], dtype), output=y, axis=1)
+    assert_close(y, ops.log_softmax(rounded(x[0, 0], dtype), 1), dtype, atol=1e-2 if dtype == torch.float16 else None,
+                 what="logsoftmax")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape, axis", [((4, 16, 64, 512), 3), ((4096, 10), 1), ((3, 1), 1), ((2, 5000), 1), ((7, 333), 1), ((1, 1, 1, 8), 3)])
+def test_softmax_shapes(dtype, shape, axis, rng):
+    x = (rng.standard_normal(shape) * 3).astype(np.float32)
+    y = empty(shape, dtype)
+    donnx.ONNXSoftmax(input=dev(x, dtype), output=y, axis=axis)
+    assert_close(y, ops.softmax(rounded(x, dtype), axis), dtype, what=f"softmax {shape}")
+
+
+@pytest.mark.parametrize("kind, keep, axes", [("Sum", True, [0]), ("Sum", False, [-1]), ("Sum", True, [0, -1]), ("Max", False, [0, -1]),
+                                              ("Max", True, [0]), ("Max", True, [-1]), ("Mean", True, [-1]), ("Mean", True, [0, -1]),
+                                              ("Mean", False, [0]), ("Min", True, [1])])
+def test_reduce_reference_cases(kind, keep, axes):
+    """tests/pure_expansions/test_expansions.py:187-237."""
+    g = gold("reduce")
+    key = "%s_%d_%s" % (kind.lower(), int(keep), "_".join(str(a) for a in axes))
+    y = empty(g[key].shape, torch.float32)
+    getattr(donnx, "ONNXReduce" + kind)(data=dev(g["x"]), reduced=y, axes=axes, keepdims=int(keep))
+    assert_close(y, g[key], atol=1e-5, what=key)
+
+
+def test_reduce_to_scalar_and_long_rows(rng):
+    g = gold("reduce")
+    y = empty((), torch.float32)
+    donnx.ONNXReduceMean(data=dev(g["x"]), reduced=y, keepdims=0)  # test_expansions.py:240-278
+    assert_close(y, g["mean_scalar"], what="mean to scalar")
+    big = rng.standard_normal((2, 1_500_000)).astype(np.float32)
+    y = empty((2, ), torch.float32)
+    donnx.ONNXReduceSum(data=dev(big), reduced=y, axes=[1], keepdims=0)  # sliced rows through the scratch buffer
+    assert_close(y, big.astype(np.float64).sum(1), rtol=1e-4, atol=1e-2, what="long-row sum")
+    one = rng.standard_normal((3_000_000, )).astype(np.float32)
+    y = empty((), torch.float32)
+    donnx.ONNXReduceMax(data=dev(one), reduced=y, keepdims=0)
+    assert float(y) == float(one.max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_elementwise_golden(dtype):
+    g = gold("elementwise")
+    x, yv = g["x"], g["y"]
+    xd, yd = dev(x, dtype), dev(yv, dtype)
+    xr, yr = rounded(x, dtype), rounded(yv, dtype)
+    out = empty(x.shape, dtype)
+    for node, ref in ((donnx.ONNXAdd, ops.add(xr, yr)), (donnx.ONNXSub, ops.sub(xr, yr)), (donnx.ONNXMul, ops.mul(xr, yr)),
+                      (donnx.ONNXDiv, ops.div(xr, yr))):
+        node(A=xd, B=yd, C=out)
+        assert_close(out, ref, dtype, what=node.__name__)
+    donnx.ONNXPow(X=xd, Y=torch.tensor(2.0, dtype=dtype, device="cuda"), Z=out)
+    assert_close(out, ops.pow_(xr, np.float32(2.0)), dtype, what="pow")
+    for node, conn, ref in ((donnx.ONNXErf, ("input", "output"), ops.erf(xr)), (donnx.ONNXTanh, ("input", "output"), ops.tanh(xr)),
+                            (donnx.ONNXExp, ("input", "output"), ops.exp(xr)), (donnx.ONNXRelu, ("X", "Y"), ops.relu(xr)),
+                            (donnx.ONNXSigmoid, ("X", "Y"), ops.sigmoid(xr)), (donnx.ONNXSoftplus, ("X", "Y"), ops.softplus(xr)),
+                            (donnx.ONNXGelu, ("X", "Y"), ops.gelu_chain(xr)), (donnx.ONNXSwish, ("X", "Y"), ops.swish(xr)),
+                            (donnx.ONNXIdentity, ("input", "output"), xr)):
+        node(**{conn[0]: xd, conn[1]: out})
+        assert_close(out, ref, dtype, what=node.__name__)
+    donnx.ONNXLeakyRelu(X=xd, Y=out, alpha=0.1)
+    assert_close(out, ops.leaky_relu(xr, 0.1), dtype, what="leakyrelu")
+    donnx.ONNXSqrt(X=dev(np.abs(x), dtype), Y=out)
+    assert_close(out, ops.sqrt(np.abs(xr)), dtype, what="sqrt")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_broadcast_forms(dtype, rng):
+    a = rng.standard_normal((8, 1, 16, 24)).astype(np.float32)
+    b = rng.standard_normal((1, 5, 16, 1)).astype(np.float32)
+    out = empty((8, 5, 16, 24), dtype)
+    donnx.ONNXAdd(A=dev(a, dtype), B=dev(b, dtype), C=out)
+    assert_close(out, ops.add(rounded(a, dtype), rounded(b, dtype)), dtype, what="general broadcast")
+    x = rng.standard_normal((4, 7, 1024)).astype(np.float32)
+    bias = rng.standard_normal((1024, )).astype(np.float32)
+    out = empty(x.shape, dtype)
+    donnx.ONNXSub(A=dev(bias, dtype), B=dev(x, dtype), C=out)
+    assert_close(out, ops.sub(rounded(bias, dtype), rounded(x, dtype)), dtype, what="vector - tensor")
+    mean = x.mean(-1, keepdims=True).astype(np.float32)
+    donnx.ONNXSub(A=dev(x, dtype), B=dev(mean, dtype), C=out)
+    assert_close(out, ops.sub(rounded(x, dtype), rounded(mean, dtype)), dtype, what="row broadcast")
+
+
+def test_cast_roundtrip(rng):
+    x = rng.standard_normal((1000, 33)).astype(np.float32)
+    h = empty(x.shape, torch.float16)
+    donnx.ONNXCast(input=dev(x), output=h, to=10)
+    assert torch.equal(h.cpu(), torch.from_numpy(x).half())
+    f = empty(x.shape, torch.float32)
+    donnx.ONNXCast(input=h, output=f, to=1)
+    assert torch.equal(f.cpu(), torch.from_numpy(x).half().float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape, perm", [((8, 64, 16, 64), (0, 2, 1, 3)), ((2, 40, 4, 64), (0, 2, 3, 1)), ((1024, 1000), (1, 0)),
+                                         ((3, 5, 7), None), ((2, 3, 4, 5, 6), (4, 0, 3, 1, 2)), ((17, ), (0, ))])
+def test_transpose_bit_exact(dtype, shape, perm, rng):
+    x = rng.standard_normal(shape).astype(np.float32)
+    xd = dev(x, dtype)
+    ref = ops.transpose(xd.cpu().numpy(), perm)
+    y = empty(ref.shape, dtype)
+    donnx.ONNXTranspose(data=xd, transposed=y, **({} if perm is None else {"perm": list(perm)}))
+    assert np.array_equal(y.cpu().numpy(), ref)
+
+
+def test_reshape_like_nodes(rng):
+    x = rng.standard_normal((4, 6, 10)).astype(np.float32)
+    y = empty((24, 10), torch.float32)
+    donnx.ONNXReshape(data=dev(x), reshaped=y)
+    assert np.array_equal(y.cpu().numpy(), x.reshape(24, 10))
+    y = empty((4, 60), torch.float32)
+    donnx.ONNXFlatten(input=dev(x), output=y, axis=1)
+    assert np.array_equal(y.cpu().numpy(), ops.flatten(x, 1))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layernorm_fused_matches_chain(dtype):
+    g = gold("layernorm")
+    x, ga, be = g["x"], g["gamma"], g["beta"]
+    y = empty(x.shape, dtype)
+    donnx.ONNXLayerNormalization(X=dev(x, dtype), Scale=dev(ga, dtype), B=dev(be, dtype), Y=y, epsilon=1e-12)
+    assert_close(y, ops.layernorm_chain(rounded(x, dtype), rounded(ga, dtype), rounded(be, dtype), 1e-12), dtype, what="layernorm")
+    r = np.roll(x, 1, axis=0)
+    donnx.ONNXLayerNormalization(X=dev(x, dtype), Residual=dev(r, dtype), Scale=dev(ga, dtype), B=dev(be, dtype), Y=y, epsilon=1e-12)
+    ref = ops.layernorm_chain(rounded(x, dtype) + rounded(r, dtype), rounded(ga, dtype), rounded(be, dtype), 1e-12)
+    assert_close(y, ref, dtype, what="layernorm + residual")
+
+
+# ------------------------------------------------------------------------------------------------
+# Conv
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("idx, bias", [(0, True), (1, False), (2, True), (3, False)])
+def test_conv_simple_reference_test(idx, bias):
+    """tests/pure_expansions/test_conv_expansion.py:9-66 through the traced-program frontend."""
+    g = gold("conv")
+    X, W, Z = g["x%d" % idx], g["w%d" % idx], g["y%d" % idx]
+    dace_Z = np.zeros_like(Z)
+    if bias:
+        B = g["b%d" % idx]
+
+        @donnx.program
+        def conv(X_: (np.float32, X.shape), W_: (np.float32, W.shape), B_: (np.float32, B.shape), Z_: (np.float32, Z.shape)):
+            donnx.ONNXConv(X=X_, W=W_, B=B_, Y=Z_)
+
+        sdfg = conv.to_sdfg()
+        sdfg.expand_library_nodes()
+        sdfg(X_=X, W_=W, Z_=dace_Z, B_=B)
+    else:
+
+        @donnx.program
+        def conv(X_: (np.float32, X.shape), W_: (np.float32, W.shape), Z_: (np.float32, Z.shape)):
+            donnx.ONNXConv(X=X_, W=W_, Y=Z_)
+
+        sdfg = conv.to_sdfg()
+        sdfg.expand_library_nodes()
+        sdfg(X_=X, W_=W, Z_=dace_Z)
+    assert np.allclose(Z, dace_Z)
+    assert_close(dace_Z, Z, torch.float32, what="conv golden")
+
+
+def test_conv_strided_padded_grouped_golden():
+    g = gold("conv")
+    y = empty(g["ys"].shape, torch.float32)
+    donnx.ONNXConv(X=dev(g["xs"]), W=dev(g["ws"]), Y=y, strides=[2, 2])
+    assert_close(y, g["ys"], what="strided conv")
+    y = empty(g["yg"].shape, torch.float32)
+    donnx.ONNXConv(X=dev(g["xg"]), W=dev(g["wg"]), B=dev(g["bg"]), Y=y, strides=[2, 1], pads=[1, 0, 2, 1], dilations=[1, 2], group=2)
+    assert_close(y, g["yg"], what="strided / padded / dilated / grouped conv")
+    y = empty(g["yd"].shape, torch.float32)
+    donnx.ONNXConv(X=dev(g["xd"]), W=dev(g["wd"]), Y=y, pads=[1, 1, 1, 1], group=12)
+    assert_close(y, g["yd"], what="depthwise conv")
+    p = empty((2, 12, 1, 1), torch.float32)
+    donnx.ONNXGlobalAveragePool(X=dev(g["xd"]), Y=p)
+    assert_close(p, g["gap"], what="global average pool")
+    status_ok()
+
+
+def test_conv_config1_full_size(rng):
+    """BASELINE config 1: X[32,3,64,64] ~ N(0,1), W[16,3,3,3] ~ U(0,1), stride 2, no pad, no bias."""
+    x = rng.standard_normal((32, 3, 64, 64)).astype(np.float32)
+    w = rng.random((16, 3, 3, 3), np.float32)
+    y = empty((32, 16, 31, 31), torch.float32)
+    donnx.ONNXConv(X=dev(x), W=dev(w), Y=y, strides=[2, 2])
+    assert_close(y, ops.conv2d(x, w, strides=(2, 2)), what="config 1")
+
+
+@pytest.mark.parametrize("cin, cout, hw", [(24, 144, (56, 56)), (144, 24, (56, 56)), (5, 40, (6, 10)), (40, 7, (4, 4)), (3, 3, (5, 5))])
+def test_conv_pointwise(cin, cout, hw, rng):
+    x = rng.standard_normal((3, cin) + hw).astype(np.float32)
+    w = (rng.standard_normal((cout, cin, 1, 1)) * 0.1).astype(np.float32)
+    b = rng.standard_normal(cout).astype(np.float32)
+    y = empty((3, cout) + hw, torch.float32)
+    donnx.ONNXConv(X=dev(x), W=dev(w), B=dev(b), Y=y)
+    assert_close(y, ops.conv2d(x, w, b), what=f"1x1 conv {cin}->{cout}")
+
+
+# ------------------------------------------------------------------------------------------------
+# Edge cases of the C ABI
+# ------------------------------------------------------------------------------------------------
+def test_empty_tensors_launch_nothing():
+    before = L.launch_count()
+    x = empty((0, 16), torch.float32)
+    K.unary(x, x, L.UN_RELU)
+    K.softmax(x, x, rows=0, cols=16)
+    K.gemm(empty((0, 8), torch.float16), empty((8, 4), torch.float16), empty((0, 4), torch.float16))
+    assert L.launch_count() == before
+
+
+def test_invalid_arguments_raise():
+    a, b = empty((4, 8), torch.float16), empty((9, 4), torch.float16)
+    with pytest.raises(L.B200Error):
+        K.gemm(a, b, empty((4, 4), torch.float16))
+    with pytest.raises(L.B200Error):
+        K.unary(torch.zeros(4), torch.zeros(4), L.UN_RELU)  # CPU tensors: no CPU path
+    with pytest.raises(L.Unsupported):
+        K.unary(empty((4, ), torch.float64), empty((4, ), torch.float64), L.UN_RELU)
