@@ -44,7 +44,7 @@ class BertEncoder:
                  eps=1e-12):
         if not torch.cuda.is_available():
             raise L.B200Error(L.ERR_CUDA, "BertEncoder needs a B200; there is no CPU path")
-        self.device = torch.device(device if device is not None else ("cuda", torch.cuda.current_device()))
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.batch, self.seq, self.heads = batch, seq, heads
         self.hidden = layer_params[0]["wq"].shape[0]
         shape = (batch, seq, self.hidden)
