@@ -6,7 +6,7 @@
 //            (so Q/K/V may live inside a packed [T, 3H] projection output - no head split);
 //   warp 1   tcgen05.mma S = Q K_j^T (128x128x64) into TMEM, later O_j = P_j V_j (128x64x128);
 //            V is consumed MN-major exactly as TMA lays it down - no transpose;
-//   warps 2-5  one query row per thread: read S from TMEM, online softmax in the log2 domain,
+//   warps 2-9  two threads per query row (64 keys each): read S from TMEM, online softmax in the log2 domain,
 //            write P_j (fp16) into shared memory in the 128-byte-swizzled K-major layout the MMA
 //            reads, then fold O_j into the fp32 running output held in registers.
 // The scores never touch HBM: traffic is Q, K, V in and O out.
@@ -19,13 +19,15 @@ namespace b200ml {
 
 namespace {
 
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 320;  // TMA warp, MMA warp, eight softmax warps
 constexpr int QT = 128;   // query rows per CTA
 constexpr int KT = 128;   // keys per iteration
 constexpr int HD = 64;    // head dimension
 constexpr int TILE_BYTES = 128 * HD * 2;         // 16 KB: Q, K_j or V_j
 constexpr int P_BYTES = QT * KT * 2;             // 32 KB: two 64-column swizzle atoms
-constexpr int AT_SMEM = 3 * TILE_BYTES + P_BYTES + 256 + 1024;
+constexpr int XCHG_FLOATS = 768;                 // row maxima (two parities) and row sums exchanged between half-warps
+constexpr int KV_SLOTS = 3;                      // K_0, V_0, K_1, V_1, ... travel through a ring of three tiles
+constexpr int AT_SMEM = (1 + KV_SLOTS) * TILE_BYTES + P_BYTES + 256 + XCHG_FLOATS * 4 + 1024;
 constexpr uint32_t AT_TMEM_COLS = 256;           // S: columns [0,128), O_j: [128,192)
 
 struct AttnArgs {
@@ -35,7 +37,14 @@ struct AttnArgs {
     __half* o;
     const __half* mask;  // [batch, seq_kv] additive, or null
     int32_t* status;
+    long long* trace;
 };
+
+#ifdef B200ML_TRACE
+#define AT_MARK(i) do { const long long _n = clock64(); tr[i] += _n - tr_last; tr_last = _n; } while (0)
+#else
+#define AT_MARK(i)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -49,19 +58,17 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sq = smem;
-    uint8_t* sk = smem + TILE_BYTES;
-    uint8_t* sv = smem + 2 * TILE_BYTES;
-    uint8_t* sp = smem + 3 * TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES + P_BYTES);
+    uint8_t* skv = smem + TILE_BYTES;  // KV_SLOTS tiles
+    uint8_t* sp = smem + (1 + KV_SLOTS) * TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sp + P_BYTES);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;
-    uint64_t* v_full = bars + 2;
-    uint64_t* k_empty = bars + 3;
-    uint64_t* v_empty = bars + 4;
-    uint64_t* s_full = bars + 5;
-    uint64_t* p_full = bars + 6;
-    uint64_t* o_full = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* kv_full = bars + 1;                // [KV_SLOTS]
+    uint64_t* kv_empty = bars + 1 + KV_SLOTS;    // [KV_SLOTS]
+    uint64_t* s_full = bars + 1 + 2 * KV_SLOTS;
+    uint64_t* p_full = s_full + 1;
+    uint64_t* o_full = s_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 3);
+    float* xchg = reinterpret_cast<float*>(sp + P_BYTES + 256);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -80,12 +87,12 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (warp == 1) {
         if (lane == 0) {
             ptx::mbar_init(q_full, 1);
-            ptx::mbar_init(k_full, 1);
-            ptx::mbar_init(v_full, 1);
-            ptx::mbar_init(k_empty, 1);
-            ptx::mbar_init(v_empty, 1);
+            for (int i = 0; i < KV_SLOTS; ++i) {
+                ptx::mbar_init(&kv_full[i], 1);
+                ptx::mbar_init(&kv_empty[i], 1);
+            }
             ptx::mbar_init(s_full, 1);
-            ptx::mbar_init(p_full, 128);
+            ptx::mbar_init(p_full, 8);  // one arrival per softmax warp
             ptx::mbar_init(o_full, 1);
             ptx::fence_mbar_init();
         }
@@ -105,20 +112,18 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (ptx::elect_one()) {
             ptx::mbar_expect_tx(q_full, TILE_BYTES);
             ptx::tma_load_4d(sq, &tmap_q, q_full, 0, q0, head, batch);
-            for (int j = 0; j < n_kv; ++j) {
-                const uint32_t par = j & 1;
-                if (!ptx::mbar_wait(k_empty, par ^ 1)) {
+            // item 2j is K_j, item 2j + 1 is V_j; item i lives in slot i % 3, so K_{j+1} is in flight while
+            // tile j is being worked on
+            for (int i = 0; i < 2 * n_kv; ++i) {
+                const int slot = i % KV_SLOTS;
+                const uint32_t par = (i / KV_SLOTS) & 1;
+                if (!ptx::mbar_wait(&kv_empty[slot], par ^ 1)) {
                     atomicExch(args.status, DEV_TIMEOUT_ATTN);
                     break;
                 }
-                ptx::mbar_expect_tx(k_full, TILE_BYTES);
-                ptx::tma_load_4d(sk, &tmap_k, k_full, 0, j * KT, head, batch);
-                if (!ptx::mbar_wait(v_empty, par ^ 1)) {
-                    atomicExch(args.status, DEV_TIMEOUT_ATTN);
-                    break;
-                }
-                ptx::mbar_expect_tx(v_full, TILE_BYTES);
-                ptx::tma_load_4d(sv, &tmap_v, v_full, 0, j * KT, head, batch);
+                ptx::mbar_expect_tx(&kv_full[slot], TILE_BYTES);
+                ptx::tma_load_4d(skv + slot * TILE_BYTES, (i & 1) ? &tmap_v : &tmap_k, &kv_full[slot], 0, (i >> 1) * KT, head,
+                                 batch);
             }
         }
     } else if (warp == 1) {
@@ -126,18 +131,19 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (ptx::elect_one()) {
             constexpr uint32_t IDESC_S = ptx::make_idesc_f16(128, KT, 0, 0);  // Q, K both K-major
             constexpr uint32_t IDESC_O = ptx::make_idesc_f16(128, HD, 0, 1);  // P K-major, V MN-major
-            const uint32_t q_addr = ptx::smem_u32(sq), k_addr = ptx::smem_u32(sk), v_addr = ptx::smem_u32(sv),
-                           p_addr = ptx::smem_u32(sp);
+            const uint32_t q_addr = ptx::smem_u32(sq), kv_addr = ptx::smem_u32(skv), p_addr = ptx::smem_u32(sp);
             bool ok = ptx::mbar_wait(q_full, 0);
             if (!ok) atomicExch(args.status, DEV_TIMEOUT_ATTN);
             for (int j = 0; ok && j < n_kv; ++j) {
                 const uint32_t par = j & 1;
                 // S_j = Q K_j^T
-                if (!ptx::mbar_wait(k_full, par)) {
+                const int ik = 2 * j, sk_ = ik % KV_SLOTS;
+                if (!ptx::mbar_wait(&kv_full[sk_], (ik / KV_SLOTS) & 1)) {
                     atomicExch(args.status, DEV_TIMEOUT_ATTN);
                     break;
                 }
                 ptx::tc_fence_after();
+                const uint32_t k_addr = kv_addr + sk_ * TILE_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint64_t a = ptx::make_smem_desc_sw128(q_addr + kk * 32, 16, 1024);
@@ -145,13 +151,15 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                     ptx::mma_f16_ss(tmem_s, a, b, IDESC_S, kk != 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(s_full);
-                ptx::mma_commit(k_empty);
+                ptx::mma_commit(&kv_empty[sk_]);
                 // O_j = P_j V_j
-                if (!ptx::mbar_wait(p_full, par) || !ptx::mbar_wait(v_full, par)) {
+                const int iv = 2 * j + 1, sv_ = iv % KV_SLOTS;
+                if (!ptx::mbar_wait(p_full, par) || !ptx::mbar_wait(&kv_full[sv_], (iv / KV_SLOTS) & 1)) {
                     atomicExch(args.status, DEV_TIMEOUT_ATTN);
                     break;
                 }
                 ptx::tc_fence_after();
+                const uint32_t v_addr = kv_addr + sv_ * TILE_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
                     // P: atom kk / 4 (64 keys each, 16 KB apart), 32 bytes per step inside the atom
@@ -161,144 +169,162 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                     ptx::mma_f16_ss(tmem_o, a, b, IDESC_O, kk != 0 ? 1u : 0u);
                 }
                 ptx::mma_commit(o_full);
-                ptx::mma_commit(v_empty);
+                ptx::mma_commit(&kv_empty[sv_]);
             }
         }
     } else {
         // ------------------------------ softmax + output ------------------------------
+        // Eight warps: warps q and q + 4 share TMEM lane quarter q; each thread owns one query row
+        // and one half (64 keys) of the 128-key tile, and one half (32 columns) of the output row.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;  // row of the query tile == TMEM lane
         const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-        float acc[HD];
+        const uint32_t s_addr = tmem_s + lane_off + half * 64;
+        const uint32_t o_addr = tmem_o + lane_off + half * 32;
+        uint8_t* p_row = sp + half * (QT * 128) + row * 128;  // this thread's 128-byte row of atom `half`
+        float acc[HD / 2];
 #pragma unroll
-        for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < HD / 2; ++i) acc[i] = 0.0f;
         float m_run = -INFINITY, l_run = 0.0f;
         const __half* mrow = args.mask ? args.mask + static_cast<int64_t>(batch) * args.seq_kv : nullptr;
         constexpr float LOG2E = 1.44269504088896340736f;
+#ifdef B200ML_TRACE
+        long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long tr_last = clock64();
+#endif
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
             const uint32_t par = j & 1;
-            const int kv0 = j * KT;
+            const int kv0 = j * KT + half * 64;  // first key of this thread's half
             if (!ptx::mbar_wait(s_full, par)) {
                 if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
                 ok = false;
                 break;
             }
             ptx::tc_fence_after();
-            // A tile is "plain" when every key is in range and there is no additive mask: the
-            // scale then commutes with the maximum and each score costs one FMNMX in pass 1 and
-            // one FFMA + one MUFU.EX2 + one FADD in pass 2.
-            const bool plain = (kv0 + KT <= args.seq_kv) && mrow == nullptr && args.scale_log2 > 0.0f;
-            // pass 1: running maximum of the scaled, masked scores (log2 domain)
-            float mx = m_run;
+            AT_MARK(0);  // waited for S
+            // A tile is "plain" when every key is in range and there is no additive mask: the scale
+            // then commutes with the maximum (one FMNMX per score) and P costs FFMA + EX2 + FADD.
+            // The scores are read from TMEM once per pass, 32 columns at a time, to keep the
+            // register footprint at two CTAs per SM.
+            const bool plain = (j * KT + KT <= args.seq_kv) && mrow == nullptr && args.scale_log2 > 0.0f;
+            float mx = -INFINITY;
             if (plain) {
-                float raw = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < KT / 32; c += 2) {
-                    uint32_t r0[32], r1[32];
-                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r0);
-                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32 + 32, r1);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(s_addr + u * 32, r);
                     ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) raw = fmaxf(raw, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
                 }
-                mx = fmaxf(mx, raw * args.scale_log2);
             } else {
 #pragma unroll 1
-                for (int c = 0; c < KT / 32; ++c) {
+                for (int u = 0; u < 2; ++u) {
                     uint32_t r[32];
-                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
+                    ptx::tmem_ld_32x32b_x32(s_addr + u * 32, r);
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int kv = kv0 + c * 32 + i;
-                        float t = __uint_as_float(r[i]) * args.scale_log2;
-                        if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
-                        if (kv >= args.seq_kv) t = -INFINITY;
-                        mx = fmaxf(mx, t);
+                        const int kv = kv0 + u * 32 + i;
+                        float v = __uint_as_float(r[i]) * args.scale_log2;
+                        if (mrow && kv < args.seq_kv) v = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, v);
+                        if (kv >= args.seq_kv) v = -INFINITY;
+                        mx = fmaxf(mx, v);
                     }
                 }
             }
+            if (plain) mx *= args.scale_log2;
+            AT_MARK(1);  // pass 1
+            // combine the two halves' maxima (the partner warp has the same lane quarter)
+            xchg[(j & 1) * 256 + half * 128 + row] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            mx = fmaxf(fmaxf(mx, xchg[(j & 1) * 256 + (half ^ 1) * 128 + row]), m_run);
+            AT_MARK(2);  // exchange
             const float m_safe = (mx == -INFINITY) ? 0.0f : mx;
             const float alpha = ex2(m_run - m_safe);  // 0 on the first tile
-            // pass 2: P = exp2(t - m), row sum, fp16 P into swizzled shared memory
             float sum = 0.0f;
             if (plain) {
                 const float neg_m = -m_safe;
-#pragma unroll 1
-                for (int c = 0; c < KT / 32; c += 2) {
-                    uint32_t r[2][32];
-                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r[0]);
-                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32 + 32, r[1]);
-                    ptx::tmem_ld_wait();
-                    uint8_t* atom = sp + (c >> 1) * (QT * 128) + row * 128;  // chunks c, c+1 = one 64-key atom
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            float p[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                p[i] = ex2(fmaf(__uint_as_float(r[u][g * 8 + i]), args.scale_log2, neg_m));
-                                sum += p[i];
-                            }
-                            const int chunk = u * 4 + g;  // 16-byte chunk within the 128-byte row
-                            *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = pack8(p);
-                        }
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < KT / 32; ++c) {
+                for (int u = 0; u < 2; ++u) {
                     uint32_t r[32];
-                    ptx::tmem_ld_32x32b_x32(tmem_s + lane_off + c * 32, r);
+                    ptx::tmem_ld_32x32b_x32(s_addr + u * 32, r);
                     ptx::tmem_ld_wait();
-                    uint8_t* atom = sp + (c >> 1) * (QT * 128) + row * 128;
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         float p[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            const int kv = kv0 + c * 32 + g * 8 + i;
-                            float t = __uint_as_float(r[g * 8 + i]) * args.scale_log2;
-                            if (mrow && kv < args.seq_kv) t = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, t);
-                            p[i] = kv < args.seq_kv ? ex2(t - m_safe) : 0.0f;
+                            p[i] = ex2(fmaf(__uint_as_float(r[g * 8 + i]), args.scale_log2, neg_m));
                             sum += p[i];
                         }
-                        const int chunk = (c & 1) * 4 + g;  // 16-byte chunk within the 128-byte row
-                        *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = pack8(p);
+                        *reinterpret_cast<uint4*>(p_row + (((u * 4 + g) ^ (row & 7)) << 4)) = pack8(p);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int u = 0; u < 2; ++u) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(s_addr + u * 32, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float p[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int kv = kv0 + u * 32 + g * 8 + i;
+                            float v = __uint_as_float(r[g * 8 + i]) * args.scale_log2;
+                            if (mrow && kv < args.seq_kv) v = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, v);
+                            p[i] = kv < args.seq_kv ? ex2(v - m_safe) : 0.0f;
+                            sum += p[i];
+                        }
+                        *reinterpret_cast<uint4*>(p_row + (((u * 4 + g) ^ (row & 7)) << 4)) = pack8(p);
                     }
                 }
             }
+            AT_MARK(3);  // pass 2
             l_run = fmaf(l_run, alpha, sum);
             m_run = mx;
             ptx::fence_proxy_async_smem();  // P visible to the tensor core's shared-memory reads
             ptx::tc_fence_before();
-            ptx::mbar_arrive(p_full);
-            // fold O_j into the running output
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(p_full);
+            AT_MARK(4);  // fence + arrive
+            // fold this thread's half of O_j into the running output
             if (!ptx::mbar_wait(o_full, par)) {
                 if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
                 ok = false;
                 break;
             }
             ptx::tc_fence_after();
+            AT_MARK(5);  // waited for O
+            uint32_t ro[32];
+            ptx::tmem_ld_32x32b_x32(o_addr, ro);
+            ptx::tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(tmem_o + lane_off + c * 32, r);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[i]));
-            }
+            for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], alpha, __uint_as_float(ro[i]));
             ptx::tc_fence_before();
+            AT_MARK(6);  // O accumulate
         }
+#ifdef B200ML_TRACE
+        if (threadIdx.x == 64 && blockIdx.x < 512) {
+            for (int i = 0; i < 7; ++i) args.trace[blockIdx.x * 8 + i] = tr[i];
+        }
+#endif
+        // the row sum is the sum of both halves' partial sums (they share every running maximum)
+        xchg[512 + half * 128 + row] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+        const float l_tot = l_run + xchg[512 + (half ^ 1) * 128 + row];
         const int q = q0 + row;
         if (ok && q < args.seq_q) {
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            __half* op = args.o + batch * args.o_stride_b + head * args.o_stride_h + static_cast<int64_t>(q) * args.o_stride_s;
+            const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+            __half* op = args.o + batch * args.o_stride_b + head * args.o_stride_h + static_cast<int64_t>(q) * args.o_stride_s +
+                         half * 32;
             if ((reinterpret_cast<uintptr_t>(op) & 15) == 0) {
 #pragma unroll
-                for (int g = 0; g < HD / 8; ++g) {
+                for (int g = 0; g < 4; ++g) {
                     float v[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[i] = acc[g * 8 + i] * inv;
@@ -306,7 +332,7 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < HD; ++i) op[i] = __float2half_rn(acc[i] * inv);
+                for (int i = 0; i < 32; ++i) op[i] = __float2half_rn(acc[i] * inv);
             }
         }
     }
@@ -371,6 +397,7 @@ int attention_f16(const b200ml_ctx* ctx, const b200ml_attention_params* p, cudaS
     a.o = static_cast<__half*>(p->o);
     a.mask = static_cast<const __half*>(p->mask);
     a.status = ctx->status_dev;
+    a.trace = static_cast<long long*>(ctx->workspace);
     const int64_t grid = p->batch * p->heads * a.q_tiles;
     B200ML_REQUIRE(grid < (1ll << 31), "attention: grid too large");
     static bool configured[64] = {};

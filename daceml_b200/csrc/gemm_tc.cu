@@ -15,46 +15,15 @@
 // Gemm with transB=1) or MN-major ([K,N] row-major, the ONNX MatMul operand); both are fed to the
 // MMA directly, so no Transpose node has to run.  Two batch loops are folded into the TMA
 // coordinates, which lets attention read Q, K, V per head straight out of a packed [T, 3H] buffer.
-#include "common.cuh"
-#include "ptx.cuh"
-#include "epilogue.cuh"
+#include "gemm_common.cuh"
+
+#include <stdlib.h>
 
 namespace b200ml {
 
+using namespace gemm;
+
 namespace {
-
-constexpr int BM = 128;
-constexpr int BK = 64;  // 64 fp16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
-constexpr int A_TILE_BYTES = BM * BK * 2;
-constexpr int EPI_WARPS = 8;  // two per TMEM lane quarter, each taking half of the tile's columns
-constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
-
-struct GemmArgs {
-    int32_t m, n, k;
-    int32_t tiles_m, tiles_n, num_tiles;
-    int32_t batch_inner;
-    int32_t epilogue;
-    // 0 when the operand is broadcast over that batch loop (its TMA coordinate stays 0)
-    int32_t a_use_inner, a_use_outer, b_use_inner, b_use_outer;
-    int64_t ldc, c_so, c_si;
-    int64_t ldr, r_so, r_si;
-    float alpha, bias_scale, residual_scale;
-    int32_t vec_ok;  // C (and residual) rows are 16-byte aligned
-    __half* c;
-    const __half* bias;
-    const __half* residual;
-    int32_t* status;
-    long long* trace;  // per-CTA cycle counters, only written when built with B200ML_TRACE
-};
-
-#ifdef B200ML_TRACE
-#define TRACE_T0() const long long _t0 = clock64()
-#define TRACE_ADD(var) var += clock64() - _t0
-#else
-#define TRACE_T0()
-#define TRACE_ADD(var)
-#endif
 
 template <int BN>
 struct GemmSmem {
@@ -317,40 +286,6 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// rank-4 fp16 tensor map {inner, rows, batch_inner, batch_outer} with a 128-byte-swizzled box.
-int make_tmap(const b200ml_ctx* ctx, CUtensorMap* out, const void* base, int64_t inner, int64_t rows, int64_t ld,
-              int64_t n_inner, int64_t s_inner, int64_t n_outer, int64_t s_outer, int box_inner, int box_rows,
-              const char* what) {
-    if (!aligned16(base)) return fail(B200ML_ERR_UNSUPPORTED, "gemm f16: %s base is not 16-byte aligned", what);
-    if (ld % 8 != 0) return fail(B200ML_ERR_UNSUPPORTED, "gemm f16: %s leading dimension %lld is not a multiple of 8", what, (long long)ld);
-    const bool use_i = n_inner > 1 && s_inner != 0;
-    const bool use_o = n_outer > 1 && s_outer != 0;
-    if ((use_i && s_inner % 8 != 0) || (use_o && s_outer % 8 != 0))
-        return fail(B200ML_ERR_UNSUPPORTED, "gemm f16: %s batch stride is not a multiple of 8 elements", what);
-    const uint64_t row_bytes = static_cast<uint64_t>(ld) * 2;
-    cuuint64_t dims[4] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows),
-                          static_cast<cuuint64_t>(use_i ? n_inner : 1), static_cast<cuuint64_t>(use_o ? n_outer : 1)};
-    // A size-1 dimension still needs a legal stride (non-zero multiple of 16 bytes).
-    const uint64_t dummy = row_bytes * static_cast<uint64_t>(rows);
-    cuuint64_t strides[3] = {row_bytes, use_i ? static_cast<uint64_t>(s_inner) * 2 : dummy,
-                             use_o ? static_cast<uint64_t>(s_outer) * 2 : dummy};
-    cuuint32_t box[4] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows), 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    if (!fn) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d (dims %llu x %llu, ld %lld)", what,
-                    (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (long long)ld);
-    return B200ML_OK;
-}
-
 template <int BN, bool B_MN>
 int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, cudaStream_t stream) {
     using S = GemmSmem<BN>;
@@ -368,6 +303,16 @@ int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, 
 }  // namespace
 
 int gemm_f16_simt(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
+int gemm_f16_pair(const b200ml_ctx* ctx, const b200ml_gemm_params* p, GemmArgs& args, int bn, cudaStream_t stream);
+
+// B200ML_GEMM_PAIR=0 keeps every GEMM on the one-CTA kernel (for A/B comparisons).
+static bool pair_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200ML_GEMM_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 // Tile width.  The main loop of a 128 x 256 tile needs 48 KB per 64-deep k-block, which is what one
 // SM can pull from L2 in the time the tensor core takes; narrower tiles are load-bound, so they
@@ -417,6 +362,13 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
         vec = vec && aligned16(p->residual) && p->ldr % 8 == 0 && p->r_stride_inner % 8 == 0 && p->r_stride_outer % 8 == 0;
     if (p->bias) vec = vec && aligned16(p->bias);
     args.vec_ok = vec ? 1 : 0;
+
+    // Tall enough outputs go to CTA pairs (256-row tiles): a third less operand traffic per SM.
+    if (pair_enabled() && p->m > BM && bn >= 128 && ctx->sm_count >= 2) {
+        args.tiles_m = (int32_t)ceil_div(p->m, 2 * BM);
+        args.num_tiles = (int32_t)((int64_t)args.tiles_m * args.tiles_n * batches);
+        return gemm_f16_pair(ctx, p, args, bn, stream);
+    }
 
     CUtensorMap ta, tb;
     int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, p->batch_inner, p->a_stride_inner, p->batch_outer,
