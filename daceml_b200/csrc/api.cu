@@ -3,12 +3,21 @@
 
 #include <cuda.h>
 #include <string.h>
+#include <stdlib.h>
 #include <new>
 
 namespace b200ml {
 
 static thread_local char g_error[512] = "";
 std::atomic<int64_t> g_launches{0};
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200ML_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 void set_error(const char* fmt, ...) {
     va_list ap;

@@ -47,9 +47,39 @@ inline int check_launch(const char* what) {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch: a kernel launched through launch_pdl() may start while its
+// predecessor in the stream is still draining, run its set-up (barrier init, TMEM allocation,
+// descriptor prefetch) and then block in pdl_wait() until the predecessor has completed and its
+// writes are visible.  B200ML_PDL=0 turns the attribute off (plain stream order).
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace b200ml
+
+#ifdef __CUDACC__
+// Lets the next kernel in the stream begin its set-up.  Issued first thing by every CTA, so a
+// dependent grid can only start once all CTAs of this grid have been scheduled.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+// Blocks until every kernel before this one in the stream has completed and flushed its writes.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 #define B200ML_REQUIRE(cond, ...)                                         \
     do {                                                                  \

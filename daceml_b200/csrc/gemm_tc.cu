@@ -51,6 +51,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_kb = (args.k + BK - 1) / BK;
@@ -79,6 +80,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();  // everything above overlaps the previous kernel's tail
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -139,6 +141,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             bool ok = true;
             long long tr_wait_acc = 0, tr_wait_full = 0;
             const long long tr_begin = clock64();
+            const unsigned long long tr_gt0 = ptx::global_timer_ns();
             for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
                 {
                     TRACE_T0();
@@ -186,6 +189,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             args.trace[blockIdx.x * 16 + 2] = tr_wait_acc;
             args.trace[blockIdx.x * 16 + 3] = tr_wait_full;
             args.trace[blockIdx.x * 16 + 4] = clock64() - tr_begin;
+            args.trace[blockIdx.x * 16 + 8] = (long long)(ptx::global_timer_ns() - tr_gt0);
 #endif
         }
     } else {
@@ -296,7 +300,7 @@ int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, 
         configured[ctx->device & 63] = true;
     }
     const int grid = args.num_tiles < ctx->sm_count ? args.num_tiles : ctx->sm_count;
-    kernel<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, args);
+    B200ML_CUDA(launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, args));
     return check_launch("gemm_f16_tc");
 }
 

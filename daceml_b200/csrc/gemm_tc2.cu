@@ -50,6 +50,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t cta = ptx::cluster_ctarank();  // 0: leader (issues the MMAs), 1: peer
@@ -82,6 +83,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     ptx::cluster_sync();  // both CTAs' barriers exist before any remote arrive or load completion
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();  // everything above overlaps the previous kernel's tail
 
     if (warp == 0) {
         // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -259,7 +261,7 @@ int launch_pair(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap&
     }
     const int max_pairs = ctx->sm_count / 2;
     const int pairs = args.num_tiles < max_pairs ? args.num_tiles : max_pairs;
-    kernel<<<2 * pairs, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, args);
+    B200ML_CUDA(launch_pdl(kernel, dim3(2 * pairs), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, args));
     return check_launch("gemm_f16_pair");
 }
 

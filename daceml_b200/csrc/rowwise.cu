@@ -216,6 +216,8 @@ __global__ void __launch_bounds__(128) layernorm_warp_kernel(const T* __restrict
                                                              const T* __restrict__ beta, T* __restrict__ y,
                                                              int64_t rows, int cols, float eps) {
     constexpr int V = Vec<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -339,9 +341,9 @@ int layernorm_t(const T* x, const T* residual, const T* bias, const T* gamma, co
         const int64_t blocks = ceil_div(rows, warps);
         B200ML_REQUIRE(blocks < (1ll << 31), "layernorm: too many rows");
         const int iters = (int)ceil_div(packets, 32);
-#define LN_LAUNCH(I)                                                                                               \
-    layernorm_warp_kernel<T, I><<<(unsigned)blocks, warps * 32, 0, stream>>>(x, residual, bias, gamma, beta, y, rows, \
-                                                                           (int)cols, eps)
+#define LN_LAUNCH(I)                                                                                             \
+    B200ML_CUDA(launch_pdl(layernorm_warp_kernel<T, I>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, x, residual, \
+                           bias, gamma, beta, y, rows, (int)cols, eps))
         if (iters <= 1) LN_LAUNCH(1);
         else if (iters <= 2) LN_LAUNCH(2);
         else if (iters <= 4) LN_LAUNCH(4);
