@@ -367,10 +367,14 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
     if (p->bias) vec = vec && aligned16(p->bias);
     args.vec_ok = vec ? 1 : 0;
 
-    // Tall enough outputs go to CTA pairs (256-row tiles): a third less operand traffic per SM.
-    if (pair_enabled() && p->m > BM && bn >= 128 && ctx->sm_count >= 2) {
+    // Outputs with more 256-row tiles than CTA pairs go to the pair kernel (a third less operand
+    // traffic per SM, and the epilogue of one tile overlaps the main loop of the next).  With at most
+    // one tile per pair nothing overlaps and the one-CTA kernel, which spreads the same work over
+    // twice as many independent tiles, is faster.
+    const int64_t pair_tiles = ceil_div(p->m, 2 * BM) * args.tiles_n * batches;
+    if (pair_enabled() && p->m > BM && bn >= 128 && pair_tiles > ctx->sm_count / 2) {
         args.tiles_m = (int32_t)ceil_div(p->m, 2 * BM);
-        args.num_tiles = (int32_t)((int64_t)args.tiles_m * args.tiles_n * batches);
+        args.num_tiles = (int32_t)pair_tiles;
         return gemm_f16_pair(ctx, p, args, bn, stream);
     }
 
