@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "epilogue.cuh"
 #include <float.h>
+#include <atomic>
 
 namespace b200ml {
 
@@ -506,3 +507,79 @@ int reduce(const b200ml_ctx* ctx, int dtype, int op, const void* x, void* y, int
 }
 
 }  // namespace b200ml
+
+// ---------------------------------------------------------------------------------------------
+// Reduction that allocates nothing (b200ml_reduce_static)
+// ---------------------------------------------------------------------------------------------
+// The sliced long-row reduction needs a place for its per-slice partial results.  b200ml_reduce takes
+// it from the context's scratch buffer, which b200ml_ctx_create obtained with cudaMalloc.  Some callers
+// must not allocate device memory at all: code that runs while a CUDA graph is being captured or
+// between the launches of a latency-critical serving loop (cudaMalloc synchronises the device and is
+// illegal during capture), plug-ins that are handed a fixed memory budget by their host framework and
+// may not grow it, and callers that run after the host allocator has been frozen.  For them the
+// partials live in the array below, which is part of the library image: every GPU that loads the
+// library holds these 4 KiB from load until the process exits.  1024 partial results cover every shape the
+// slicing policy produces on a B200 except 513 to 591 long rows at once (two slices each).
+constexpr int64_t kStaticScratchFloats = 1024;
+static __device__ __align__(256) float g_reduce_static_scratch[kStaticScratchFloats];
+
+namespace b200ml {
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::atomic<float*> g_static_scratch_ptr[kMaxDevices];
+std::atomic<int> g_static_sm_count[kMaxDevices];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address
+// on the current device comes from cudaGetSymbolAddress.  Done once per device, on the first call
+// made with that device current.
+int static_scratch_for_current_device(float** ptr, int* sm_count) {
+    int dev = 0;
+    B200ML_CUDA(cudaGetDevice(&dev));
+    B200ML_REQUIRE(dev >= 0 && dev < kMaxDevices, "reduce_static: device index %d out of range", dev);
+    float* p = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        void* sym = nullptr;
+        B200ML_CUDA(cudaGetSymbolAddress(&sym, g_reduce_static_scratch));
+        int sms = 0;
+        B200ML_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        g_static_sm_count[dev].store(sms, std::memory_order_relaxed);
+        p = static_cast<float*>(sym);
+        g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+    }
+    *ptr = p;
+    *sm_count = g_static_sm_count[dev].load(std::memory_order_relaxed);
+    return B200ML_OK;
+}
+
+}  // namespace
+}  // namespace b200ml
+
+extern "C" int b200ml_reduce_static(int32_t dtype, int32_t op, const void* x, void* y, int64_t outer, int64_t red,
+                                    int64_t inner, b200ml_stream stream) {
+    using namespace b200ml;
+    B200ML_REQUIRE(dtype == B200ML_F16 || dtype == B200ML_F32, "reduce_static: unknown dtype %d", dtype);
+    B200ML_REQUIRE(op >= B200ML_RED_SUM && op <= B200ML_RED_MIN, "reduce_static: unknown op %d", op);
+    B200ML_REQUIRE(outer >= 0 && red >= 0 && inner >= 0, "reduce_static: negative extent");
+    if (outer == 0 || inner == 0) return B200ML_OK;
+    B200ML_REQUIRE(x && y, "reduce_static: null tensor");
+    float* scratch = nullptr;
+    int sms = 0;
+    int rc = static_scratch_for_current_device(&scratch, &sms);
+    if (rc) return rc;
+    // A context that exists only on this stack frame: it points the shared reduction code at the static
+    // array instead of an allocated buffer.  Nothing is allocated and nothing needs zeroing: the first
+    // stage writes every partial the second stage reads.
+    b200ml_ctx local;
+    (void)cudaGetDevice(&local.device);
+    local.sm_count = sms;
+    local.workspace = scratch;
+    local.workspace_bytes = kStaticScratchFloats * (int64_t)sizeof(float);
+    rc = reduce(&local, dtype, op, x, y, outer, red, inner, static_cast<cudaStream_t>(stream));
+    if (rc == B200ML_ERR_WORKSPACE)
+        return fail(B200ML_ERR_WORKSPACE,
+                    "reduce_static: %lld rows of %lld elements need more than the %lld partial sums of the built-in scratch "
+                    "array; use b200ml_reduce with a context instead",
+                    (long long)outer, (long long)red, (long long)kStaticScratchFloats);
+    return rc;
+}

@@ -27,7 +27,7 @@ BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_MAX, BIN_MIN = range(7)
 EXPORTED_SYMBOLS = [
     "b200ml_ctx_create", "b200ml_ctx_destroy", "b200ml_ctx_device_status", "b200ml_ctx_workspace_bytes",
     "b200ml_last_error", "b200ml_version", "b200ml_launch_count", "b200ml_gemm", "b200ml_softmax",
-    "b200ml_layernorm", "b200ml_reduce", "b200ml_unary", "b200ml_binary", "b200ml_bias_act", "b200ml_transpose",
+    "b200ml_layernorm", "b200ml_reduce", "b200ml_reduce_static", "b200ml_unary", "b200ml_binary", "b200ml_bias_act", "b200ml_transpose",
     "b200ml_cast", "b200ml_conv2d", "b200ml_se_gate", "b200ml_attention_f16",
 ]
 
@@ -120,6 +120,7 @@ def load_library(path=None):
         lib.b200ml_softmax.argtypes = [vp, c_i32, vp, vp, vp, c_i64, c_i64, c_i64, c_f, c_i32, vp]
         lib.b200ml_layernorm.argtypes = [vp, c_i32, vp, vp, vp, vp, vp, vp, c_i64, c_i64, c_f, vp]
         lib.b200ml_reduce.argtypes = [vp, c_i32, c_i32, vp, vp, c_i64, c_i64, c_i64, vp]
+        lib.b200ml_reduce_static.argtypes = [c_i32, c_i32, vp, vp, c_i64, c_i64, c_i64, vp]
         lib.b200ml_unary.argtypes = [vp, c_i32, c_i32, vp, vp, c_i64, c_f, c_f, vp]
         lib.b200ml_binary.argtypes = [vp, c_i32, c_i32, vp, vp, vp, c_i32, i64p, i64p, i64p, vp]
         lib.b200ml_bias_act.argtypes = [vp, c_i32, vp, vp, vp, vp, c_i64, c_i64, c_i32, vp]

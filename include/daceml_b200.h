@@ -130,6 +130,24 @@ typedef enum { B200ML_RED_SUM = 0, B200ML_RED_MEAN = 1, B200ML_RED_MAX = 2, B200
 int b200ml_reduce(b200ml_ctx* ctx, int32_t dtype, int32_t op, const void* x, void* y, int64_t outer,
                   int64_t reduce, int64_t inner, b200ml_stream stream);
 
+/* The same reduction for callers that may not allocate device memory: no context is needed, and the
+ * scratch for the per-slice partial results of long rows is a 4 KiB array built into the library
+ * (resident on every GPU that loads it, until the process exits) instead of a cudaMalloc'ed buffer.
+ * Meant for code running under CUDA-graph capture or inside a serving loop (where cudaMalloc would
+ * synchronise the device or is illegal), and for plug-ins whose host framework fixes their memory
+ * budget.  It has no counterpart in the reference.
+ *   - Works on the current device and the given stream; calls no allocating routine.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call before any stream capture begins.
+ *   - Limit: outer * slices <= 1024 partial results.  Rows are sliced only when reduce > 4096 and
+ *     outer < 4 * SM count, into ceil(4 * SMs / outer) slices (at most reduce / 2048); on a B200 only
+ *     513..591 long rows at once exceed the limit.  Such a request fails with B200ML_ERR_WORKSPACE
+ *     and a message; b200ml_reduce with a context serves it.
+ *   - All calls share the one array and it keeps the last call's partials; nothing has to be
+ *     zeroed, but two calls that overlap on the GPU (different streams) race on it. */
+int b200ml_reduce_static(int32_t dtype, int32_t op, const void* x, void* y, int64_t outer,
+                         int64_t reduce, int64_t inner, b200ml_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* Element-wise kernels                                                       */
 /* ------------------------------------------------------------------------- */
