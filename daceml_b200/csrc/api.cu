@@ -36,6 +36,7 @@ int fail(int code, const char* fmt, ...) {
 
 int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
 int gemm_f32(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
+int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
 int softmax(int dtype, const void* x, const void* mask, void* y, int64_t rows, int64_t cols, int64_t mask_row_div,
             float scale, int is_log, cudaStream_t s);
 int layernorm(int dtype, const void* x, const void* residual, const void* bias, const void* gamma, const void* beta,
@@ -173,6 +174,10 @@ int b200ml_gemm(b200ml_ctx* ctx, const b200ml_gemm_params* p, b200ml_stream stre
     B200ML_REQUIRE(p->ldc >= p->n, "gemm: ldc too small");
     DeviceGuard guard(ctx->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (p->epilogue & B200ML_EPI_LAYERNORM) {
+        if (p->dtype != B200ML_F16) return fail(B200ML_ERR_UNSUPPORTED, "gemm + layernorm: fp16 only");
+        return gemm_f16_layernorm(ctx, p, s);
+    }
     return p->dtype == B200ML_F16 ? gemm_f16(ctx, p, s) : gemm_f32(ctx, p, s);
 }
 

@@ -1,0 +1,355 @@
+// fp16 GEMM whose epilogue also applies LayerNorm over the output row:
+//     Y = LayerNorm(act(alpha * A.B + bias) + residual) * gamma + beta
+// for outputs of up to 1024 columns.  One cluster of N / 256 CTAs covers a 128-row block of the whole
+// output width; each CTA computes a 128 x 256 tile exactly like the one-CTA GEMM (TMA ring -> tcgen05.mma
+// -> TMEM), then the CTAs of the cluster exchange per-row partial sums through distributed shared
+// memory: mean first, then the mean of squared deviations (two passes, as the ReduceMean / Sub / Pow /
+// ReduceMean chain of the exported graph computes it), and normalise their own columns.  The finished
+// pre-normalisation row is parked in TMEM (fp32) between the passes, so nothing is re-read from memory.
+// This removes the separate LayerNorm kernel (one read and one write of the activation) behind the
+// attention output projection and the second FFN matrix product.
+#include "gemm_common.cuh"
+
+namespace b200ml {
+
+using namespace gemm;
+
+namespace {
+
+constexpr int LN_BN = 256;
+constexpr int LN_STAGES = 4;
+constexpr int LN_STAGE_BYTES = A_TILE_BYTES + LN_BN * BK * 2;
+constexpr int LN_SMEM = LN_STAGES * LN_STAGE_BYTES + 256 /* barriers */ + 3 * BM * 4 /* row statistics */ + 1024;
+
+struct LnArgs {
+    GemmArgs g;
+    const __half* gamma;
+    const __half* beta;
+    float eps;
+    int32_t cluster;  // CTAs per cluster = N / 256
+};
+
+template <int CLUSTER, bool B_MN>
+__global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const LnArgs la) {
+    const GemmArgs& args = la.g;
+    constexpr uint32_t TMEM_COLS = LN_BN;
+    constexpr uint32_t IDESC = ptx::make_idesc_f16(BM, LN_BN, 0, B_MN ? 1 : 0);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + LN_STAGES * LN_STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + LN_STAGES;
+    uint64_t* tmem_full_bar = empty_bar + LN_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+    float* red = reinterpret_cast<float*>(smem + LN_STAGES * LN_STAGE_BYTES + 256);  // [2][128] half-row partials
+    float* stats = red + 2 * BM;                                                       // [128] this CTA's row partial
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const int mt = blockIdx.x / CLUSTER;  // one 128-row block per cluster
+    const int m0 = mt * BM;
+    const int n0 = static_cast<int>(rank) * LN_BN;
+    const int num_kb = (args.k + BK - 1) / BK;
+
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        if (lane == 0) {
+            for (int s = 0; s < LN_STAGES; ++s) {
+                ptx::mbar_init(&full_bar[s], 1);
+                ptx::mbar_init(&empty_bar[s], 1);
+            }
+            ptx::mbar_init(tmem_full_bar, 1);
+            ptx::fence_mbar_init();
+        }
+        __syncwarp();
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    bool epi_ok = true;
+    if (warp == 0) {
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+                    atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
+                    break;
+                }
+                uint8_t* sa = smem + stage * LN_STAGE_BYTES;
+                uint8_t* sb = sa + A_TILE_BYTES;
+                ptx::mbar_expect_tx(&full_bar[stage], LN_STAGE_BYTES);
+                ptx::tma_load_4d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, 0, 0);
+                if (B_MN) {
+#pragma unroll
+                    for (int j = 0; j < LN_BN / 64; ++j)
+                        ptx::tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + j * 64, kb * BK, 0, 0);
+                } else {
+                    ptx::tma_load_4d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, 0, 0);
+                }
+                if (++stage == LN_STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+                    atomicExch(args.status, DEV_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t a_addr = ptx::smem_u32(smem + stage * LN_STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    const uint64_t a_desc = ptx::make_smem_desc_sw128(a_addr + kk * (UMMA_K * 2), 16, 1024);
+                    const uint64_t b_desc = B_MN ? ptx::make_smem_desc_sw128(b_addr + kk * (UMMA_K * 128), 64 * BK * 2, 1024)
+                                                 : ptx::make_smem_desc_sw128(b_addr + kk * (UMMA_K * 2), 16, 1024);
+                    ptx::mma_f16_ss(tmem_base, a_desc, b_desc, IDESC, (kb | kk) != 0 ? 1u : 0u);
+                }
+                ptx::mma_commit(&empty_bar[stage]);
+                if (++stage == LN_STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (ok) ptx::mma_commit(tmem_full_bar);
+        }
+    }
+
+    // ------------------------------ epilogue: three passes over the row parked in TMEM ------------------------------
+    const bool is_epi = warp >= 2;
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;           // columns [half * 128, half * 128 + 128) of this CTA's tile
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = m0 + row_in_tile;
+    const bool row_ok = row < args.m;
+    const uint32_t t_base = tmem_base + half * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int col_base = n0 + half * 128;
+    const float inv_n = 1.0f / static_cast<float>(args.n);
+    float mean = 0.0f, rstd = 0.0f;
+
+    // pass A: finish the GEMM epilogue in fp32, park the values in TMEM, row sum
+    if (is_epi) {
+        if (!ptx::mbar_wait(tmem_full_bar, 0)) {
+            if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+            epi_ok = false;
+        }
+        ptx::tc_fence_after();
+        float s = 0.0f;
+        if (epi_ok) {
+            const __half* r_row = args.residual ? args.residual + static_cast<int64_t>(row) * args.ldr : nullptr;
+            const bool has_bias = (args.epilogue & B200ML_EPI_BIAS) && args.bias;
+            const bool has_res = (args.epilogue & B200ML_EPI_RESIDUAL) && r_row && row_ok;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const int col0 = col_base + c * 32;
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);
+                uint4 rb[4], rr[4];
+                if (has_bias) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) rb[g] = __ldg(reinterpret_cast<const uint4*>(args.bias + col0 + g * 8));
+                }
+                if (has_res) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) rr[g] = __ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8));
+                }
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    float b[8], q[8];
+                    if (has_bias) unpack8(rb[g], b);
+                    if (has_res) unpack8(rr[g], q);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float v = args.alpha * __uint_as_float(r[g * 8 + j]);
+                        if (has_bias) v = fmaf(args.bias_scale, b[j], v);
+                        v = apply_act(v, args.epilogue);
+                        if (has_res) v = fmaf(args.residual_scale, q[j], v);
+                        s += v;
+                        r[g * 8 + j] = __float_as_uint(v);
+                    }
+                }
+                ptx::tmem_st_32x32b_x32(t_base + c * 32, r);
+            }
+            ptx::tmem_st_wait();
+        }
+        red[half * BM + row_in_tile] = s;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (half == 0) stats[row_in_tile] = red[row_in_tile] + red[BM + row_in_tile];
+    }
+    __syncwarp();
+    ptx::cluster_sync_acq_rel();  // #1: every CTA's row sums are visible
+    if (is_epi) {
+        float tot = 0.0f;
+#pragma unroll
+        for (int r = 0; r < CLUSTER; ++r) tot += ptx::ld_shared_cluster_f32(&stats[row_in_tile], r);
+        mean = tot * inv_n;
+    }
+    __syncwarp();
+    ptx::cluster_sync_acq_rel();  // #2: all reads of the sums are done before stats is reused
+    // pass B: sum of squared deviations
+    if (is_epi) {
+        float q = 0.0f;
+        if (epi_ok) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float d = __uint_as_float(r[j]) - mean;
+                    q = fmaf(d, d, q);
+                }
+            }
+        }
+        red[half * BM + row_in_tile] = q;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (half == 0) stats[row_in_tile] = red[row_in_tile] + red[BM + row_in_tile];
+    }
+    __syncwarp();
+    ptx::cluster_sync_acq_rel();  // #3
+    if (is_epi) {
+        float tot = 0.0f;
+#pragma unroll
+        for (int r = 0; r < CLUSTER; ++r) tot += ptx::ld_shared_cluster_f32(&stats[row_in_tile], r);
+        rstd = 1.0f / sqrtf(tot * inv_n + la.eps);
+        // pass C: normalise, scale, shift, store.  Every lane takes part in the (warp-collective) TMEM loads;
+        // only the global stores are guarded by the row bound.
+        if (epi_ok) {
+            __half* c_row = args.c + static_cast<int64_t>(row) * args.ldc;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const int col0 = col_base + c * 32;
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);
+                uint4 rg[4], rb[4];
+                if (la.gamma) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) rg[g] = __ldg(reinterpret_cast<const uint4*>(la.gamma + col0 + g * 8));
+                }
+                if (la.beta) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) rb[g] = __ldg(reinterpret_cast<const uint4*>(la.beta + col0 + g * 8));
+                }
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    float gm[8], bt[8], o[8];
+                    if (la.gamma) unpack8(rg[g], gm);
+                    if (la.beta) unpack8(rb[g], bt);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float v = (__uint_as_float(r[g * 8 + j]) - mean) * rstd;
+                        if (la.gamma) v *= gm[j];
+                        if (la.beta) v += bt[j];
+                        o[j] = v;
+                    }
+                    if (row_ok) *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(o);
+                }
+            }
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_acq_rel();  // #4: no CTA leaves while a peer may still read its statistics
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        if (*reinterpret_cast<volatile int32_t*>(args.status) != DEV_OK) {
+            for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        }
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int CLUSTER, bool B_MN>
+int launch_ln(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const LnArgs& la, int tiles_m,
+              cudaStream_t stream) {
+    auto kernel = gemm_f16_ln_kernel<CLUSTER, B_MN>;
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        B200ML_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LN_SMEM));
+        configured[ctx->device & 63] = true;
+    }
+    B200ML_CUDA(launch_pdl(kernel, dim3(tiles_m * CLUSTER), dim3(GEMM_THREADS), LN_SMEM, stream, ta, tb, la));
+    return check_launch("gemm_f16_ln");
+}
+
+}  // namespace
+
+// Returns B200ML_ERR_UNSUPPORTED (without a launch) for shapes the fused kernel does not cover.
+int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream) {
+    const int64_t batches = p->batch_outer * p->batch_inner;
+    const bool shape_ok = batches == 1 && p->a_layout == 0 && p->n % LN_BN == 0 && p->n >= LN_BN && p->n <= 1024 &&
+                          (p->n / LN_BN == 1 || p->n / LN_BN == 2 || p->n / LN_BN == 4) && p->m < (1ll << 24);
+    bool vec = aligned16(p->a) && p->lda % 8 == 0 && aligned16(p->b) && p->ldb % 8 == 0 && aligned16(p->c) && p->ldc % 8 == 0;
+    if (p->residual) vec = vec && aligned16(p->residual) && p->ldr % 8 == 0;
+    if (p->bias) vec = vec && aligned16(p->bias);
+    if (p->ln_gamma) vec = vec && aligned16(p->ln_gamma);
+    if (p->ln_beta) vec = vec && aligned16(p->ln_beta);
+    if (!shape_ok || !vec)
+        return fail(B200ML_ERR_UNSUPPORTED, "gemm + layernorm: needs fp16, N in {256, 512, 1024}, one batch and 16-byte aligned rows");
+    LnArgs la{};
+    GemmArgs& args = la.g;
+    args.m = (int32_t)p->m;
+    args.n = (int32_t)p->n;
+    args.k = (int32_t)p->k;
+    args.epilogue = p->epilogue;
+    args.ldc = p->ldc;
+    args.ldr = p->ldr;
+    args.alpha = p->alpha;
+    args.bias_scale = p->bias_scale;
+    args.residual_scale = p->residual_scale;
+    args.vec_ok = 1;
+    args.c = static_cast<__half*>(p->c);
+    args.bias = static_cast<const __half*>(p->bias);
+    args.residual = static_cast<const __half*>(p->residual);
+    args.status = ctx->status_dev;
+    la.gamma = static_cast<const __half*>(p->ln_gamma);
+    la.beta = static_cast<const __half*>(p->ln_beta);
+    la.eps = p->ln_eps;
+    la.cluster = (int32_t)(p->n / LN_BN);
+    const int tiles_m = (int)ceil_div(p->m, BM);
+    CUtensorMap ta, tb;
+    int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, 1, 0, 1, 0, BK, BM, "A");
+    if (rc) return rc;
+    if (p->b_layout == 1) {
+        rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, 1, 0, 1, 0, BK, LN_BN, "B");
+        if (rc) return rc;
+        switch (la.cluster) {
+            case 1: return launch_ln<1, false>(ctx, ta, tb, la, tiles_m, stream);
+            case 2: return launch_ln<2, false>(ctx, ta, tb, la, tiles_m, stream);
+            default: return launch_ln<4, false>(ctx, ta, tb, la, tiles_m, stream);
+        }
+    }
+    rc = make_tmap(ctx, &tb, p->b, p->n, p->k, p->ldb, 1, 0, 1, 0, 64, BK, "B");
+    if (rc) return rc;
+    switch (la.cluster) {
+        case 1: return launch_ln<1, true>(ctx, ta, tb, la, tiles_m, stream);
+        case 2: return launch_ln<2, true>(ctx, ta, tb, la, tiles_m, stream);
+        default: return launch_ln<4, true>(ctx, ta, tb, la, tiles_m, stream);
+    }
+}
+
+}  // namespace b200ml

@@ -120,7 +120,7 @@ def _gelu_chain(g, x, shape):
 
 
 def bert_layer_sdfg(p, batch, seq, heads, fused=True, eps=1e-12, dtype=torch.float16, name="bert_layer",
-                    out_name="__return"):
+                    out_name="__return", fuse_layernorm=True):
     """``p`` holds ``wq, bq, wk, bk, wv, bv, wo, bo, ln1_g, ln1_b, w1, b1, w2, b2, ln2_g, ln2_b`` with
     nn.Linear ``[out, in]`` weight layout (and optionally ``mask`` of shape [batch, seq])."""
     hidden = p["wq"].shape[0]
@@ -136,13 +136,21 @@ def bert_layer_sdfg(p, batch, seq, heads, fused=True, eps=1e-12, dtype=torch.flo
         bqkv = g.constant("bqkv", torch.cat([p["bq"], p["bk"], p["bv"]], 0).to(dtype))
         qkv = g.node("FusedMatMul", dict(A=x, B=wqkv, Bias=bqkv), (batch, seq, 3 * hidden), transB=1)
         ctx = g.node("Attention", dict(Q=qkv, Mask=mask), bsh, num_heads=heads, scale=1.0 / math.sqrt(d))
-        attn = g.node("FusedMatMul", dict(A=ctx, B=c["wo"], Bias=c["bo"], Residual=x), bsh, transB=1)
-        h1 = g.node("LayerNormalization", dict(X=attn, Scale=c["ln1_g"], B=c["ln1_b"]), bsh, axis=-1, epsilon=eps)
+        y = g.output(out_name, bsh)
+        if fuse_layernorm:  # the residual Add and the LayerNorm chain ride in the epilogue of the matrix product
+            h1 = g.node("FusedMatMul", dict(A=ctx, B=c["wo"], Bias=c["bo"], Residual=x, LnScale=c["ln1_g"], LnBias=c["ln1_b"]),
+                        bsh, transB=1, ln_epsilon=eps)
+        else:
+            attn = g.node("FusedMatMul", dict(A=ctx, B=c["wo"], Bias=c["bo"], Residual=x), bsh, transB=1)
+            h1 = g.node("LayerNormalization", dict(X=attn, Scale=c["ln1_g"], B=c["ln1_b"]), bsh, axis=-1, epsilon=eps)
         inter = g.node("FusedMatMul", dict(A=h1, B=c["w1"], Bias=c["b1"]), (batch, seq, ffn), transB=1,
                        activation="Gelu")
-        out = g.node("FusedMatMul", dict(A=inter, B=c["w2"], Bias=c["b2"], Residual=h1), bsh, transB=1)
-        y = g.output(out_name, bsh)
-        g.node("LayerNormalization", dict(X=out, Scale=c["ln2_g"], B=c["ln2_b"]), bsh, out=y, axis=-1, epsilon=eps)
+        if fuse_layernorm:
+            g.node("FusedMatMul", dict(A=inter, B=c["w2"], Bias=c["b2"], Residual=h1, LnScale=c["ln2_g"], LnBias=c["ln2_b"]),
+                   bsh, out=y, transB=1, ln_epsilon=eps)
+        else:
+            out = g.node("FusedMatMul", dict(A=inter, B=c["w2"], Bias=c["b2"], Residual=h1), bsh, transB=1)
+            g.node("LayerNormalization", dict(X=out, Scale=c["ln2_g"], B=c["ln2_b"]), bsh, out=y, axis=-1, epsilon=eps)
         return g.sdfg
 
     def linear(inp, w, b, n_out):

@@ -18,7 +18,7 @@ LIB_PATH = os.environ.get("DACEML_B200_LIB") or os.path.join(_HERE, "lib", "libd
 # status codes / enums (mirrors of the header)
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
 F16, F32 = 0, 1
-EPI_BIAS, EPI_RELU, EPI_GELU, EPI_RESIDUAL, EPI_SWISH = 1, 2, 4, 8, 16
+EPI_BIAS, EPI_RELU, EPI_GELU, EPI_RESIDUAL, EPI_SWISH, EPI_LAYERNORM = 1, 2, 4, 8, 16, 32
 RED_SUM, RED_MEAN, RED_MAX, RED_MIN = 0, 1, 2, 3
 (UN_COPY, UN_RELU, UN_SIGMOID, UN_ERF, UN_SQRT, UN_EXP, UN_LOG, UN_TANH, UN_SWISH, UN_GELU, UN_RECIPROCAL,
  UN_LEAKYRELU, UN_AFFINE, UN_POWS, UN_SOFTPLUS, UN_CLIP, UN_NEG, UN_ABS) = range(18)
@@ -58,6 +58,7 @@ class GemmParams(ctypes.Structure):
         ("reserved", ctypes.c_int32),
         ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p),
         ("c", ctypes.c_void_p),
+        ("ln_gamma", ctypes.c_void_p), ("ln_beta", ctypes.c_void_p), ("ln_eps", ctypes.c_float), ("reserved2", ctypes.c_int32),
     ]
 
 

@@ -61,7 +61,7 @@ def _matmul_plan(a_shape, b_shape):
 
 
 def _launch_gemm(a, b, out, plan, *, b_layout=0, a_layout=0, alpha=1.0, bias=None, bias_scale=1.0, residual=None,
-                 residual_scale=1.0, act=0):
+                 residual_scale=1.0, act=0, ln=None):
     ctx = L.get_context(a.device)
     p = L.GemmParams()
     p.dtype = L.dtype_code(a.dtype)
@@ -81,6 +81,11 @@ def _launch_gemm(a, b, out, plan, *, b_layout=0, a_layout=0, alpha=1.0, bias=Non
     p.bias = bias.data_ptr() if bias is not None else None
     if residual is not None:
         p.residual, p.ldr, p.r_stride_outer = residual.data_ptr(), n, m * n
+    if ln is not None:  # (gamma, beta, eps): LayerNorm over the finished row inside the GEMM epilogue
+        p.epilogue |= L.EPI_LAYERNORM
+        p.ln_gamma = ln[0].data_ptr() if ln[0] is not None else None
+        p.ln_beta = ln[1].data_ptr() if ln[1] is not None else None
+        p.ln_eps = ln[2]
     K.gemm_raw(ctx, p, L.current_stream(a.device))
 
 
@@ -644,12 +649,37 @@ class B200FusedMatMul(ONNXForward):
         n = b.shape[0] if tb else b.shape[1]
         plan = dict(batch=1, m=prod(a.shape[:-1]), k=k, n=n, a_batched=False, b_batched=False)
         act, alpha = _ACT[node.activation], float(node.alpha)
+        if node.ln_epsilon is None:
 
-        def run(ins, outs):
-            _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
+            def run(ins, outs):
+                _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
+                             residual=ins.get("Residual"), act=act)
+
+            return KernelTasklet(node.label, run, kernels=("gemm",))
+
+        # LayerNorm of the result: inside the GEMM epilogue where the fused kernel covers the shape (fp16, N a
+        # multiple of 256 up to 1024), else as a second launch on a pre-normalisation buffer.
+        eps = float(node.ln_epsilon)
+        fusable = a.dtype == torch.float16 and n in (256, 512, 1024) and k % 8 == 0
+        if fusable:
+
+            def run_fused(ins, outs):
+                _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
+                             residual=ins.get("Residual"), act=act, ln=(ins.get("LnScale"), ins.get("LnBias"), eps))
+
+            return KernelTasklet(node.label, run_fused, kernels=("gemm_layernorm",))
+        scratch = {}
+
+        def run_split(ins, outs):
+            y = outs["Y"]
+            tmp = scratch.get("t")
+            if tmp is None or tmp.device != y.device:
+                tmp = scratch["t"] = torch.empty_like(y)
+            _launch_gemm(ins["A"], ins["B"], tmp, plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
                          residual=ins.get("Residual"), act=act)
+            K.layernorm(tmp, y, gamma=ins.get("LnScale"), beta=ins.get("LnBias"), eps=eps)
 
-        return KernelTasklet(node.label, run, kernels=("gemm",))
+        return KernelTasklet(node.label, run_split, kernels=("gemm", "layernorm"))
 
 
 @op_implementation(op="Attention", name="b200")

@@ -78,8 +78,9 @@ _S = [
                dict(axis=-1, epsilon=1e-5), fused=True),
     ONNXSchema("Gelu", ["X"], ["Y"], fused=True),
     ONNXSchema("Swish", ["X"], ["Y"], fused=True),
-    ONNXSchema("FusedMatMul", ["A", "B", ("Bias", OPTIONAL), ("Residual", OPTIONAL)], ["Y"],
-               dict(alpha=1.0, transB=0, activation=""), fused=True),
+    ONNXSchema("FusedMatMul", ["A", "B", ("Bias", OPTIONAL), ("Residual", OPTIONAL), ("LnScale", OPTIONAL),
+                               ("LnBias", OPTIONAL)], ["Y"],
+               dict(alpha=1.0, transB=0, activation="", ln_epsilon=None), fused=True),
     ONNXSchema("Attention", ["Q", ("K", OPTIONAL), ("V", OPTIONAL), ("Mask", OPTIONAL)], ["Y"], dict(num_heads=1, scale=None), fused=True),
     ONNXSchema("FusedConv", ["X", "W", ("B", OPTIONAL), ("Gate", OPTIONAL), ("Residual", OPTIONAL)],
                ["Y", ("Pool", OPTIONAL)],

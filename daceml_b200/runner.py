@@ -56,7 +56,7 @@ class BertEncoder:
                 c = s.compile()
                 c.device = self.device
                 self.layers.append(c)
-            self.launches_per_forward = sum(len(c.plan) for c in self.layers)
+            self.launches_per_forward = sum(len(c.kernel_names()) for c in self.layers)
             self._graphed: Optional[GraphedCall] = None
             self._cuda_graph = cuda_graph
             if cuda_graph:

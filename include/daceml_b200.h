@@ -75,7 +75,11 @@ enum {
     B200ML_EPI_RELU = 2,
     B200ML_EPI_GELU = 4, /* 0.5 x (1 + erf(x / sqrt 2)), the Div/Erf/Add/Mul/Mul chain */
     B200ML_EPI_RESIDUAL = 8,
-    B200ML_EPI_SWISH = 16 /* x * sigmoid(x), the Sigmoid/Mul pair */
+    B200ML_EPI_SWISH = 16, /* x * sigmoid(x), the Sigmoid/Mul pair */
+    /* LayerNorm over the N axis of the finished row (after bias / activation / residual), with ln_gamma, ln_beta and
+     * ln_eps: the ReduceMean/Sub/Pow/ReduceMean/Add/Sqrt/Div/Mul/Add chain folded into the GEMM.  F16 only, N a
+     * multiple of 256 up to 1024; other shapes return B200ML_ERR_UNSUPPORTED (run b200ml_layernorm after the GEMM). */
+    B200ML_EPI_LAYERNORM = 32
 };
 
 typedef struct {
@@ -98,6 +102,10 @@ typedef struct {
     const void* bias;     /* [N] or null */
     const void* residual; /* [M,N] with ldr, or null */
     void* c;
+    const void* ln_gamma; /* [N] or null (B200ML_EPI_LAYERNORM) */
+    const void* ln_beta;  /* [N] or null */
+    float ln_eps;
+    int32_t reserved2;
 } b200ml_gemm_params;
 
 /* Replaces PureMatMul / PureEinsum / PureGemm and the BLAS library node they lower to

@@ -164,7 +164,17 @@ def test_exported_graphs_expand_completely():
     fused = graphs.bert_layer_sdfg(p, 2, 128, 2, fused=True)
     fused.expand_library_nodes()
     order = fused.states()[0].topological_compute_nodes()
-    assert [t.kernels[0] for t in order] == ["gemm", "attention", "gemm", "layernorm", "gemm", "gemm", "layernorm"]
+    assert [k for t in order for k in t.kernels] == ["gemm", "attention", "gemm", "layernorm", "gemm", "gemm", "layernorm"]
+    wide = {k: (v if v.dim() == 1 else v) for k, v in p.items()}
+    H2 = 256
+    p2 = dict(wq=rn(H2, H2), bq=rn(H2), wk=rn(H2, H2), bk=rn(H2), wv=rn(H2, H2), bv=rn(H2), wo=rn(H2, H2), bo=rn(H2),
+              ln1_g=torch.ones(H2), ln1_b=torch.zeros(H2), w1=rn(512, H2), b1=rn(512), w2=rn(H2, 512), b2=rn(H2),
+              ln2_g=torch.ones(H2), ln2_b=torch.zeros(H2))
+    f2 = graphs.bert_layer_sdfg(p2, 2, 128, 4, fused=True)
+    f2.expand_library_nodes()
+    # a hidden size the fused kernel covers: LayerNorm rides in the GEMM epilogue, five launches per layer
+    assert [k for t in f2.states()[0].topological_compute_nodes() for k in t.kernels] == [
+        "gemm", "attention", "gemm_layernorm", "gemm", "gemm_layernorm"]
     unfused = graphs.bert_layer_sdfg(p, 2, 128, 2, fused=False)
     n_nodes = len([n for n, _ in unfused.all_nodes_recursive() if isinstance(n, donnx.ONNXOp)])
     assert n_nodes == 56  # the exported graph: LayerNorm and GELU decomposed, weights as Transpose -> MatMul -> Add

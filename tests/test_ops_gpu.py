@@ -274,6 +274,38 @@ def test_layernorm_fused_matches_chain(dtype):
     assert_close(y, ref, dtype, what="layernorm + residual")
 
 
+@pytest.mark.parametrize("m, n, k", [(4096, 1024, 1024), (300, 512, 264), (128, 256, 64), (1000, 1024, 4096)])
+@pytest.mark.parametrize("trans_b", [1, 0])
+def test_matmul_with_layernorm_epilogue(m, n, k, trans_b, rng):
+    """FusedMatMul with LnScale / LnBias: bias + residual + LayerNorm inside the GEMM (cluster-wide row statistics)."""
+    dtype = torch.float16
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k) if trans_b else (k, n)) * 0.05).astype(np.float32)
+    bias, res = rng.standard_normal(n).astype(np.float32), rng.standard_normal((m, n)).astype(np.float32)
+    gamma, beta = (1 + 0.2 * rng.standard_normal(n)).astype(np.float32), (0.2 * rng.standard_normal(n)).astype(np.float32)
+    y = empty((m, n), dtype)
+    donnx.ONNXFusedMatMul(A=dev(a, dtype), B=dev(w, dtype), Bias=dev(bias, dtype), Residual=dev(res, dtype), LnScale=dev(gamma, dtype),
+                          LnBias=dev(beta, dtype), Y=y, transB=trans_b, ln_epsilon=1e-12)
+    wr = rounded(w, dtype)
+    pre = ops.matmul(rounded(a, dtype), wr.T.copy() if trans_b else wr) + rounded(bias, dtype) + rounded(res, dtype)
+    ref = ops.layernorm_chain(pre.astype(np.float32), rounded(gamma, dtype), rounded(beta, dtype), 1e-12)
+    assert_close(y, ref, dtype, atol=5e-3, what=f"gemm+layernorm {m}x{n}x{k}")
+    status_ok()
+
+
+def test_matmul_with_layernorm_split_path(rng):
+    """A width the fused kernel does not cover (N = 384) runs as GEMM + LayerNorm and gives the same answer."""
+    dtype = torch.float16
+    m, n, k = 200, 384, 128
+    a, w = rng.standard_normal((m, k)).astype(np.float32), (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    gamma = (1 + 0.2 * rng.standard_normal(n)).astype(np.float32)
+    y = empty((m, n), dtype)
+    donnx.ONNXFusedMatMul(A=dev(a, dtype), B=dev(w, dtype), LnScale=dev(gamma, dtype), Y=y, transB=1, ln_epsilon=1e-5)
+    pre = ops.matmul(rounded(a, dtype), rounded(w, dtype).T.copy())
+    ref = ops.layernorm_chain(pre.astype(np.float16).astype(np.float32), rounded(gamma, dtype), np.zeros(n, np.float32), 1e-5)
+    assert_close(y, ref, dtype, atol=5e-3, what="gemm then layernorm")
+
+
 # ------------------------------------------------------------------------------------------------
 # Conv
 # ------------------------------------------------------------------------------------------------
