@@ -3,9 +3,8 @@
 // for outputs of up to 1024 columns.  One cluster of N / 256 CTAs covers a 128-row block of the whole
 // output width; each CTA computes a 128 x 256 tile exactly like the one-CTA GEMM (TMA ring -> tcgen05.mma
 // -> TMEM), then the CTAs of the cluster exchange per-row partial sums through distributed shared
-// memory: mean first, then the mean of squared deviations (two passes, as the ReduceMean / Sub / Pow /
-// ReduceMean chain of the exported graph computes it), and normalise their own columns.  The finished
-// pre-normalisation row is parked in TMEM (fp32) between the passes, so nothing is re-read from memory.
+// memory (sum and sum of squares in fp32), and normalise their own columns.  The finished
+// pre-normalisation row is parked in TMEM (fp32) between the two passes, so nothing is re-read from memory.
 // This removes the separate LayerNorm kernel (one read and one write of the activation) behind the
 // attention output projection and the second FFN matrix product.
 #include "gemm_common.cuh"
@@ -19,7 +18,7 @@ namespace {
 constexpr int LN_BN = 256;
 constexpr int LN_STAGES = 4;
 constexpr int LN_STAGE_BYTES = A_TILE_BYTES + LN_BN * BK * 2;
-constexpr int LN_SMEM = LN_STAGES * LN_STAGE_BYTES + 256 /* barriers */ + 3 * BM * 4 /* row statistics */ + 1024;
+constexpr int LN_SMEM = LN_STAGES * LN_STAGE_BYTES + 256 /* barriers */ + 6 * BM * 4 /* row statistics */ + 1024;
 
 struct LnArgs {
     GemmArgs g;
@@ -43,8 +42,8 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     uint64_t* empty_bar = full_bar + LN_STAGES;
     uint64_t* tmem_full_bar = empty_bar + LN_STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
-    float* red = reinterpret_cast<float*>(smem + LN_STAGES * LN_STAGE_BYTES + 256);  // [2][128] half-row partials
-    float* stats = red + 2 * BM;                                                       // [128] this CTA's row partial
+    float* red = reinterpret_cast<float*>(smem + LN_STAGES * LN_STAGE_BYTES + 256);  // [4][128]: sum and sum of squares per column half
+    float* stats = red + 4 * BM;                                                       // [2][128]: this CTA's row sum and sum of squares
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
@@ -148,132 +147,129 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const float inv_n = 1.0f / static_cast<float>(args.n);
     float mean = 0.0f, rstd = 0.0f;
 
-    // pass A: finish the GEMM epilogue in fp32, park the values in TMEM, row sum
+    // pass A: finish the GEMM epilogue in fp32, park the values in TMEM, accumulate the row's sum and sum of squares
     if (is_epi) {
         if (!ptx::mbar_wait(tmem_full_bar, 0)) {
             if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
             epi_ok = false;
         }
         ptx::tc_fence_after();
-        float s = 0.0f;
+        float s1 = 0.0f, s2 = 0.0f;
         if (epi_ok) {
             const __half* r_row = args.residual ? args.residual + static_cast<int64_t>(row) * args.ldr : nullptr;
             const bool has_bias = (args.epilogue & B200ML_EPI_BIAS) && args.bias;
             const bool has_res = (args.epilogue & B200ML_EPI_RESIDUAL) && r_row && row_ok;
+            const bool relu = (args.epilogue & B200ML_EPI_RELU) != 0;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                const int col0 = col_base + c * 32;
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);
-                uint4 rb[4], rr[4];
-                if (has_bias) {
+            for (int c = 0; c < 4; c += 2) {
+                uint32_t r[2][32];
+                uint4 rb[2][4], rr[2][4];
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) rb[g] = __ldg(reinterpret_cast<const uint4*>(args.bias + col0 + g * 8));
-                }
-                if (has_res) {
+                for (int u = 0; u < 2; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) rr[g] = __ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8));
+                for (int u = 0; u < 2; ++u) {
+                    const int col0 = col_base + (c + u) * 32;
+                    if (has_bias) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) rb[u][g] = __ldg(reinterpret_cast<const uint4*>(args.bias + col0 + g * 8));
+                    }
+                    if (has_res) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) rr[u][g] = __ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8));
+                    }
                 }
                 ptx::tmem_ld_wait();
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float b[8], q[8];
-                    if (has_bias) unpack8(rb[g], b);
-                    if (has_res) unpack8(rr[g], q);
+                for (int u = 0; u < 2; ++u) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float v = args.alpha * __uint_as_float(r[g * 8 + j]);
-                        if (has_bias) v = fmaf(args.bias_scale, b[j], v);
-                        v = apply_act(v, args.epilogue);
-                        if (has_res) v = fmaf(args.residual_scale, q[j], v);
-                        s += v;
-                        r[g * 8 + j] = __float_as_uint(v);
+                    for (int g = 0; g < 4; ++g) {
+                        float b[8], q[8];
+                        if (has_bias) unpack8(rb[u][g], b);
+                        if (has_res) unpack8(rr[u][g], q);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float v = args.alpha * __uint_as_float(r[u][g * 8 + j]);
+                            if (has_bias) v = fmaf(args.bias_scale, b[j], v);
+                            if (relu) v = fmaxf(v, 0.0f);
+                            if (has_res) v = fmaf(args.residual_scale, q[j], v);
+                            s1 += v;
+                            s2 = fmaf(v, v, s2);
+                            r[u][g * 8 + j] = __float_as_uint(v);
+                        }
                     }
+                    ptx::tmem_st_32x32b_x32(t_base + (c + u) * 32, r[u]);
                 }
-                ptx::tmem_st_32x32b_x32(t_base + c * 32, r);
             }
             ptx::tmem_st_wait();
         }
-        red[half * BM + row_in_tile] = s;
+        red[half * BM + row_in_tile] = s1;
+        red[(2 + half) * BM + row_in_tile] = s2;
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (half == 0) stats[row_in_tile] = red[row_in_tile] + red[BM + row_in_tile];
-    }
-    __syncwarp();
-    ptx::cluster_sync_acq_rel();  // #1: every CTA's row sums are visible
-    if (is_epi) {
-        float tot = 0.0f;
-#pragma unroll
-        for (int r = 0; r < CLUSTER; ++r) tot += ptx::ld_shared_cluster_f32(&stats[row_in_tile], r);
-        mean = tot * inv_n;
-    }
-    __syncwarp();
-    ptx::cluster_sync_acq_rel();  // #2: all reads of the sums are done before stats is reused
-    // pass B: sum of squared deviations
-    if (is_epi) {
-        float q = 0.0f;
-        if (epi_ok) {
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float d = __uint_as_float(r[j]) - mean;
-                    q = fmaf(d, d, q);
-                }
-            }
+        if (half == 0) {
+            stats[row_in_tile] = red[row_in_tile] + red[BM + row_in_tile];
+            stats[BM + row_in_tile] = red[2 * BM + row_in_tile] + red[3 * BM + row_in_tile];
         }
-        red[half * BM + row_in_tile] = q;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (half == 0) stats[row_in_tile] = red[row_in_tile] + red[BM + row_in_tile];
     }
     __syncwarp();
-    ptx::cluster_sync_acq_rel();  // #3
+    ptx::cluster_sync_acq_rel();  // #1: every CTA's row statistics are visible
     if (is_epi) {
-        float tot = 0.0f;
+        float t1 = 0.0f, t2 = 0.0f;
 #pragma unroll
-        for (int r = 0; r < CLUSTER; ++r) tot += ptx::ld_shared_cluster_f32(&stats[row_in_tile], r);
-        rstd = 1.0f / sqrtf(tot * inv_n + la.eps);
-        // pass C: normalise, scale, shift, store.  Every lane takes part in the (warp-collective) TMEM loads;
+        for (int r = 0; r < CLUSTER; ++r) {
+            t1 += ptx::ld_shared_cluster_f32(&stats[row_in_tile], r);
+            t2 += ptx::ld_shared_cluster_f32(&stats[BM + row_in_tile], r);
+        }
+        mean = t1 * inv_n;
+        // mean of squared deviations from the fp32 sums; clamped at zero against rounding
+        const float var = fmaxf(fmaf(-mean, mean, t2 * inv_n), 0.0f);
+        rstd = 1.0f / sqrtf(var + la.eps);
+        // pass B: normalise, scale, shift, store.  Every lane takes part in the (warp-collective) TMEM loads;
         // only the global stores are guarded by the row bound.
         if (epi_ok) {
             __half* c_row = args.c + static_cast<int64_t>(row) * args.ldc;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                const int col0 = col_base + c * 32;
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);
-                uint4 rg[4], rb[4];
-                if (la.gamma) {
+            for (int c = 0; c < 4; c += 2) {
+                uint32_t r[2][32];
+                uint4 rg[2][4], rb[2][4];
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) rg[g] = __ldg(reinterpret_cast<const uint4*>(la.gamma + col0 + g * 8));
-                }
-                if (la.beta) {
+                for (int u = 0; u < 2; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) rb[g] = __ldg(reinterpret_cast<const uint4*>(la.beta + col0 + g * 8));
+                for (int u = 0; u < 2; ++u) {
+                    const int col0 = col_base + (c + u) * 32;
+                    if (la.gamma) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) rg[u][g] = __ldg(reinterpret_cast<const uint4*>(la.gamma + col0 + g * 8));
+                    }
+                    if (la.beta) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) rb[u][g] = __ldg(reinterpret_cast<const uint4*>(la.beta + col0 + g * 8));
+                    }
                 }
                 ptx::tmem_ld_wait();
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float gm[8], bt[8], o[8];
-                    if (la.gamma) unpack8(rg[g], gm);
-                    if (la.beta) unpack8(rb[g], bt);
+                for (int u = 0; u < 2; ++u) {
+                    const int col0 = col_base + (c + u) * 32;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float v = (__uint_as_float(r[g * 8 + j]) - mean) * rstd;
-                        if (la.gamma) v *= gm[j];
-                        if (la.beta) v += bt[j];
-                        o[j] = v;
+                    for (int g = 0; g < 4; ++g) {
+                        float gm[8], bt[8], o[8];
+                        if (la.gamma) unpack8(rg[u][g], gm);
+                        if (la.beta) unpack8(rb[u][g], bt);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float v = (__uint_as_float(r[u][g * 8 + j]) - mean) * rstd;
+                            if (la.gamma) v *= gm[j];
+                            if (la.beta) v += bt[j];
+                            o[j] = v;
+                        }
+                        if (row_ok) *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(o);
                     }
-                    if (row_ok) *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(o);
                 }
             }
         }
     }
     ptx::tc_fence_before();
     __syncthreads();
-    ptx::cluster_sync_acq_rel();  // #4: no CTA leaves while a peer may still read its statistics
+    ptx::cluster_sync_acq_rel();  // #2: no CTA leaves while a peer may still read its statistics
     if (warp == 1) {
         ptx::tc_fence_after();
         if (*reinterpret_cast<volatile int32_t*>(args.status) != DEV_OK) {
@@ -308,8 +304,10 @@ int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaS
     if (p->bias) vec = vec && aligned16(p->bias);
     if (p->ln_gamma) vec = vec && aligned16(p->ln_gamma);
     if (p->ln_beta) vec = vec && aligned16(p->ln_beta);
-    if (!shape_ok || !vec)
-        return fail(B200ML_ERR_UNSUPPORTED, "gemm + layernorm: needs fp16, N in {256, 512, 1024}, one batch and 16-byte aligned rows");
+    const bool act_ok = (p->epilogue & (B200ML_EPI_GELU | B200ML_EPI_SWISH)) == 0;  // only ReLU is folded in before the norm
+    if (!shape_ok || !vec || !act_ok)
+        return fail(B200ML_ERR_UNSUPPORTED,
+                    "gemm + layernorm: needs fp16, N in {256, 512, 1024}, one batch, 16-byte aligned rows, no GELU / Swish");
     LnArgs la{};
     GemmArgs& args = la.g;
     args.m = (int32_t)p->m;

@@ -660,7 +660,7 @@ class B200FusedMatMul(ONNXForward):
         # LayerNorm of the result: inside the GEMM epilogue where the fused kernel covers the shape (fp16, N a
         # multiple of 256 up to 1024), else as a second launch on a pre-normalisation buffer.
         eps = float(node.ln_epsilon)
-        fusable = a.dtype == torch.float16 and n in (256, 512, 1024) and k % 8 == 0
+        fusable = a.dtype == torch.float16 and n in (256, 512, 1024) and k % 8 == 0 and act in (0, L.EPI_RELU)
         if fusable:
 
             def run_fused(ins, outs):
