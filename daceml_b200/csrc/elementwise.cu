@@ -83,7 +83,8 @@ __global__ void __launch_bounds__(256) unary_kernel(const T* __restrict__ x, T* 
             float f[Pack<T>::N];
             Pack<T>::load(x + i, f);
 #pragma unroll
-            for (int j = 0; j < Pack<T>::N; ++j) f[j] = unary_apply(op, f[j], p0, p1);
+            for (int j = 0; j < Pack<T>::N; ++j)
+                f[j] = (sizeof(T) == 2 && op == B200ML_UN_GELU) ? gelu_erf_fast(f[j]) : unary_apply(op, f[j], p0, p1);
             Pack<T>::store(y + i, f);
         } else {
             stf(y + i, unary_apply(op, ldf(x + i), p0, p1));
@@ -140,6 +141,11 @@ __global__ void __launch_bounds__(256) binary_bcast_kernel(const T* __restrict__
     }
 }
 
+template <typename T>
+__device__ __forceinline__ float act_for(float v, int act) { return apply_act(v, act); }
+template <>
+__device__ __forceinline__ float act_for<__half>(float v, int act) { return apply_act_f16(v, act); }
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias,
                                                        const T* __restrict__ residual, T* __restrict__ y, int64_t n,
@@ -156,7 +162,7 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
                 for (int j = 0; j < Pack<T>::N; ++j) f[j] += t[j];
             }
 #pragma unroll
-            for (int j = 0; j < Pack<T>::N; ++j) f[j] = apply_act(f[j], act);
+            for (int j = 0; j < Pack<T>::N; ++j) f[j] = act_for<T>(f[j], act);
             if (residual) {
                 Pack<T>::load(residual + i, t);
 #pragma unroll
@@ -165,7 +171,7 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
             Pack<T>::store(y + i, f);
         } else {
             float v = ldf(x + i) + (bias ? ldf(bias + i % cols) : 0.0f);
-            v = apply_act(v, act);
+            v = act_for<T>(v, act);
             if (residual) v += ldf(residual + i);
             stf(y + i, v);
         }

@@ -58,6 +58,14 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
     return (0.5f * x) * phi2;
 }
 
+// Activation for results that are stored as fp16: GELU through the one-MUFU form above.
+__device__ __forceinline__ float apply_act_f16(float v, int32_t flags) {
+    if (flags & B200ML_EPI_RELU) v = fmaxf(v, 0.0f);
+    if (flags & B200ML_EPI_GELU) v = gelu_erf_fast(v);
+    if (flags & B200ML_EPI_SWISH) v = v * sigmoidf_(v);
+    return v;
+}
+
 // Residual / bias packets of one 32-column chunk, fetched before the accumulator arrives.
 struct EpiloguePrefetch {
     uint4 res[4];

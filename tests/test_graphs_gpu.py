@@ -81,6 +81,36 @@ def test_bert_layer_golden_fp16(fused):
     status_ok()
 
 
+@pytest.mark.parametrize("which", ["bert", "mlp", "mbconv"])
+def test_fusion_pass_preserves_results(which):
+    """auto_optimize on the exported graph (fusion pass + expansion) against the oracle and the node-by-node run."""
+    from daceml_b200.util.utils import auto_optimize
+    if which == "bert":
+        g = gold("bert_layer")
+        p = {k: t(g[k]) for k in g.files if k not in ("x", "y_fp32", "y_fp16")}
+        s = graphs.bert_layer_sdfg(p, 2, 40, 2, fused=False)
+        auto_optimize(s, cuda=True)
+        assert len(s.states()[0].topological_compute_nodes()) == 5
+        y = s(input=t(g["x"], torch.float16).cuda())
+        ref = ops.bert_layer(t(g["x"]).half().float().numpy(), {k: v.half().float().numpy() for k, v in p.items()}, heads=2,
+                             store=np.float32)
+        assert_close(y, ref, torch.float16, atol=1e-2, what="fused-by-pass bert layer")
+    elif which == "mlp":
+        g = gold("mlp")
+        p = {k: t(g[k]) for k in ("w1", "b1", "w2", "b2", "w3", "b3")}
+        s = graphs.mlp_sdfg(p, g["x"].shape[0], fused=False)
+        auto_optimize(s, cuda=True)
+        assert_close(s(input=t(g["x"]).cuda()), g["y"], what="fused-by-pass mlp")
+    else:
+        g = gold("mbconv")
+        p = {k: t(g[k]) for k in g.files if k not in ("x", "y")}
+        s = graphs.mbconv_sdfg(p, g["x"].shape, fused=False)
+        auto_optimize(s, cuda=True)
+        assert len(s.states()[0].topological_compute_nodes()) == 4
+        assert_close(s(input=t(g["x"]).cuda()), g["y"], what="fused-by-pass mbconv")
+    status_ok()
+
+
 def test_bert_layer_with_attention_mask():
     g = gold("bert_layer")
     p = {k: t(g[k]) for k in g.files if k not in ("x", "y_fp32", "y_fp16")}
