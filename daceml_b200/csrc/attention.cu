@@ -1,13 +1,20 @@
 // Fused attention for fp16 tensors with head_dim 64: O = softmax(scale * Q K^T + mask) V.
 //
-// One CTA per (batch, head, 128 query rows); two CTAs share an SM.  Per 64-key tile:
+// One CTA per (batch, head, 128 query rows).  A CTA is small on purpose - 192 threads, 128 TMEM
+// columns, ~54 KB of shared memory - so that FOUR of them share an SM: the softmax of one tile is a
+// chain of dependent steps (TMEM load, row maximum, exponentials, publish), and what hides that
+// latency is other CTAs' chains on the same SM sub-partition.  Per 32-key tile:
 //   warp 0   TMA loads of Q (once) and of the K_j / V_j tiles straight from the caller's strided
 //            tensors (so Q/K/V may live inside a packed [T, 3H] projection output - no head split);
-//   warp 1   tcgen05.mma S_j = Q K_j^T (128x64x64) into TMEM, O_j = P_j V_j (128x64x64);
-//            V is consumed MN-major exactly as TMA lays it down - no transpose;
-//   warps 2-5  one query row per thread: read S_j from TMEM, online softmax in the log2 domain,
-//            write P_j (fp16) into shared memory in the 128-byte-swizzled K-major layout the MMA
-//            reads, then fold O_{j-1} into the fp32 running output held in registers.
+//   warp 1   tcgen05.mma S_j = Q K_j^T (128x32x64) into one of two S buffers in TMEM, and
+//            O += P_j V_j (128x64x32) into the accumulator in TMEM; V is consumed MN-major exactly as
+//            TMA lays it down - no transpose;
+//   warps 2-5  one query row per thread: read S_j from TMEM, online softmax in the log2 domain, write
+//            P_j (fp16) into shared memory in the 128-byte-swizzled K-major layout the MMA reads (tiles
+//            alternate between the two halves of the 128-byte rows).
+// O stays in TMEM for the whole CTA.  It is rescaled only when a row maximum of the warp has grown by
+// more than 2^8 since the last rescale (P then stays below 256, safe in fp16), which after the first
+// tiles is rare; in the steady state the softmax threads never touch O.
 // The scores never touch HBM: traffic is Q, K, V in and O out.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -19,15 +26,19 @@ namespace b200ml {
 namespace {
 
 constexpr int AT_THREADS = 192;  // TMA warp, MMA warp, four softmax warps (one query row per thread)
+constexpr int AT_CTAS_PER_SM = 4;
 constexpr int QT = 128;          // query rows per CTA
-constexpr int KT = 64;           // keys per iteration
+constexpr int KT = 32;           // keys per iteration
 constexpr int HD = 64;           // head dimension
 constexpr int Q_BYTES = QT * HD * 2;     // 16 KB
-constexpr int KV_BYTES = KT * HD * 2;    // 8 KB: one K_j or V_j tile
-constexpr int P_BYTES = QT * KT * 2;     // 16 KB: one 64-key swizzle atom
-constexpr int KV_SLOTS = 4;              // K and V tiles travel through one ring in the order the MMA warp consumes them
-constexpr int AT_SMEM = Q_BYTES + KV_SLOTS * KV_BYTES + 2 * P_BYTES + 256 + 1024;
-constexpr uint32_t AT_TMEM_COLS = 256;   // S_even [0,64), S_odd [64,128), O_even [128,192), O_odd [192,256)
+constexpr int KV_BYTES = KT * HD * 2;    // 4 KB: one K_j or V_j tile
+constexpr int P_BYTES = QT * 128;        // 16 KB: rows of 128 bytes = two tiles of 32 keys side by side
+constexpr int KV_SLOTS = 5;              // K and V tiles travel through one ring in the order the MMA warp consumes them
+constexpr int AT_SMEM = Q_BYTES + KV_SLOTS * KV_BYTES + P_BYTES + 256 + 1024;
+constexpr uint32_t AT_TMEM_COLS = 128;   // S_0 [0,32), S_1 [32,64), O [64,128)
+constexpr uint32_t O_COL = 64;
+constexpr float RESCALE_STEP = 8.0f;     // log2 of the growth of a row maximum that forces a rescale
+constexpr float M_NONE = -1.0e30f;       // running maximum of a row that has seen no finite score yet
 
 struct AttnArgs {
     int32_t heads, seq_q, seq_kv, q_tiles;
@@ -36,7 +47,7 @@ struct AttnArgs {
     __half* o;
     const __half* mask;  // [batch, seq_kv] additive, or null
     int32_t* status;
-    long long* trace;
+    long long* trace;  // per-CTA cycle counters, only written when built with B200ML_TRACE
 };
 
 #ifdef B200ML_TRACE
@@ -51,28 +62,35 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// Everything the softmax warps and the tensor core exchange is double-buffered (S and O in TMEM, P in
-// shared memory), so S_{j+1} = Q K_{j+1}^T and O_{j-1} = P_{j-1} V_{j-1} run on the tensor core while
-// the softmax of tile j runs on the SIMT pipes.  The fold of O_{j-1} into the running output is
-// deferred by one tile for the same reason.
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM)
 attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const AttnArgs args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sq = smem;
-    uint8_t* skv = smem + Q_BYTES;                       // KV_SLOTS tiles of 8 KB
-    uint8_t* sp = skv + KV_SLOTS * KV_BYTES;             // two P buffers
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sp + 2 * P_BYTES);
+    uint8_t* skv = smem + Q_BYTES;                       // KV_SLOTS tiles of 4 KB
+    uint8_t* sp = skv + KV_SLOTS * KV_BYTES;             // P: 128 rows of 128 bytes (1024-byte aligned: 16 KB + 5 * 4 KB)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sp + P_BYTES);
     uint64_t* q_full = bars + 0;
     uint64_t* kv_full = bars + 1;               // [KV_SLOTS]
     uint64_t* kv_empty = kv_full + KV_SLOTS;    // [KV_SLOTS]
-    uint64_t* s_full = kv_empty + KV_SLOTS;     // [2]
-    uint64_t* p_full = s_full + 2;              // [2]
-    uint64_t* o_full = p_full + 2;              // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    uint64_t* s_full = kv_empty + KV_SLOTS;     // [2] S_b holds a new tile
+    uint64_t* s_free = s_full + 2;              // [2] the softmax warps have S_b in registers
+    uint64_t* p_full = s_free + 2;              // [2] P half b is written (and O rescaled if it had to be)
+    uint64_t* o_full = p_full + 2;              // [2] O += P_b V finished: P half b may be overwritten
+    uint64_t* o_final = o_full + 2;             // every product of this CTA has finished
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_final + 1);
 
     pdl_launch_dependents();
+#ifdef B200ML_TRACE
+    const long long tr_entry = clock64();
+#endif
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int qt = blockIdx.x % args.q_tiles;
@@ -96,9 +114,11 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             }
             for (int i = 0; i < 2; ++i) {
                 ptx::mbar_init(&s_full[i], 1);
-                ptx::mbar_init(&p_full[i], 4);  // one arrival per softmax warp
+                ptx::mbar_init(&s_free[i], 4);  // one arrival per softmax warp
+                ptx::mbar_init(&p_full[i], 4);
                 ptx::mbar_init(&o_full[i], 1);
             }
+            ptx::mbar_init(o_final, 1);
             ptx::fence_mbar_init();
         }
         __syncwarp();
@@ -111,7 +131,7 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();  // everything above overlaps the previous kernel's tail
 
-    // The ring carries K_0, then for every j: K_{j+1} (if any), V_j -- the order of consumption.
+    // Order of consumption, which the ring follows: K_0, K_1, then for every j: K_{j+2} (if any), V_j.
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (ptx::elect_one()) {
@@ -131,8 +151,9 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 ++item;
             };
             load(&tmap_k, 0);
+            if (ok && n_kv > 1) load(&tmap_k, 1);
             for (int j = 0; ok && j < n_kv; ++j) {
-                if (j + 1 < n_kv) load(&tmap_k, j + 1);
+                if (j + 2 < n_kv) load(&tmap_k, j + 2);
                 if (ok) load(&tmap_v, j);
             }
         }
@@ -143,13 +164,29 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             constexpr uint32_t IDESC_O = ptx::make_idesc_f16(128, HD, 0, 1);  // P K-major, V MN-major
             const uint32_t q_addr = ptx::smem_u32(sq), kv_addr = ptx::smem_u32(skv), p_addr = ptx::smem_u32(sp);
             int item = 0;
+#ifdef B200ML_TRACE
+            if (blockIdx.x < 512) args.trace[blockIdx.x * 20 + 10] = clock64() - tr_entry;
+#endif
             bool ok = ptx::mbar_wait(q_full, 0);
             if (!ok) atomicExch(args.status, DEV_TIMEOUT_ATTN);
-            // S_t = Q K_t^T into S buffer t & 1; the buffer's previous tile was consumed before P_{t-2} was
-            // published, which this thread has already waited for.
+#ifdef B200ML_TRACE
+            if (blockIdx.x < 512) args.trace[blockIdx.x * 20 + 11] = clock64() - tr_entry;
+#endif
+            // S_t = Q K_t^T into S buffer t & 1
+#ifdef B200ML_TRACE
+            long long mw[4] = {0, 0, 0, 0};
+#define MW_T0() const long long _w0 = clock64()
+#define MW_ADD(i) mw[i] += clock64() - _w0
+#else
+#define MW_T0()
+#define MW_ADD(i)
+#endif
             auto issue_s = [&](int t) {
                 const int slot = item % KV_SLOTS;
-                if (!ptx::mbar_wait(&kv_full[slot], (item / KV_SLOTS) & 1)) {
+                MW_T0();
+                const bool got = ptx::mbar_wait(&kv_full[slot], (item / KV_SLOTS) & 1);
+                MW_ADD(1);
+                if (!got) {
                     atomicExch(args.status, DEV_TIMEOUT_ATTN);
                     ok = false;
                     return;
@@ -167,161 +204,214 @@ attention_f16_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                 ++item;
             };
             if (ok) issue_s(0);
+            if (ok && n_kv > 1) issue_s(1);
             for (int j = 0; ok && j < n_kv; ++j) {
-                if (j + 1 < n_kv) issue_s(j + 1);
-                if (!ok) break;
-                // O_j = P_j V_j into O buffer j & 1 (its previous tile was folded before P_j was published)
+                const int b = j & 1;
+                const uint32_t use = (j >> 1) & 1;  // parity of the buffer's use counter
+                if (j + 2 < n_kv) {
+                    // S_j is in registers: its buffer takes the tile after next
+                    MW_T0();
+                    const bool got = ptx::mbar_wait(&s_free[b], use);
+                    MW_ADD(0);
+                    if (!got) {
+                        atomicExch(args.status, DEV_TIMEOUT_ATTN);
+                        break;
+                    }
+                    issue_s(j + 2);
+                    if (!ok) break;
+                }
+                // O += P_j V_j
                 const int slot = item % KV_SLOTS;
-                if (!ptx::mbar_wait(&p_full[j & 1], (j >> 1) & 1) || !ptx::mbar_wait(&kv_full[slot], (item / KV_SLOTS) & 1)) {
+                bool got;
+                {
+                    MW_T0();
+                    got = ptx::mbar_wait(&p_full[b], use);
+                    MW_ADD(2);
+                }
+                {
+                    MW_T0();
+                    got = got && ptx::mbar_wait(&kv_full[slot], (item / KV_SLOTS) & 1);
+                    MW_ADD(3);
+                }
+                if (!got) {
                     atomicExch(args.status, DEV_TIMEOUT_ATTN);
                     break;
                 }
                 ptx::tc_fence_after();
                 const uint32_t v_addr = kv_addr + slot * KV_BYTES;
-                const uint32_t pj_addr = p_addr + (j & 1) * P_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
                     // P: 32 bytes per 16-key step inside the 128-byte swizzle row; V: 16 key rows of 128 bytes per step
-                    const uint64_t a = ptx::make_smem_desc_sw128(pj_addr + kk * 32, 16, 1024);
-                    const uint64_t b = ptx::make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024);
-                    ptx::mma_f16_ss(tmem_base + 128 + (j & 1) * HD, a, b, IDESC_O, kk != 0 ? 1u : 0u);
+                    const uint64_t a = ptx::make_smem_desc_sw128(p_addr + (b * 2 + kk) * 32, 16, 1024);
+                    const uint64_t v = ptx::make_smem_desc_sw128(v_addr + kk * 2048, 16, 1024);
+                    ptx::mma_f16_ss(tmem_base + O_COL, a, v, IDESC_O, (j != 0 || kk != 0) ? 1u : 0u);
                 }
-                ptx::mma_commit(&o_full[j & 1]);
+                ptx::mma_commit(&o_full[b]);
                 ptx::mma_commit(&kv_empty[slot]);
                 ++item;
             }
+            ptx::mma_commit(o_final);  // arrives when every product issued above has finished
+#ifdef B200ML_TRACE
+            if (blockIdx.x < 512) for (int i = 0; i < 4; ++i) args.trace[blockIdx.x * 20 + 14 + i] = mw[i];
+#endif
         }
     } else {
         // ------------------------------ softmax + output ------------------------------
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;    // the TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;  // row of the query tile == TMEM lane
         const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-        float acc[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
+        const uint32_t o_addr = tmem_base + O_COL + lane_off;
+        uint8_t* p_row = sp + row * 128;
+        float m_used = M_NONE, l_run = 0.0f;
         const __half* mrow = args.mask ? args.mask + static_cast<int64_t>(batch) * args.seq_kv : nullptr;
         constexpr float LOG2E = 1.44269504088896340736f;
+        bool ok = true;
 #ifdef B200ML_TRACE
         long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tr_last = clock64();
+        const long long tr_begin = tr_last;
 #endif
-        bool ok = true;
-        // folds O_t (finished by the tensor core) into the running output: acc = acc * alpha_t + O_t
-        auto fold = [&](int t, float alpha) {
-            if (!ptx::mbar_wait(&o_full[t & 1], (t >> 1) & 1)) {
-                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
-                ok = false;
-                return;
-            }
-            ptx::tc_fence_after();
-            AT_MARK(4);
-#pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                uint32_t ro[32];
-                ptx::tmem_ld_32x32b_x32(tmem_base + 128 + (t & 1) * HD + lane_off + c * 32, ro);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(ro[i]));
-            }
-            ptx::tc_fence_before();
-            AT_MARK(5);
-        };
-        for (int j = 0; ok && j < n_kv; ++j) {
+        for (int j = 0; j < n_kv; ++j) {
             const int kv0 = j * KT;
-            const uint32_t s_addr = tmem_base + (j & 1) * KT + lane_off;
-            uint8_t* p_row = sp + (j & 1) * P_BYTES + row * 128;
-            if (!ptx::mbar_wait(&s_full[j & 1], (j >> 1) & 1)) {
-                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
-                ok = false;
-                break;
-            }
+            const int b = j & 1;
+            const uint32_t use = (j >> 1) & 1;
+            ok = __all_sync(0xffffffffu, ptx::mbar_wait(&s_full[b], use));
+            if (!ok) break;
             ptx::tc_fence_after();
             AT_MARK(0);
+#ifdef B200ML_TRACE
+            if (j == 0 && threadIdx.x == 64 && blockIdx.x < 512) args.trace[blockIdx.x * 20 + 12] = clock64() - tr_entry;
+#endif
             // A tile is "plain" when every key is in range and there is no additive mask: the scale then
-            // commutes with the maximum (one FMNMX per score) and P costs FFMA + EX2 + FADD per score.
+            // commutes with the maximum (one FMNMX per two scores) and P costs FFMA + EX2 + FADD per score.
             const bool plain = (kv0 + KT <= args.seq_kv) && mrow == nullptr && args.scale_log2 > 0.0f;
-            uint32_t r[2][32];
-            ptx::tmem_ld_32x32b_x32(s_addr, r[0]);
-            ptx::tmem_ld_32x32b_x32(s_addr + 32, r[1]);
+            uint32_t r[32];
+            ptx::tmem_ld_32x32b_x32(tmem_base + b * KT + lane_off, r);
             ptx::tmem_ld_wait();
-            float mx = -INFINITY;
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&s_free[b]);
+            AT_MARK(1);
+            float mx;
             if (plain) {
+                float mx0 = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+                float mx1 = max3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(r[0][i]), __uint_as_float(r[1][i])));
-                mx *= args.scale_log2;
+                for (int i = 6; i < 30; i += 4) {
+                    mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                    mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                }
+                mx = max3(mx0, mx1, fmaxf(__uint_as_float(r[30]), __uint_as_float(r[31]))) * args.scale_log2;
             } else {
                 // store the scaled, masked score back into the register it came from
+                mx = -INFINITY;
 #pragma unroll
-                for (int u = 0; u < 2; ++u)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int kv = kv0 + u * 32 + i;
-                        float v = __uint_as_float(r[u][i]) * args.scale_log2;
-                        if (mrow && kv < args.seq_kv) v = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, v);
-                        if (kv >= args.seq_kv) v = -INFINITY;
-                        r[u][i] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
-                    }
-            }
-            mx = fmaxf(mx, m_run);
-            const float m_safe = (mx == -INFINITY) ? 0.0f : mx;
-            const float alpha = ex2(m_run - m_safe);  // 0 on the first tile
-            AT_MARK(1);
-            float sum = 0.0f;
-            const float c_mul = plain ? args.scale_log2 : 1.0f;
-            const float neg_m = -m_safe;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float p[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        p[i] = ex2(fmaf(__uint_as_float(r[u][g * 8 + i]), c_mul, neg_m));
-                        sum += p[i];
-                    }
-                    *reinterpret_cast<uint4*>(p_row + (((u * 4 + g) ^ (row & 7)) << 4)) = pack8(p);
+                for (int i = 0; i < 32; ++i) {
+                    const int kv = kv0 + i;
+                    float v = __uint_as_float(r[i]) * args.scale_log2;
+                    if (mrow && kv < args.seq_kv) v = fmaf(__half2float(__ldg(mrow + kv)), LOG2E, v);
+                    if (kv >= args.seq_kv) v = -INFINITY;
+                    r[i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
                 }
             }
-            l_run = fmaf(l_run, alpha, sum);
-            m_run = mx;
             AT_MARK(2);
+            if (j >= 2) {
+                // the product of the tile before last has finished reading this half of P
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait(&o_full[b], use ^ 1));
+                if (!ok) break;
+            }
+            AT_MARK(3);
+            if (__any_sync(0xffffffffu, mx > m_used + RESCALE_STEP)) {
+                const float m_new = fmaxf(m_used, mx);
+                const float f = ex2(m_used - m_new);  // 0 for a row that had no finite score so far
+                l_run *= f;
+                m_used = m_new;
+                if (j >= 1) {
+                    // O must be at rest: wait for the product of the previous tile as well
+                    ok = __all_sync(0xffffffffu, ptx::mbar_wait(&o_full[b ^ 1], ((j - 1) >> 1) & 1));
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < HD / 16; ++c) {
+                        uint32_t ro[16];
+                        ptx::tmem_ld_32x32b_x16(o_addr + c * 16, ro);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * f);
+                        ptx::tmem_st_32x32b_x16(o_addr + c * 16, ro);
+                    }
+                    ptx::tmem_st_wait();
+                }
+#ifdef B200ML_TRACE
+                tr[7] += 1;
+#endif
+            }
+            AT_MARK(4);
+            float sum0 = 0.0f, sum1 = 0.0f;
+            const float c_mul = plain ? args.scale_log2 : 1.0f;
+            const float neg_m = -m_used;
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+                float p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) p[i] = ex2(fmaf(__uint_as_float(r[q8 * 8 + i]), c_mul, neg_m));
+                sum0 += (p[0] + p[1]) + (p[2] + p[3]);
+                sum1 += (p[4] + p[5]) + (p[6] + p[7]);
+                *reinterpret_cast<uint4*>(p_row + (((b * 4 + q8) ^ (row & 7)) << 4)) = pack8(p);
+            }
+            l_run += sum0 + sum1;
+            AT_MARK(5);
             ptx::fence_proxy_async_smem();  // P visible to the tensor core's shared-memory reads
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&p_full[j & 1]);
-            AT_MARK(3);
-            if (j >= 1) fold(j - 1, alpha_prev);
-            alpha_prev = alpha;
+            if (lane == 0) ptx::mbar_arrive(&p_full[b]);
+            AT_MARK(6);
         }
-        if (ok && n_kv >= 1) fold(n_kv - 1, alpha_prev);
 #ifdef B200ML_TRACE
         if (threadIdx.x == 64 && blockIdx.x < 512) {
-            for (int i = 0; i < 7; ++i) args.trace[blockIdx.x * 8 + i] = tr[i];
+            long long* t = args.trace + blockIdx.x * 20;
+            for (int i = 0; i < 8; ++i) t[i] = tr[i];
+            t[8] = clock64() - tr_begin;
+            t[9] = tr_begin - tr_entry;
         }
 #endif
+        if (!ok && lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
+        const bool done = __all_sync(0xffffffffu, ptx::mbar_wait(o_final, 0));
+        if (!done && lane == 0) atomicExch(args.status, DEV_TIMEOUT_ATTN);
+        ptx::tc_fence_after();
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
         const int q = q0 + row;
-        if (ok && q < args.seq_q) {
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            __half* op = args.o + batch * args.o_stride_b + head * args.o_stride_h + static_cast<int64_t>(q) * args.o_stride_s;
-            if ((reinterpret_cast<uintptr_t>(op) & 15) == 0) {
+        const bool store = ok && done && n_kv >= 1 && q < args.seq_q;
+        __half* op = args.o + batch * args.o_stride_b + head * args.o_stride_h + static_cast<int64_t>(q) * args.o_stride_s;
+        const bool vec = (reinterpret_cast<uintptr_t>(op) & 15) == 0;
 #pragma unroll
-                for (int g = 0; g < HD / 8; ++g) {
-                    float v[8];
+        for (int c = 0; c < HD / 32; ++c) {
+            uint32_t x[32];
+            ptx::tmem_ld_32x32b_x32(o_addr + c * 32, x);  // every lane loads; only the stores are guarded
+            ptx::tmem_ld_wait();
+            if (store) {
+                if (vec) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = acc[g * 8 + i] * inv;
-                    *reinterpret_cast<uint4*>(op + g * 8) = pack8(v);
+                    for (int g8 = 0; g8 < 4; ++g8) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(x[g8 * 8 + i]) * inv;
+                        *reinterpret_cast<uint4*>(op + c * 32 + g8 * 8) = pack8(v);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) op[c * 32 + i] = __float2half_rn(__uint_as_float(x[i]) * inv);
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < HD; ++i) op[i] = __float2half_rn(acc[i] * inv);
             }
         }
     }
 
     ptx::tc_fence_before();
     __syncthreads();
+#ifdef B200ML_TRACE
+    if (threadIdx.x == 64 && blockIdx.x < 512) args.trace[blockIdx.x * 20 + 13] = clock64() - tr_entry;
+#endif
     if (warp == 1) {
         ptx::tc_fence_after();
         if (*reinterpret_cast<volatile int32_t*>(args.status) != DEV_OK) {
@@ -386,6 +476,7 @@ int attention_f16(const b200ml_ctx* ctx, const b200ml_attention_params* p, cudaS
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         B200ML_CUDA(cudaFuncSetAttribute(attention_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
+        B200ML_CUDA(cudaFuncSetAttribute(attention_f16_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
         configured[ctx->device & 63] = true;
     }
     B200ML_CUDA(launch_pdl(attention_f16_kernel, dim3((unsigned)grid), dim3(AT_THREADS), AT_SMEM, stream, tq, tk, tv, a));
