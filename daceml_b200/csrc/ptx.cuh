@@ -77,6 +77,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
+// Non-blocking test: has the phase with the given parity completed?
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // Wall-clock limit of every device-side wait.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
@@ -86,6 +101,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3ffu) == 0) {
+            if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        }
+    }
+    return true;
+}
+
+// Same contract as mbar_wait, but polls with the non-blocking test instead of the potentially
+// suspending try_wait: for the waits on a kernel's critical path, where the wake-up latency counts.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_test_wait(bar, parity)) {
         if ((++spins & 0x3ffu) == 0) {
             if (global_timer_ns() - t0 > kWaitLimitNs) return false;
         }
