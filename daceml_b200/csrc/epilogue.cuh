@@ -85,6 +85,55 @@ __device__ __forceinline__ void epilogue_prefetch_32(const EpilogueParams& ep, E
     }
 }
 
+// Finishes 32 consecutive columns of one output row held as raw fp32 bits in r and returns them as four
+// packets of eight fp16 values (the caller stages them in shared memory for a bulk tensor store).  The
+// bias / residual packets come from epilogue_prefetch_32; every branch on ep.flags is warp-uniform.
+__device__ __forceinline__ void epilogue_pack_32(const EpilogueParams& ep, const uint32_t (&r)[32],
+                                                 const EpiloguePrefetch& pf, bool has_bias, bool has_res, uint4 (&out)[4]) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (ep.alpha != 1.0f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= ep.alpha;
+    }
+    if (has_bias) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float b[8];
+            unpack8(pf.bias[g], b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[g * 8 + j] = fmaf(ep.bias_scale, b[j], v[g * 8 + j]);
+        }
+    }
+    if (ep.flags & B200ML_EPI_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = gelu_erf_fast(v[j]);
+    } else if (ep.flags & B200ML_EPI_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+    } else if (ep.flags & B200ML_EPI_SWISH) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoidf_(v[j]);
+    }
+    if (has_res) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            float q[8];
+            unpack8(pf.res[g], q);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[g * 8 + j] = fmaf(ep.residual_scale, q[j], v[g * 8 + j]);
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[g * 8 + j];
+        out[g] = pack8(o);
+    }
+}
+
 // Finishes 32 consecutive columns [col0, col0 + 32) of one output row held as raw fp32 bits in r.
 // Every branch on ep.flags is warp-uniform; the per-element work is alpha, bias, activation,
 // residual, one fp16 conversion.

@@ -26,6 +26,7 @@ struct GemmArgs {
     int64_t ldr, r_so, r_si;
     float alpha, bias_scale, residual_scale;
     int32_t vec_ok;  // C (and residual) rows are 16-byte aligned
+    int32_t tma_store;  // the kernel got a tensor map of C: finished tiles leave through shared memory and bulk stores
     __half* c;
     const __half* bias;
     const __half* residual;

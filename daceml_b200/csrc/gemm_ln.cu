@@ -7,6 +7,9 @@
 // pre-normalisation row is parked in TMEM (fp32) between the two passes, so nothing is re-read from memory.
 // This removes the separate LayerNorm kernel (one read and one write of the activation) behind the
 // attention output projection and the second FFN matrix product.
+// The normalised rows leave through shared memory (the pipeline stages are free by then): each epilogue
+// warp stages 32 rows x 64 columns in the 128-byte swizzle of a tensor map and one lane issues a bulk
+// tensor store; rows past M are clipped by the tensor map.
 #include "gemm_common.cuh"
 
 namespace b200ml {
@@ -31,7 +34,7 @@ struct LnArgs {
 template <int CLUSTER, bool B_MN>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const LnArgs la) {
+                   const __grid_constant__ CUtensorMap tmap_c, const LnArgs la) {
     const GemmArgs& args = la.g;
     constexpr uint32_t TMEM_COLS = LN_BN;
     constexpr uint32_t IDESC = ptx::make_idesc_f16(BM, LN_BN, 0, B_MN ? 1 : 0);
@@ -57,6 +60,7 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         if (lane == 0) {
@@ -226,7 +230,9 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         // pass B: normalise, scale, shift, store.  Every lane takes part in the (warp-collective) TMEM loads;
         // only the global stores are guarded by the row bound.
         if (epi_ok) {
-            __half* c_row = args.c + static_cast<int64_t>(row) * args.ldc;
+            // every product has finished (tmem_full), so the first pipeline stage is free to stage the output
+            uint8_t* stage_tile = smem + (warp - 2) * 4096;
+            uint8_t* stage_row = stage_tile + lane * 128;
 #pragma unroll 1
             for (int c = 0; c < 4; c += 2) {
                 uint32_t r[2][32];
@@ -246,9 +252,10 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     }
                 }
                 ptx::tmem_ld_wait();
+                if (lane == 0) ptx::tma_store_wait_read<0>();  // the previous store has read the staging tile
+                __syncwarp();
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int col0 = col_base + (c + u) * 32;
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         float gm[8], bt[8], o[8];
@@ -261,10 +268,17 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                             if (la.beta) v += bt[j];
                             o[j] = v;
                         }
-                        if (row_ok) *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = pack8(o);
+                        *reinterpret_cast<uint4*>(stage_row + (((u * 4 + g) ^ (lane & 7)) << 4)) = pack8(o);
                     }
                 }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::tma_store_4d(&tmap_c, stage_tile, col_base + c * 32, m0 + quarter * 32, 0, 0);
+                    ptx::tma_store_commit();
+                }
             }
+            if (lane == 0) ptx::tma_store_wait<0>();  // the bulk stores have landed before the CTA may leave
         }
     }
     ptx::tc_fence_before();
@@ -280,15 +294,15 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 }
 
 template <int CLUSTER, bool B_MN>
-int launch_ln(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const LnArgs& la, int tiles_m,
-              cudaStream_t stream) {
+int launch_ln(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const LnArgs& la,
+              int tiles_m, cudaStream_t stream) {
     auto kernel = gemm_f16_ln_kernel<CLUSTER, B_MN>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         B200ML_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LN_SMEM));
         configured[ctx->device & 63] = true;
     }
-    B200ML_CUDA(launch_pdl(kernel, dim3(tiles_m * CLUSTER), dim3(GEMM_THREADS), LN_SMEM, stream, ta, tb, la));
+    B200ML_CUDA(launch_pdl(kernel, dim3(tiles_m * CLUSTER), dim3(GEMM_THREADS), LN_SMEM, stream, ta, tb, tc, la));
     return check_launch("gemm_f16_ln");
 }
 
@@ -329,24 +343,26 @@ int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaS
     la.eps = p->ln_eps;
     la.cluster = (int32_t)(p->n / LN_BN);
     const int tiles_m = (int)ceil_div(p->m, BM);
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, 1, 0, 1, 0, BK, BM, "A");
+    if (rc) return rc;
+    rc = make_tmap(ctx, &tc, p->c, p->n, p->m, p->ldc, 1, 0, 1, 0, 64, 32, "C");
     if (rc) return rc;
     if (p->b_layout == 1) {
         rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, 1, 0, 1, 0, BK, LN_BN, "B");
         if (rc) return rc;
         switch (la.cluster) {
-            case 1: return launch_ln<1, false>(ctx, ta, tb, la, tiles_m, stream);
-            case 2: return launch_ln<2, false>(ctx, ta, tb, la, tiles_m, stream);
-            default: return launch_ln<4, false>(ctx, ta, tb, la, tiles_m, stream);
+            case 1: return launch_ln<1, false>(ctx, ta, tb, tc, la, tiles_m, stream);
+            case 2: return launch_ln<2, false>(ctx, ta, tb, tc, la, tiles_m, stream);
+            default: return launch_ln<4, false>(ctx, ta, tb, tc, la, tiles_m, stream);
         }
     }
     rc = make_tmap(ctx, &tb, p->b, p->n, p->k, p->ldb, 1, 0, 1, 0, 64, BK, "B");
     if (rc) return rc;
     switch (la.cluster) {
-        case 1: return launch_ln<1, true>(ctx, ta, tb, la, tiles_m, stream);
-        case 2: return launch_ln<2, true>(ctx, ta, tb, la, tiles_m, stream);
-        default: return launch_ln<4, true>(ctx, ta, tb, la, tiles_m, stream);
+        case 1: return launch_ln<1, true>(ctx, ta, tb, tc, la, tiles_m, stream);
+        case 2: return launch_ln<2, true>(ctx, ta, tb, tc, la, tiles_m, stream);
+        default: return launch_ln<4, true>(ctx, ta, tb, tc, la, tiles_m, stream);
     }
 }
 

@@ -30,14 +30,19 @@ struct GemmSmem {
     static constexpr int B_TILE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int OUT_BYTES = BN >= 128 ? EPI_WARPS * 32 * 128 : 0;  // a 32-row x 128-byte staging tile per epilogue warp
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;  // + slack for 1024-byte alignment
 };
 
-template <int BN, bool B_MN>
+// TMA_OUT: finished tiles leave through shared memory - each epilogue warp stages 32 rows x 64 columns
+// (4 KB, in the 128-byte swizzle a tensor map expects) and one lane issues a bulk tensor store, instead
+// of every lane writing 16-byte pieces of 32 different rows; ragged edges are clipped by the tensor map.
+template <int BN, bool B_MN, bool TMA_OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmArgs args) {
+                   const __grid_constant__ CUtensorMap tmap_c, const GemmArgs args) {
+    static_assert(!TMA_OUT || BN >= 128, "the staged output path moves 64 columns per store");
     using S = GemmSmem<BN>;
     constexpr int STAGES = S::STAGES;
     constexpr uint32_t TMEM_COLS = 2 * BN;  // 128, 256 or 512: a power of two
@@ -45,7 +50,8 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    uint8_t* out_stage = smem + STAGES * S::STAGE_BYTES;  // 1024-byte aligned: every stage is a multiple of 1 KB
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(out_stage + S::OUT_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full_bar = empty_bar + STAGES;
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
@@ -59,6 +65,7 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (TMA_OUT) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         if (lane == 0) {
@@ -235,6 +242,43 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const bool row_ok = row < args.m;
             const bool vec = args.vec_ok != 0;
             const uint32_t t_base = tmem_base + acc * BN + half * WCOLS + (static_cast<uint32_t>(quarter * 32) << 16);
+            if constexpr (TMA_OUT) {
+                // 64 columns at a time: TMEM -> registers -> epilogue math -> swizzled staging tile -> bulk store
+                uint8_t* stage_row = out_stage + (warp - 2) * 4096 + lane * 128;
+                const bool has_bias = (ep.flags & B200ML_EPI_BIAS) && args.bias != nullptr;
+                const bool has_res = (ep.flags & B200ML_EPI_RESIDUAL) && r_row != nullptr;
+#pragma unroll 1
+                for (int c = 0; c < CHUNKS; c += 2) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 >= args.n) break;  // warp-uniform
+                    uint32_t r[2][32];
+                    EpiloguePrefetch pf[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
+                    if (row_ok) {
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            epilogue_prefetch_32(ep, pf[u], r_row, args.bias, col0 + u * 32, args.n, true);
+                    }
+                    ptx::tmem_ld_wait();
+                    if (lane == 0) ptx::tma_store_wait_read<0>();  // the previous store has read the staging tile
+                    __syncwarp();
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        uint4 o[4];
+                        epilogue_pack_32(ep, r[u], pf[u], has_bias, has_res && row_ok, o);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            *reinterpret_cast<uint4*>(stage_row + (((u * 4 + g) ^ (lane & 7)) << 4)) = o[g];
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_4d(&tmap_c, out_stage + (warp - 2) * 4096, col0, mt * BM + quarter * 32, bi, bo);
+                        ptx::tma_store_commit();
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c = 0; c < CHUNKS; c += GROUP) {
                 const int col0 = n0 + c * 32;
@@ -261,12 +305,14 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     }
                 }
             }
+            }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tmem_empty_bar[acc]);
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
+        if (TMA_OUT && lane == 0) ptx::tma_store_wait<0>();  // every bulk store of this warp has landed
 #ifdef B200ML_TRACE
         if (threadIdx.x == 64) {
             args.trace[blockIdx.x * 16 + 5] = tr_wait_epi;
@@ -290,18 +336,28 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
 }
 
-template <int BN, bool B_MN>
-int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, cudaStream_t stream) {
+template <int BN, bool B_MN, bool TMA_OUT>
+int launch_impl(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmArgs& args,
+                cudaStream_t stream) {
     using S = GemmSmem<BN>;
-    auto kernel = gemm_f16_tc_kernel<BN, B_MN>;
+    auto kernel = gemm_f16_tc_kernel<BN, B_MN, TMA_OUT>;
     static bool configured[64] = {};  // per instantiation and device
     if (!configured[ctx->device & 63]) {
         B200ML_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         configured[ctx->device & 63] = true;
     }
     const int grid = args.num_tiles < ctx->sm_count ? args.num_tiles : ctx->sm_count;
-    B200ML_CUDA(launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, args));
+    B200ML_CUDA(launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, tc, args));
     return check_launch("gemm_f16_tc");
+}
+
+template <int BN, bool B_MN>
+int launch(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmArgs& args,
+           cudaStream_t stream) {
+    if constexpr (BN >= 128) {
+        if (args.tma_store) return launch_impl<BN, B_MN, true>(ctx, ta, tb, tc, args, stream);
+    }
+    return launch_impl<BN, B_MN, false>(ctx, ta, tb, tc, args, stream);
 }
 
 }  // namespace
@@ -378,27 +434,37 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
         return gemm_f16_pair(ctx, p, args, bn, stream);
     }
 
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, p->batch_inner, p->a_stride_inner, p->batch_outer,
                        p->a_stride_outer, BK, BM, "A");
     if (rc) return rc;
+    // C leaves through bulk tensor stores (64 columns x 32 rows per store) when its rows are 16-byte aligned
+    // and N is a whole number of 64-column pieces; otherwise the warps store their rows themselves.
+    args.tma_store = 0;
+    tc = ta;
+    if (bn >= 128 && args.vec_ok && p->n % 64 == 0) {
+        rc = make_tmap(ctx, &tc, p->c, p->n, p->m, p->ldc, p->batch_inner, p->c_stride_inner, p->batch_outer,
+                       p->c_stride_outer, 64, 32, "C");
+        if (rc) return rc;
+        args.tma_store = 1;
+    }
     if (p->b_layout == 1) {
         rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, p->batch_inner, p->b_stride_inner, p->batch_outer,
                        p->b_stride_outer, BK, bn, "B");
         if (rc) return rc;
         switch (bn) {
-            case 256: return launch<256, false>(ctx, ta, tb, args, stream);
-            case 128: return launch<128, false>(ctx, ta, tb, args, stream);
-            default: return launch<64, false>(ctx, ta, tb, args, stream);
+            case 256: return launch<256, false>(ctx, ta, tb, tc, args, stream);
+            case 128: return launch<128, false>(ctx, ta, tb, tc, args, stream);
+            default: return launch<64, false>(ctx, ta, tb, tc, args, stream);
         }
     } else {
         rc = make_tmap(ctx, &tb, p->b, p->n, p->k, p->ldb, p->batch_inner, p->b_stride_inner, p->batch_outer,
                        p->b_stride_outer, 64, BK, "B");
         if (rc) return rc;
         switch (bn) {
-            case 256: return launch<256, true>(ctx, ta, tb, args, stream);
-            case 128: return launch<128, true>(ctx, ta, tb, args, stream);
-            default: return launch<64, true>(ctx, ta, tb, args, stream);
+            case 256: return launch<256, true>(ctx, ta, tb, tc, args, stream);
+            case 128: return launch<128, true>(ctx, ta, tb, tc, args, stream);
+            default: return launch<64, true>(ctx, ta, tb, tc, args, stream);
         }
     }
 }

@@ -13,6 +13,10 @@
 //   tmem_full[a]   one per CTA; multicast commit after the last k-block of a tile;
 //   tmem_empty[a]  lives in the even CTA; the 16 epilogue warps of the pair arrive on it.
 // No multicast loads are used: every byte is fetched once, by the CTA that owns it.
+//
+// Finished tiles leave through shared memory: each epilogue warp stages 32 rows x 64 columns (4 KB, in
+// the 128-byte swizzle a tensor map expects) and one lane issues a bulk tensor store, instead of every
+// lane writing 16-byte pieces of 32 different rows.  Ragged edges are clipped by the tensor map.
 #include "gemm_common.cuh"
 
 #include <cooperative_groups.h>
@@ -28,14 +32,15 @@ struct PairSmem {
     static constexpr int B_TILE_BYTES = (BN / 2) * BK * 2;  // this CTA's half of the B tile
     static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     static constexpr int STAGES = (BN == 256) ? 6 : 8;
+    static constexpr int OUT_BYTES = EPI_WARPS * 32 * 128;  // one 32-row x 128-byte staging tile per epilogue warp
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;
 };
 
-template <int BN, bool B_MN>
+template <int BN, bool B_MN, bool TMA_OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const GemmArgs args) {
+                     const __grid_constant__ CUtensorMap tmap_c, const GemmArgs args) {
     using S = PairSmem<BN>;
     constexpr int STAGES = S::STAGES;
     constexpr int HALF_N = BN / 2;
@@ -44,7 +49,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+    uint8_t* out_stage = smem + STAGES * S::STAGE_BYTES;  // 1024-byte aligned: every stage is a multiple of 1 KB
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(out_stage + S::OUT_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full_bar = empty_bar + STAGES;
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
@@ -61,6 +67,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (TMA_OUT) ptx::prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         if (lane == 0) {
@@ -207,6 +214,44 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const bool row_ok = row < args.m;
             const bool vec = args.vec_ok != 0;
             const uint32_t t_base = tmem_base + acc * BN + half * WCOLS + (static_cast<uint32_t>(quarter * 32) << 16);
+            if constexpr (TMA_OUT) {
+                // 64 columns at a time: TMEM -> registers -> epilogue math -> swizzled staging tile -> bulk store
+                static_assert(CHUNKS % 2 == 0, "the staged path moves two 32-column chunks per store");
+                uint8_t* stage_row = out_stage + (warp - 2) * 4096 + lane * 128;
+                const bool has_bias = (ep.flags & B200ML_EPI_BIAS) && args.bias != nullptr;
+                const bool has_res = (ep.flags & B200ML_EPI_RESIDUAL) && r_row != nullptr;
+#pragma unroll 1
+                for (int c = 0; c < CHUNKS; c += 2) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 >= args.n) break;  // warp-uniform
+                    uint32_t r[2][32];
+                    EpiloguePrefetch pf[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
+                    if (row_ok) {
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            epilogue_prefetch_32(ep, pf[u], r_row, args.bias, col0 + u * 32, args.n, true);
+                    }
+                    ptx::tmem_ld_wait();
+                    if (lane == 0) ptx::tma_store_wait_read<0>();  // the previous store has read the staging tile
+                    __syncwarp();
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        uint4 o[4];
+                        epilogue_pack_32(ep, r[u], pf[u], has_bias, has_res && row_ok, o);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            *reinterpret_cast<uint4*>(stage_row + (((u * 4 + g) ^ (lane & 7)) << 4)) = o[g];
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_4d(&tmap_c, out_stage + (warp - 2) * 4096, col0, mt * (2 * BM) + static_cast<int>(cta) * BM + quarter * 32, bi, bo);
+                        ptx::tma_store_commit();
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c = 0; c < CHUNKS; c += GROUP) {
                 const int col0 = n0 + c * 32;
@@ -229,12 +274,14 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     }
                 }
             }
+            }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::leader_addr(&tmem_empty_bar[acc]));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
+        if (TMA_OUT && lane == 0) ptx::tma_store_wait<0>();  // every bulk store of this warp has landed
     }
 
     // ------------------------------ teardown ------------------------------
@@ -250,10 +297,11 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
 }
 
-template <int BN, bool B_MN>
-int launch_pair(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& args, cudaStream_t stream) {
+template <int BN, bool B_MN, bool TMA_OUT>
+int launch_pair_impl(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmArgs& args,
+                cudaStream_t stream) {
     using S = PairSmem<BN>;
-    auto kernel = gemm_f16_pair_kernel<BN, B_MN>;
+    auto kernel = gemm_f16_pair_kernel<BN, B_MN, TMA_OUT>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         B200ML_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
@@ -261,8 +309,15 @@ int launch_pair(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap&
     }
     const int max_pairs = ctx->sm_count / 2;
     const int pairs = args.num_tiles < max_pairs ? args.num_tiles : max_pairs;
-    B200ML_CUDA(launch_pdl(kernel, dim3(2 * pairs), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, args));
+    B200ML_CUDA(launch_pdl(kernel, dim3(2 * pairs), dim3(GEMM_THREADS), S::TOTAL, stream, ta, tb, tc, args));
     return check_launch("gemm_f16_pair");
+}
+
+template <int BN, bool B_MN>
+int launch_pair(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmArgs& args,
+                cudaStream_t stream) {
+    return args.tma_store ? launch_pair_impl<BN, B_MN, true>(ctx, ta, tb, tc, args, stream)
+                          : launch_pair_impl<BN, B_MN, false>(ctx, ta, tb, tc, args, stream);
 }
 
 }  // namespace
@@ -270,21 +325,33 @@ int launch_pair(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap&
 // 256 x BN tiles on CTA pairs.  BN is 256 or 128; args.tiles_m / tiles_n / num_tiles are already in
 // units of those tiles.  The B tensor map's box covers this CTA's half of the tile.
 int gemm_f16_pair(const b200ml_ctx* ctx, const b200ml_gemm_params* p, GemmArgs& args, int bn, cudaStream_t stream) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, p->batch_inner, p->a_stride_inner, p->batch_outer,
                        p->a_stride_outer, BK, BM, "A");
     if (rc) return rc;
+    // C leaves through bulk tensor stores (64 columns x 32 rows per store) when its rows are 16-byte aligned
+    // and N is a whole number of 64-column pieces; otherwise the warps store their rows themselves.
+    args.tma_store = 0;
+    tc = ta;
+    if (args.vec_ok && p->n % 64 == 0 && (p->batch_inner == 1 || p->c_stride_inner % 8 == 0) &&
+        (p->batch_outer == 1 || p->c_stride_outer % 8 == 0)) {
+        rc = make_tmap(ctx, &tc, p->c, p->n, p->m, p->ldc, p->batch_inner, p->c_stride_inner, p->batch_outer,
+                       p->c_stride_outer, 64, 32, "C");
+        if (rc) return rc;
+        args.tma_store = 1;
+    }
     if (p->b_layout == 1) {
         rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, p->batch_inner, p->b_stride_inner, p->batch_outer,
                        p->b_stride_outer, BK, bn / 2, "B");
         if (rc) return rc;
-        return bn == 256 ? launch_pair<256, false>(ctx, ta, tb, args, stream)
-                         : launch_pair<128, false>(ctx, ta, tb, args, stream);
+        return bn == 256 ? launch_pair<256, false>(ctx, ta, tb, tc, args, stream)
+                         : launch_pair<128, false>(ctx, ta, tb, tc, args, stream);
     }
     rc = make_tmap(ctx, &tb, p->b, p->n, p->k, p->ldb, p->batch_inner, p->b_stride_inner, p->batch_outer,
                    p->b_stride_outer, 64, BK, "B");
     if (rc) return rc;
-    return bn == 256 ? launch_pair<256, true>(ctx, ta, tb, args, stream) : launch_pair<128, true>(ctx, ta, tb, args, stream);
+    return bn == 256 ? launch_pair<256, true>(ctx, ta, tb, tc, args, stream)
+                     : launch_pair<128, true>(ctx, ta, tb, tc, args, stream);
 }
 
 }  // namespace b200ml

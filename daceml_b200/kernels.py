@@ -39,8 +39,9 @@ def gemm_raw(ctx, params, stream):
 
 
 def gemm(a, b, out, *, b_layout=0, a_layout=0, bias=None, residual=None, act=0, alpha=1.0, bias_scale=1.0,
-         residual_scale=1.0):
-    """out[M,N] = act(alpha * A.B + bias_scale * bias) + residual_scale * residual for 2-D operands.
+         residual_scale=1.0, ln=None):
+    """out[M,N] = act(alpha * A.B + bias_scale * bias) + residual_scale * residual for 2-D operands;
+    with ``ln=(gamma, beta, eps)`` the rows of that result are layer-normalised before they are stored.
 
     ``a`` is [M,K] (or [K,M] with ``a_layout=1``), ``b`` is [K,N] (``b_layout=0``) or [N,K]
     (``b_layout=1``); rows may be strided (last dimension contiguous)."""
@@ -65,6 +66,11 @@ def gemm(a, b, out, *, b_layout=0, a_layout=0, bias=None, residual=None, act=0, 
     p.bias = bias.data_ptr() if bias is not None else None
     if residual is not None:
         p.residual, p.ldr = residual.data_ptr(), residual.stride(0)
+    if ln is not None:
+        p.epilogue |= L.EPI_LAYERNORM
+        p.ln_gamma = ln[0].data_ptr() if ln[0] is not None else None
+        p.ln_beta = ln[1].data_ptr() if ln[1] is not None else None
+        p.ln_eps = ln[2]
     gemm_raw(ctx, p, _stream(a))
     return out
 
