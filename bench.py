@@ -53,46 +53,72 @@ def layer_params(seed):
 
 
 class ClockSampler:
-    """Samples nvidia-smi while the timed region runs (reads settings, changes nothing)."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and the clock event reasons of one GPU through NVML every few milliseconds
+    while the timed region runs (reads state, changes nothing).  ``window()`` brackets the timed region;
+    only samples taken inside it are reported."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
     def __init__(self, device_index):
-        self.idx, self.rows, self.proc = device_index, [], None
+        self.idx, self.rows, self.stop_flag, self.thread, self.h, self.nvml = device_index, [], False, None, None, None
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+        except Exception:  # no NVML: report that instead of a clock
+            self.nvml = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v for v in vis.split(",") if v.strip() != ""]
+            if self.idx < len(ids) and ids[self.idx].strip().isdigit():
+                return int(ids[self.idx])
+        return self.idx
+
+    def _loop(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                self.rows.append((time.perf_counter(), n.nvmlDeviceGetClockInfo(self.h, n.NVML_CLOCK_SM),
+                                  n.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons")
+                                  else n.nvmlDeviceGetCurrentClocksThrottleReasons(self.h),
+                                  n.nvmlDeviceGetPowerUsage(self.h) / 1000.0))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def begin(self):
+        self.t_begin = time.perf_counter()
+
+    def end(self):
+        self.t_end = time.perf_counter()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
+        if self.nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        self.stop_flag = True
+        self.thread.join(1.0)
         try:
-            self.proc.wait(2)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[1]))
-                mx = float(r[2])
-                for n, v in zip(names, r[4:8]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-            except (ValueError, IndexError):
-                continue
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+            mx = float(self.nvml.nvmlDeviceGetMaxClockInfo(self.h, self.nvml.NVML_CLOCK_SM))
+        except Exception:
+            mx = None
+        inside = [r for r in self.rows if self.t_begin is not None and self.t_begin <= r[0] <= self.t_end]
+        used = inside if inside else self.rows
+        reasons = set()
+        for r in used:
+            for bit, name in self.REASONS.items():
+                if r[2] & bit:
+                    reasons.add(name)
+        sm = [float(r[1]) for r in used]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm), "in_timed_region": bool(inside),
+                "power_w": float(np.median([r[3] for r in used])) if used else None}
 
 
 def run_reference(args, rank):
@@ -185,16 +211,16 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-timed region ----
-    bufs[0].copy_(x0)
-    warm_graph.replay()
-    if world > 1:
-        D.gather_outputs(final_buf, out=gathered)  # warms NCCL
     sampler = ClockSampler(local_rank)
-    barrier()
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+    if world > 1:
+        D.gather_outputs(final_buf, out=gathered)  # warms NCCL
     barrier()
+    bufs[0].copy_(x0)
+    warm_graph.replay()  # the W untimed steps, straight before the timed ones
+    barrier()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     timed_graph.replay()
@@ -202,6 +228,7 @@ def main():
         D.gather_outputs(final_buf, out=gathered)
     e1.record()
     barrier()
+    sampler.end()
     ms = e0.elapsed_time(e1)
     if world > 1:
         tms = torch.tensor([ms], device=dev)

@@ -366,13 +366,14 @@ int gemm_f16_simt(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream
 int gemm_f16_pair(const b200ml_ctx* ctx, const b200ml_gemm_params* p, GemmArgs& args, int bn, cudaStream_t stream);
 
 // B200ML_GEMM_PAIR=0 keeps every GEMM on the one-CTA kernel (for A/B comparisons).
-static bool pair_enabled() {
-    static const bool on = [] {
+static int pair_mode() {
+    static const int mode = [] {
         const char* e = getenv("B200ML_GEMM_PAIR");
-        return !(e && e[0] == '0');
+        return e ? atoi(e) : 1;
     }();
-    return on;
+    return mode;
 }
+static bool pair_enabled() { return pair_mode() != 0; }
 
 // Tile width.  The main loop of a 128 x 256 tile needs 48 KB per 64-deep k-block, which is what one
 // SM can pull from L2 in the time the tensor core takes; narrower tiles are load-bound, so they
@@ -428,7 +429,7 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
     // one tile per pair nothing overlaps and the one-CTA kernel, which spreads the same work over
     // twice as many independent tiles, is faster.
     const int64_t pair_tiles = ceil_div(p->m, 2 * BM) * args.tiles_n * batches;
-    if (pair_enabled() && p->m > BM && bn >= 128 && pair_tiles > ctx->sm_count / 2) {
+    if (pair_enabled() && p->m > BM && bn >= 128 && (pair_tiles > ctx->sm_count / 2 || pair_mode() == 2)) {
         args.tiles_m = (int32_t)ceil_div(p->m, 2 * BM);
         args.num_tiles = (int32_t)pair_tiles;
         return gemm_f16_pair(ctx, p, args, bn, stream);
