@@ -149,6 +149,62 @@ def run_reference(args, rank):
     print(json.dumps(out), flush=True)
 
 
+def run_hbm_kernels(args):
+    """The memory-bound kernels of the unfused BERT-large layer, each on operand sets that cycle through more than
+    the 126 MB L2, timed with CUDA events over one CUDA graph: algorithmic bytes (every operand once) / time."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the product path has no CPU fallback")
+    from daceml_b200 import kernels as K, lib as L
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    T = BATCH * SEQ
+    g = torch.Generator().manual_seed(3)
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=g).half().to(dev)
+
+    gamma, beta, bias_h, bias_f = rnd(HIDDEN), rnd(HIDDEN), rnd(HIDDEN), rnd(FFN)
+    cases = []
+    n = 4  # 4 x 134 MB of scores
+    sc = [rnd(BATCH * HEADS * SEQ, SEQ) for _ in range(n)]
+    so = [torch.empty_like(t) for t in sc]
+    cases.append(("softmax_warp_kernel", "scores [8*16*512, 512] fp16, scale 1/8", n, 2 * sc[0].numel() * 2,
+                  lambda i: K.softmax(sc[i], so[i], rows=sc[i].shape[0], cols=SEQ, scale=0.125)))
+    n = 24  # 24 x 25 MB
+    xs, rs, ys = [rnd(T, HIDDEN) for _ in range(n)], [rnd(T, HIDDEN) for _ in range(n)], [torch.empty(T, HIDDEN, dtype=torch.float16, device=dev) for _ in range(n)]
+    cases.append(("layernorm_warp_kernel", "LayerNorm(x + bias + residual) [4096, 1024] fp16", n, 3 * T * HIDDEN * 2,
+                  lambda i: K.layernorm(xs[i], ys[i], gamma=gamma, beta=beta, residual=rs[i], bias=bias_h, eps=1e-12)))
+    cases.append(("binary_fast_kernel", "residual add [4096, 1024] fp16", n, 3 * T * HIDDEN * 2,
+                  lambda i: K.binary(xs[i], rs[i], ys[i], L.BIN_ADD)))
+    n = 6  # 6 x 67 MB
+    hs, ho = [rnd(T, FFN) for _ in range(n)], [torch.empty(T, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
+    cases.append(("bias_act_kernel", "bias + GELU(erf) [4096, 4096] fp16", n, 2 * T * FFN * 2,
+                  lambda i: K.bias_act(hs[i], ho[i], bias=bias_f, act=L.EPI_GELU)))
+    reps = max(args.steps // 4, 12)
+    for name, what, nset, nbytes, fn in cases:
+        for i in range(min(nset, max(args.warmup, 3))):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for r in range(reps):
+                fn(r % nset)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        gbs = nbytes / us / 1e3
+        print(json.dumps({"kernel": name, "workload": what, "launches": reps, "us_per_launch": us, "bytes_per_launch": nbytes,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                                       "peak_kind": "STREAM-style copy, of %s" % pk["source"]},
+                          "l2": "%d operand sets cycled (%.0f MB)" % (nset, nset * nbytes / 1e6)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -156,8 +212,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=24)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--hbm-kernels", action="store_true",
+                    help="instead of the layer: time the HBM-bound kernels of the unfused graph (softmax, LayerNorm, bias+GELU, "
+                         "residual add) at the layer's shapes and print one JSON line per kernel with its bandwidth")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.hbm_kernels:
+        run_hbm_kernels(args)
+        return
 
     from daceml_b200 import distributed as D
     if args.impl == "reference":
@@ -212,7 +274,7 @@ def main():
 
     # ---- device-timed region ----
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not os.environ.get("BENCH_NO_CLOCK_SAMPLER"):
         sampler.start()
     if world > 1:
         D.gather_outputs(final_buf, out=gathered)  # warms NCCL

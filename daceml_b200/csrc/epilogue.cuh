@@ -43,8 +43,9 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return q;
 }
 
-// GELU (erf form) for fp16 outputs: Phi is evaluated through erfc(|z|) = 2^(-q(|z|)), q a fitted
-// degree-5 polynomial (|erf error| < 7e-7, no cancellation on the negative side), one MUFU.EX2.
+// GELU (erf form) for fp16 outputs.  With z = |x| / sqrt(2) and e = erfc(z) = 2^(-q(z)), q a fitted degree-5
+// polynomial (|erf error| < 7e-7, one MUFU.EX2): Phi(x) = 1 - e/2 for x >= 0 and e/2 for x < 0, hence
+// gelu(x) = max(x, 0) - |x| e / 2 - no cancellation on the negative side, no select.
 __device__ __forceinline__ float gelu_erf_fast(float x) {
     const float z = fabsf(x) * 0.70710678118654752440f;
     float q = fmaf(z, 0.0029446918051689863f, -0.02959194779396057f);
@@ -54,8 +55,7 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
     q *= z;
     float e;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-q));
-    const float phi2 = x < 0.0f ? e : 2.0f - e;
-    return (0.5f * x) * phi2;
+    return fmaf(-0.70710678118654752440f * z, e, fmaxf(x, 0.0f));  // |x| / 2 = z / sqrt(2)
 }
 
 // Activation for results that are stored as fp16: GELU through the one-MUFU form above.

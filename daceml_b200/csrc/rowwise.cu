@@ -63,69 +63,104 @@ __device__ __forceinline__ void st1(__half* p, float v) { *p = __float2half_rn(v
 template <typename T>
 __device__ __forceinline__ float softmax_exp(float d);
 template <>
-__device__ __forceinline__ float softmax_exp<__half>(float d) { return exp2f(d * 1.44269504088896340736f); }
+__device__ __forceinline__ float softmax_exp<__half>(float d) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(d * 1.44269504088896340736f));
+    return e;
+}
 template <>
 __device__ __forceinline__ float softmax_exp<float>(float d) { return expf(d); }
 
 // ---------------------------------------------------------------------------------------------
-// Softmax: one warp per row, the row held in registers (ITERS packets per lane).
+// Softmax: R rows per warp, the rows held in registers (ITERS packets per lane and row).  Short rows
+// give a lane only a few 16-byte loads; taking several rows at once keeps enough bytes in flight per SM
+// to cover the HBM latency, and interleaves the shuffle reductions of independent rows.
 // ---------------------------------------------------------------------------------------------
-template <typename T, int ITERS>
+template <typename T, int ITERS, int R>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__ x, const T* __restrict__ mask,
                                                            T* __restrict__ y, int64_t rows, int cols,
                                                            int64_t mask_row_div, float scale, int is_log) {
     constexpr int V = Vec<T>::N;
     const int lane = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const T* xr = x + row * cols;
-    const T* mr = mask ? mask + (row / mask_row_div) * cols : nullptr;
-    float v[ITERS][V];
-    float mx = -FLT_MAX;
+    const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
+    if (row0 >= rows) return;
+    float v[R][ITERS][V];
+    float mx[R];
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int c = (it * 32 + lane) * V;
-        if (c < cols) {
-            Vec<T>::load(xr + c, v[it]);
-            if (mr) {
-                float mv[V];
-                Vec<T>::load(mr + c, mv);
+    for (int r = 0; r < R; ++r) {
+        mx[r] = -FLT_MAX;
+        const int64_t row = row0 + r;
+        if (row < rows) {
+            const T* xr = x + row * cols;
 #pragma unroll
-                for (int j = 0; j < V; ++j) v[it][j] = fmaf(v[it][j], scale, mv[j]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < V; ++j) v[it][j] *= scale;
-            }
-#pragma unroll
-            for (int j = 0; j < V; ++j) mx = fmaxf(mx, v[it][j]);
-        }
-    }
-    mx = warp_max(mx);
-    float sum = 0.0f;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int c = (it * 32 + lane) * V;
-        if (c < cols) {
-#pragma unroll
-            for (int j = 0; j < V; ++j) {
-                const float d = v[it][j] - mx;
-                const float e = softmax_exp<T>(d);
-                sum += e;
-                v[it][j] = is_log ? d : e;
+            for (int it = 0; it < ITERS; ++it) {
+                const int c = (it * 32 + lane) * V;
+                if (c < cols) Vec<T>::load(xr + c, v[r][it]);
             }
         }
     }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    const float lse = logf(sum);
-    T* yr = y + row * cols;
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int c = (it * 32 + lane) * V;
-        if (c < cols) {
+    for (int r = 0; r < R; ++r) {
+        const int64_t row = row0 + r;
+        if (row < rows) {
+            const T* mr = mask ? mask + (row / mask_row_div) * cols : nullptr;
 #pragma unroll
-            for (int j = 0; j < V; ++j) v[it][j] = is_log ? v[it][j] - lse : v[it][j] * inv;
-            Vec<T>::store(yr + c, v[it]);
+            for (int it = 0; it < ITERS; ++it) {
+                const int c = (it * 32 + lane) * V;
+                if (c < cols) {
+                    if (mr) {
+                        float mv[V];
+                        Vec<T>::load(mr + c, mv);
+#pragma unroll
+                        for (int j = 0; j < V; ++j) v[r][it][j] = fmaf(v[r][it][j], scale, mv[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < V; ++j) v[r][it][j] *= scale;
+                    }
+#pragma unroll
+                    for (int j = 0; j < V; ++j) mx[r] = fmaxf(mx[r], v[r][it][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) mx[r] = warp_max(mx[r]);
+    float sum[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        sum[r] = 0.0f;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int c = (it * 32 + lane) * V;
+            if (c < cols) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    const float d = v[r][it][j] - mx[r];
+                    const float e = softmax_exp<T>(d);
+                    sum[r] += e;
+                    v[r][it][j] = is_log ? d : e;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) sum[r] = warp_sum(sum[r]);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int64_t row = row0 + r;
+        if (row < rows) {
+            const float inv = 1.0f / sum[r];
+            const float lse = logf(sum[r]);
+            T* yr = y + row * cols;
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                const int c = (it * 32 + lane) * V;
+                if (c < cols) {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) v[r][it][j] = is_log ? v[r][it][j] - lse : v[r][it][j] * inv;
+                    Vec<T>::store(yr + c, v[r][it]);
+                }
+            }
         }
     }
 }
@@ -188,16 +223,18 @@ int softmax_t(const T* x, const T* mask, T* y, int64_t rows, int64_t cols, int64
     const int64_t packets = cols / V;
     if (vec && packets <= 32 * 8) {
         const int warps = 8;
-        const int64_t blocks = ceil_div(rows, warps);
-        B200ML_REQUIRE(blocks < (1ll << 31), "softmax: too many rows");
         const int iters = (int)ceil_div(packets, 32);
-#define SM_LAUNCH(I)                                                                                          \
-    softmax_warp_kernel<T, I><<<(unsigned)blocks, warps * 32, 0, stream>>>(x, mask, y, rows, (int)cols, mask_row_div, \
-                                                                         scale, is_log)
-        if (iters <= 1) SM_LAUNCH(1);
-        else if (iters <= 2) SM_LAUNCH(2);
-        else if (iters <= 4) SM_LAUNCH(4);
-        else SM_LAUNCH(8);
+        // two rows per warp while a row fits four packets per lane: more loads in flight, still 4-5 blocks per SM
+        const int rpw = iters <= 4 ? 2 : 1;
+        const int64_t blocks = ceil_div(rows, (int64_t)warps * rpw);
+        B200ML_REQUIRE(blocks < (1ll << 31), "softmax: too many rows");
+#define SM_LAUNCH(I, R)                                                                                          \
+    softmax_warp_kernel<T, I, R><<<(unsigned)blocks, warps * 32, 0, stream>>>(x, mask, y, rows, (int)cols, mask_row_div, \
+                                                                            scale, is_log)
+        if (iters <= 1) SM_LAUNCH(1, 2);
+        else if (iters <= 2) SM_LAUNCH(2, 2);
+        else if (iters <= 4) SM_LAUNCH(4, 2);
+        else SM_LAUNCH(8, 1);
 #undef SM_LAUNCH
         return check_launch("softmax_warp");
     }
