@@ -337,8 +337,8 @@ def main():
                 "peak_kind": "sustained cuBLAS bf16, of %s" % pk["source"], "launches_timed": len(ev),
                 "avg_launch_us": gemm_ms * 1e3 / max(len(ev), 1), "flops_per_launch": gemm_flops / max(len(ev), 1),
                 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the layer's four launches, from
-                # the ncu capture summarised in profiles/bert_large_layer_kernels_full.md (14.9 / 19.0 / 17.0 / 51.4 MB)
-                "traffic": 25.6e6, "traffic_unit": "bytes per launch (ncu, mean of the 4 GEMM launches of a layer)",
+                # the ncu --set full capture of one layer summarised under profiles/ (14.8 / 18.9 / 17.0 / 51.2 MB)
+                "traffic": 25.5e6, "traffic_unit": "bytes per launch (ncu, mean of the 4 GEMM launches of a layer)",
                 "layer_frac_of_tensor_peak": value / world * LAYER_FLOPS / BATCH / 1e12 / pk["tf_sustained"]}
 
     # ---- end to end through the public API with host buffers: H2D of the step's input, layer, D2H of its output ----
