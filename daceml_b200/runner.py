@@ -12,6 +12,18 @@ from daceml_b200 import graphs
 from daceml_b200 import lib as L
 
 
+def upload_graph(graph: "torch.cuda.CUDAGraph") -> bool:
+    """``cudaGraphUpload``: moves an instantiated graph to the device ahead of its first replay, which otherwise pays
+    for the upload (about 1.6 us per kernel node).  Returns False when the CUDA Python bindings are missing."""
+    try:
+        from cuda.bindings import runtime as cudart
+        err = cudart.cudaGraphUpload(graph.raw_cuda_graph_exec(), torch.cuda.current_stream().cuda_stream)[0]
+        torch.cuda.synchronize()
+        return err == cudart.cudaError_t.cudaSuccess
+    except Exception:
+        return False
+
+
 class GraphedCall:
     """Captures ``fn()`` (kernel launches on the current stream over static buffers) in a CUDA graph."""
 
@@ -28,6 +40,7 @@ class GraphedCall:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             fn()
+        self.uploaded = upload_graph(self.graph)
 
     def __call__(self):
         self.graph.replay()
