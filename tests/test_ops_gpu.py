@@ -89,6 +89,24 @@ def test_matmul_tensor_core_shapes(dtype, m, n, k, rng):
     status_ok()
 
 
+@pytest.mark.parametrize("m, n, k", [(4000, 3072, 256), (2080, 1024, 320)])
+def test_matmul_pair_kernel_ragged_rows(m, n, k, rng):
+    """More 256-row tiles than CTA pairs, M not a multiple of the tile nor of the 32-row store boxes: the CTA-pair
+    kernel with its staged bulk stores, bias + GELU + residual in the epilogue; the tensor map clips the last rows."""
+    dtype = torch.float16
+    a, w = rng.standard_normal((m, k)).astype(np.float32), (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    bias, res = rng.standard_normal(n).astype(np.float32), rng.standard_normal((m, n)).astype(np.float32)
+    guard = torch.full((m + 64, n), 7.0, dtype=dtype, device="cuda")
+    y = guard[:m]
+    donnx.ONNXFusedMatMul(A=dev(a, dtype), B=dev(w, dtype), Bias=dev(bias, dtype), Residual=dev(res, dtype), Y=y, transB=1,
+                          activation="Gelu")
+    pre = ops.matmul(rounded(a, dtype), rounded(w, dtype).T.copy()) + rounded(bias, dtype)
+    ref = ops.gelu_chain(pre.astype(np.float32)) + rounded(res, dtype)
+    assert_close(y, ref, dtype, what=f"pair gemm {m}x{n}x{k}")
+    assert bool((guard[m:] == 7.0).all()), "rows past M were written"
+    status_ok()
+
+
 def test_gemm_golden_and_rules():
     g = gold("gemm")
     y = empty((7, 5), torch.float32)
