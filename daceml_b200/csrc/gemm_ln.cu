@@ -7,6 +7,10 @@
 // pre-normalisation row is parked in TMEM (fp32) between the two passes, so nothing is re-read from memory.
 // This removes the separate LayerNorm kernel (one read and one write of the activation) behind the
 // attention output projection and the second FFN matrix product.
+// The residual comes in the same way it goes out: once the main loop's loads are issued, the producer turns the
+// next two pipeline stages into sixteen 32-row x 64-column tiles of the residual (TMA, 128-byte swizzle), which land
+// while the last products run; each lane then reads its row's 16-byte pieces from shared memory instead of issuing
+// 16-byte loads to 32 different rows of global memory.
 // The normalised rows leave through shared memory (the pipeline stages are free by then): each epilogue
 // warp stages 32 rows x 64 columns in the 128-byte swizzle of a tensor map and one lane issues a bulk
 // tensor store; rows past M are clipped by the tensor map.
@@ -34,7 +38,8 @@ struct LnArgs {
 template <int CLUSTER, bool B_MN>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const __grid_constant__ CUtensorMap tmap_c, const LnArgs la) {
+                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_r,
+                   const LnArgs la) {
     const GemmArgs& args = la.g;
     constexpr uint32_t TMEM_COLS = LN_BN;
     constexpr uint32_t IDESC = ptx::make_idesc_f16(BM, LN_BN, 0, B_MN ? 1 : 0);
@@ -44,7 +49,8 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + LN_STAGES * LN_STAGE_BYTES);
     uint64_t* empty_bar = full_bar + LN_STAGES;
     uint64_t* tmem_full_bar = empty_bar + LN_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+    uint64_t* res_full_bar = tmem_full_bar + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_full_bar + 1);
     float* red = reinterpret_cast<float*>(smem + LN_STAGES * LN_STAGE_BYTES + 256);  // [4][128]: sum and sum of squares per column half
     float* stats = red + 4 * BM;                                                       // [2][128]: this CTA's row sum and sum of squares
 
@@ -56,11 +62,18 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int m0 = mt * BM;
     const int n0 = static_cast<int>(rank) * LN_BN;
     const int num_kb = (args.k + BK - 1) / BK;
+    const bool res_tiles = (args.epilogue & B200ML_EPI_RESIDUAL) && args.residual != nullptr;
+    // residual tile t (0..15: epilogue warp t / 2, its 64-column half t % 2) lives in the two stages after the last k-block
+    auto res_tile = [&](int t) -> uint8_t* {
+        const int sx = num_kb % LN_STAGES, sy = (num_kb + 1) % LN_STAGES;
+        return t < 12 ? smem + sx * LN_STAGE_BYTES + t * 4096 : smem + sy * LN_STAGE_BYTES + (t - 12) * 4096;
+    };
 
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
         ptx::prefetch_tensormap(&tmap_c);
+        if (res_tiles) ptx::prefetch_tensormap(&tmap_r);
     }
     if (warp == 1) {
         if (lane == 0) {
@@ -69,6 +82,7 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 ptx::mbar_init(&empty_bar[s], 1);
             }
             ptx::mbar_init(tmem_full_bar, 1);
+            ptx::mbar_init(res_full_bar, 1);
             ptx::fence_mbar_init();
         }
         __syncwarp();
@@ -105,6 +119,28 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 if (++stage == LN_STAGES) {
                     stage = 0;
                     phase ^= 1;
+                }
+            }
+            if (res_tiles) {
+                // two more turns of the ring: the stages after the last k-block take the residual tiles
+                bool ok = true;
+                for (int extra = 0; extra < 2 && ok; ++extra) {
+                    ok = ptx::mbar_wait(&empty_bar[stage], phase ^ 1);
+                    if (++stage == LN_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) {
+                    atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
+                } else {
+                    ptx::mbar_expect_tx(res_full_bar, 16 * 4096);
+#pragma unroll 1
+                    for (int t = 0; t < 16; ++t) {
+                        const int w = t >> 1;  // epilogue warp index: quarter = (w + 2) & 3, column half = w >> 2
+                        const int q = (w + 2) & 3, h = w >> 2;
+                        ptx::tma_load_4d(res_tile(t), &tmap_r, res_full_bar, n0 + h * 128 + (t & 1) * 64, m0 + q * 32, 0, 0);
+                    }
                 }
             }
         }
@@ -144,8 +180,6 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;           // columns [half * 128, half * 128 + 128) of this CTA's tile
     const int row_in_tile = quarter * 32 + lane;
-    const int row = m0 + row_in_tile;
-    const bool row_ok = row < args.m;
     const uint32_t t_base = tmem_base + half * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
     const int col_base = n0 + half * 128;
     const float inv_n = 1.0f / static_cast<float>(args.n);
@@ -160,9 +194,12 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         ptx::tc_fence_after();
         float s1 = 0.0f, s2 = 0.0f;
         if (epi_ok) {
-            const __half* r_row = args.residual ? args.residual + static_cast<int64_t>(row) * args.ldr : nullptr;
             const bool has_bias = (args.epilogue & B200ML_EPI_BIAS) && args.bias;
-            const bool has_res = (args.epilogue & B200ML_EPI_RESIDUAL) && r_row && row_ok;
+            const bool has_res = res_tiles;  // rows past M read the zeros the tensor map fills in
+            if (has_res && !ptx::mbar_wait(res_full_bar, 0)) {
+                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                epi_ok = false;
+            }
             const bool relu = (args.epilogue & B200ML_EPI_RELU) != 0;
 #pragma unroll 1
             for (int c = 0; c < 4; c += 2) {
@@ -178,8 +215,10 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         for (int g = 0; g < 4; ++g) rb[u][g] = __ldg(reinterpret_cast<const uint4*>(args.bias + col0 + g * 8));
                     }
                     if (has_res) {
+                        const uint8_t* tile_row = res_tile((warp - 2) * 2 + ((c + u) >> 1)) + lane * 128;
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) rr[u][g] = __ldg(reinterpret_cast<const uint4*>(r_row + col0 + g * 8));
+                        for (int g = 0; g < 4; ++g)
+                            rr[u][g] = *reinterpret_cast<const uint4*>(tile_row + (((((c + u) & 1) * 4 + g) ^ (lane & 7)) << 4));
                     }
                 }
                 ptx::tmem_ld_wait();
@@ -294,15 +333,15 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 }
 
 template <int CLUSTER, bool B_MN>
-int launch_ln(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const LnArgs& la,
-              int tiles_m, cudaStream_t stream) {
+int launch_ln(const b200ml_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tr,
+              const LnArgs& la, int tiles_m, cudaStream_t stream) {
     auto kernel = gemm_f16_ln_kernel<CLUSTER, B_MN>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         B200ML_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LN_SMEM));
         configured[ctx->device & 63] = true;
     }
-    B200ML_CUDA(launch_pdl(kernel, dim3(tiles_m * CLUSTER), dim3(GEMM_THREADS), LN_SMEM, stream, ta, tb, tc, la));
+    B200ML_CUDA(launch_pdl(kernel, dim3(tiles_m * CLUSTER), dim3(GEMM_THREADS), LN_SMEM, stream, ta, tb, tc, tr, la));
     return check_launch("gemm_f16_ln");
 }
 
@@ -348,21 +387,26 @@ int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaS
     if (rc) return rc;
     rc = make_tmap(ctx, &tc, p->c, p->n, p->m, p->ldc, 1, 0, 1, 0, 64, 32, "C");
     if (rc) return rc;
+    CUtensorMap tr = tc;
+    if ((p->epilogue & B200ML_EPI_RESIDUAL) && p->residual) {
+        rc = make_tmap(ctx, &tr, p->residual, p->n, p->m, p->ldr, 1, 0, 1, 0, 64, 32, "residual");
+        if (rc) return rc;
+    }
     if (p->b_layout == 1) {
         rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, 1, 0, 1, 0, BK, LN_BN, "B");
         if (rc) return rc;
         switch (la.cluster) {
-            case 1: return launch_ln<1, false>(ctx, ta, tb, tc, la, tiles_m, stream);
-            case 2: return launch_ln<2, false>(ctx, ta, tb, tc, la, tiles_m, stream);
-            default: return launch_ln<4, false>(ctx, ta, tb, tc, la, tiles_m, stream);
+            case 1: return launch_ln<1, false>(ctx, ta, tb, tc, tr, la, tiles_m, stream);
+            case 2: return launch_ln<2, false>(ctx, ta, tb, tc, tr, la, tiles_m, stream);
+            default: return launch_ln<4, false>(ctx, ta, tb, tc, tr, la, tiles_m, stream);
         }
     }
     rc = make_tmap(ctx, &tb, p->b, p->n, p->k, p->ldb, 1, 0, 1, 0, 64, BK, "B");
     if (rc) return rc;
     switch (la.cluster) {
-        case 1: return launch_ln<1, true>(ctx, ta, tb, tc, la, tiles_m, stream);
-        case 2: return launch_ln<2, true>(ctx, ta, tb, tc, la, tiles_m, stream);
-        default: return launch_ln<4, true>(ctx, ta, tb, tc, la, tiles_m, stream);
+        case 1: return launch_ln<1, true>(ctx, ta, tb, tc, tr, la, tiles_m, stream);
+        case 2: return launch_ln<2, true>(ctx, ta, tb, tc, tr, la, tiles_m, stream);
+        default: return launch_ln<4, true>(ctx, ta, tb, tc, tr, la, tiles_m, stream);
     }
 }
 
