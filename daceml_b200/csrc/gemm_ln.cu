@@ -14,7 +14,7 @@
 // The normalised rows leave through shared memory (the pipeline stages are free by then): each epilogue
 // warp stages 32 rows x 64 columns in the 128-byte swizzle of a tensor map and one lane issues a bulk
 // tensor store; rows past M are clipped by the tensor map.
-#include "gemm_common.cuh"
+#include "gemm_ln_epilogue.cuh"
 
 namespace b200ml {
 
@@ -26,14 +26,6 @@ constexpr int LN_BN = 256;
 constexpr int LN_STAGES = 4;
 constexpr int LN_STAGE_BYTES = A_TILE_BYTES + LN_BN * BK * 2;
 constexpr int LN_SMEM = LN_STAGES * LN_STAGE_BYTES + 256 /* barriers */ + 6 * BM * 4 /* row statistics */ + 1024;
-
-struct LnArgs {
-    GemmArgs g;
-    const __half* gamma;
-    const __half* beta;
-    float eps;
-    int32_t cluster;  // CTAs per cluster = N / 256
-};
 
 template <int CLUSTER, bool B_MN>
 __global__ void __cluster_dims__(CLUSTER, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
@@ -95,7 +87,6 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
 
-    bool epi_ok = true;
     if (warp == 0) {
         if (ptx::elect_one()) {
             int stage = 0;
@@ -175,151 +166,13 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
     }
 
-    // ------------------------------ epilogue: three passes over the row parked in TMEM ------------------------------
-    const bool is_epi = warp >= 2;
-    const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;           // columns [half * 128, half * 128 + 128) of this CTA's tile
-    const int row_in_tile = quarter * 32 + lane;
-    const uint32_t t_base = tmem_base + half * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int col_base = n0 + half * 128;
-    const float inv_n = 1.0f / static_cast<float>(args.n);
-    float mean = 0.0f, rstd = 0.0f;
-
-    // pass A: finish the GEMM epilogue in fp32, park the values in TMEM, accumulate the row's sum and sum of squares
-    if (is_epi) {
-        if (!ptx::mbar_wait(tmem_full_bar, 0)) {
-            if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
-            epi_ok = false;
-        }
-        ptx::tc_fence_after();
-        float s1 = 0.0f, s2 = 0.0f;
-        if (epi_ok) {
-            const bool has_bias = (args.epilogue & B200ML_EPI_BIAS) && args.bias;
-            const bool has_res = res_tiles;  // rows past M read the zeros the tensor map fills in
-            if (has_res && !ptx::mbar_wait(res_full_bar, 0)) {
-                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
-                epi_ok = false;
-            }
-            const bool relu = (args.epilogue & B200ML_EPI_RELU) != 0;
-#pragma unroll 1
-            for (int c = 0; c < 4; c += 2) {
-                uint32_t r[2][32];
-                uint4 rb[2][4], rr[2][4];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int col0 = col_base + (c + u) * 32;
-                    if (has_bias) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) rb[u][g] = __ldg(reinterpret_cast<const uint4*>(args.bias + col0 + g * 8));
-                    }
-                    if (has_res) {
-                        const uint8_t* tile_row = res_tile((warp - 2) * 2 + ((c + u) >> 1)) + lane * 128;
-#pragma unroll
-                        for (int g = 0; g < 4; ++g)
-                            rr[u][g] = *reinterpret_cast<const uint4*>(tile_row + (((((c + u) & 1) * 4 + g) ^ (lane & 7)) << 4));
-                    }
-                }
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float b[8], q[8];
-                        if (has_bias) unpack8(rb[u][g], b);
-                        if (has_res) unpack8(rr[u][g], q);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float v = args.alpha * __uint_as_float(r[u][g * 8 + j]);
-                            if (has_bias) v = fmaf(args.bias_scale, b[j], v);
-                            if (relu) v = fmaxf(v, 0.0f);
-                            if (has_res) v = fmaf(args.residual_scale, q[j], v);
-                            s1 += v;
-                            s2 = fmaf(v, v, s2);
-                            r[u][g * 8 + j] = __float_as_uint(v);
-                        }
-                    }
-                    ptx::tmem_st_32x32b_x32(t_base + (c + u) * 32, r[u]);
-                }
-            }
-            ptx::tmem_st_wait();
-        }
-        red[half * BM + row_in_tile] = s1;
-        red[(2 + half) * BM + row_in_tile] = s2;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (half == 0) {
-            stats[row_in_tile] = red[row_in_tile] + red[BM + row_in_tile];
-            stats[BM + row_in_tile] = red[2 * BM + row_in_tile] + red[3 * BM + row_in_tile];
-        }
-    }
-    __syncwarp();
-    ptx::cluster_sync_acq_rel();  // #1: every CTA's row statistics are visible
-    if (is_epi) {
-        float t1 = 0.0f, t2 = 0.0f;
-#pragma unroll
-        for (int r = 0; r < CLUSTER; ++r) {
-            t1 += ptx::ld_shared_cluster_f32(&stats[row_in_tile], r);
-            t2 += ptx::ld_shared_cluster_f32(&stats[BM + row_in_tile], r);
-        }
-        mean = t1 * inv_n;
-        // mean of squared deviations from the fp32 sums; clamped at zero against rounding
-        const float var = fmaxf(fmaf(-mean, mean, t2 * inv_n), 0.0f);
-        rstd = 1.0f / sqrtf(var + la.eps);
-        // pass B: normalise, scale, shift, store.  Every lane takes part in the (warp-collective) TMEM loads;
-        // only the global stores are guarded by the row bound.
-        if (epi_ok) {
-            // every product has finished (tmem_full), so the first pipeline stage is free to stage the output
-            uint8_t* stage_tile = smem + (warp - 2) * 4096;
-            uint8_t* stage_row = stage_tile + lane * 128;
-#pragma unroll 1
-            for (int c = 0; c < 4; c += 2) {
-                uint32_t r[2][32];
-                uint4 rg[2][4], rb[2][4];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) ptx::tmem_ld_32x32b_x32(t_base + (c + u) * 32, r[u]);
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int col0 = col_base + (c + u) * 32;
-                    if (la.gamma) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) rg[u][g] = __ldg(reinterpret_cast<const uint4*>(la.gamma + col0 + g * 8));
-                    }
-                    if (la.beta) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) rb[u][g] = __ldg(reinterpret_cast<const uint4*>(la.beta + col0 + g * 8));
-                    }
-                }
-                ptx::tmem_ld_wait();
-                if (lane == 0) ptx::tma_store_wait_read<0>();  // the previous store has read the staging tile
-                __syncwarp();
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float gm[8], bt[8], o[8];
-                        if (la.gamma) unpack8(rg[u][g], gm);
-                        if (la.beta) unpack8(rb[u][g], bt);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float v = (__uint_as_float(r[u][g * 8 + j]) - mean) * rstd;
-                            if (la.gamma) v *= gm[j];
-                            if (la.beta) v += bt[j];
-                            o[j] = v;
-                        }
-                        *reinterpret_cast<uint4*>(stage_row + (((u * 4 + g) ^ (lane & 7)) << 4)) = pack8(o);
-                    }
-                }
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::tma_store_4d(&tmap_c, stage_tile, col_base + c * 32, m0 + quarter * 32, 0, 0);
-                    ptx::tma_store_commit();
-                }
-            }
-            if (lane == 0) ptx::tma_store_wait<0>();  // the bulk stores have landed before the CTA may leave
-        }
-    }
+    ResidualTiles res;
+    res.first = smem + (num_kb % LN_STAGES) * LN_STAGE_BYTES;
+    res.second = smem + ((num_kb + 1) % LN_STAGES) * LN_STAGE_BYTES;
+    res.split = 12;
+    res.present = res_tiles;
+    // every product has finished by pass B (tmem_full), so the first pipeline stage is free to stage the output
+    layernorm_epilogue<CLUSTER, 2>(la, &tmap_c, tmem_base, smem, res, red, stats, tmem_full_bar, res_full_bar, m0, n0, 0, 1, warp, lane);
     ptx::tc_fence_before();
     __syncthreads();
     ptx::cluster_sync_acq_rel();  // #2: no CTA leaves while a peer may still read its statistics
@@ -383,15 +236,15 @@ int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaS
     la.cluster = (int32_t)(p->n / LN_BN);
     const int tiles_m = (int)ceil_div(p->m, BM);
     CUtensorMap ta, tb, tc;
-    int rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, 1, 0, 1, 0, BK, BM, "A");
-    if (rc) return rc;
-    rc = make_tmap(ctx, &tc, p->c, p->n, p->m, p->ldc, 1, 0, 1, 0, 64, 32, "C");
+    int rc = make_tmap(ctx, &tc, p->c, p->n, p->m, p->ldc, 1, 0, 1, 0, 64, 32, "C");
     if (rc) return rc;
     CUtensorMap tr = tc;
     if ((p->epilogue & B200ML_EPI_RESIDUAL) && p->residual) {
         rc = make_tmap(ctx, &tr, p->residual, p->n, p->m, p->ldr, 1, 0, 1, 0, 64, 32, "residual");
         if (rc) return rc;
     }
+    rc = make_tmap(ctx, &ta, p->a, p->k, p->m, p->lda, 1, 0, 1, 0, BK, BM, "A");
+    if (rc) return rc;
     if (p->b_layout == 1) {
         rc = make_tmap(ctx, &tb, p->b, p->k, p->n, p->ldb, 1, 0, 1, 0, BK, LN_BN, "B");
         if (rc) return rc;
