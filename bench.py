@@ -205,6 +205,90 @@ def run_hbm_kernels(args):
                           "l2": "%d operand sets cycled (%.0f MB)" % (nset, nset * nbytes / 1e6)}), flush=True)
 
 
+def run_other_configs(args):
+    """Configurations 1, 2 and 4 (fp32, parity cases of the test-suite) timed the same way as the layer: the compiled
+    graph replayed from one CUDA graph, CUDA events around it.  `bytes` = every kernel's operands and results once."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the product path has no CPU fallback")
+    from daceml_b200 import graphs
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    torch.manual_seed(0)
+    rng = np.random.default_rng(4)
+
+    def w(*shape):
+        return torch.from_numpy((rng.standard_normal(shape) * 0.05).astype(np.float32))
+
+    net = torch.nn.Sequential(torch.nn.Linear(784, 120), torch.nn.ReLU(), torch.nn.Linear(120, 32), torch.nn.ReLU(),
+                              torch.nn.Linear(32, 10), torch.nn.LogSoftmax(dim=-1))
+    mlp_p = {k: v.detach() for k, v in dict(w1=net[0].weight, b1=net[0].bias, w2=net[2].weight, b2=net[2].bias,
+                                            w3=net[4].weight, b3=net[4].bias).items()}
+    mb_p = dict(w_exp=w(144, 24, 1, 1), b_exp=w(144), w_dw=w(144, 1, 3, 3), b_dw=w(144), w_se1=w(6, 144, 1, 1), b_se1=w(6),
+                w_se2=w(144, 6, 1, 1), b_se2=w(144), w_proj=w(24, 144, 1, 1), b_proj=w(24))
+    cases = [
+        ("config 1: Conv fp32 X[32,3,64,64] W[16,3,3,3] stride 2", graphs.conv_sdfg((32, 3, 64, 64), (16, 3, 3, 3), strides=(2, 2)).compile(),
+         {"X": torch.randn(32, 3, 64, 64, device=dev), "W": torch.rand(16, 3, 3, 3, device=dev)}, "Y", (32, 16, 31, 31),
+         2 * 32 * 16 * 31 * 31 * 27),
+        ("config 2: MLP fp32 784-120-32-10 + LogSoftmax, batch 4096", graphs.mlp_sdfg(mlp_p, 4096, fused=True).compile(),
+         {"input": torch.randn(4096, 784, device=dev)}, "__return", (4096, 10), 2 * 4096 * (784 * 120 + 120 * 32 + 32 * 10)),
+        ("config 4: MBConv block fp32 [128,24,56,56], expand 144, SE 6", graphs.mbconv_sdfg(mb_p, (128, 24, 56, 56), fused=True).compile(),
+         {"input": torch.randn(128, 24, 56, 56, device=dev)}, "__return", (128, 24, 56, 56),
+         2 * 128 * 56 * 56 * (24 * 144 + 9 * 144 + 144 * 24)),
+    ]
+    reps = max(args.steps // 8, 10)
+    for name, comp, inputs, out_name, out_shape, flops in cases:
+        comp.device = dev
+        kw = dict(inputs)
+        kw[out_name] = torch.empty(out_shape, dtype=torch.float32, device=dev)
+        for _ in range(max(args.warmup, 3)):
+            comp(**kw)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                comp(**kw)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        arrays = dict(comp._transients)
+        arrays.update(comp.sdfg.constants)
+        arrays.update(kw)
+        nbytes, per_kernel = 0, []
+        for tasklet, ins, outs in comp.plan:
+            kb = 0
+            for arr in list(ins.values()) + list(outs.values()):
+                t = arrays.get(arr)
+                if t is not None:
+                    kb += t.numel() * t.element_size()
+            nbytes += kb
+            # the kernel on its own, same operands, one CUDA graph of `reps` launches
+            call = lambda: tasklet.fn({c: arrays[n] for c, n in ins.items()}, {c: arrays[n] for c, n in outs.items()})
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1):
+                for _ in range(reps):
+                    call()
+            g1.replay()
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            g1.replay()
+            a1.record()
+            torch.cuda.synchronize()
+            kus = a0.elapsed_time(a1) * 1e3 / reps
+            per_kernel.append({"kernel": "+".join(tasklet.kernels), "us": round(kus, 2), "MB": round(kb / 1e6, 2),
+                               "GB/s": round(kb / kus / 1e3, 1)})
+        print(json.dumps({"workload": name, "kernels": comp.kernel_names(), "launches_per_run": len(comp.kernel_names()),
+                          "per_kernel": per_kernel, "us_per_run": us, "samples_per_s": out_shape[0] / (us * 1e-6), "flops": flops, "tflops": flops / us / 1e6,
+                          "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / pk["hbm_gbs"],
+                          "dtype": "f32", "data": "synthetic"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,10 +299,16 @@ def main():
     ap.add_argument("--hbm-kernels", action="store_true",
                     help="instead of the layer: time the HBM-bound kernels of the unfused graph (softmax, LayerNorm, bias+GELU, "
                          "residual add) at the layer's shapes and print one JSON line per kernel with its bandwidth")
+    ap.add_argument("--other-configs", action="store_true",
+                    help="instead of the layer: time the fp32 configurations 1 (strided conv), 2 (MLP) and 4 (MBConv block) "
+                         "at their full sizes and print one JSON line each")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.hbm_kernels:
         run_hbm_kernels(args)
+        return
+    if args.other_configs:
+        run_other_configs(args)
         return
 
     from daceml_b200 import distributed as D

@@ -25,22 +25,53 @@ struct ConvGeom {
     int32_t n, c, h, w, m, kh, kw, sh, sw, pt, pl, dh, dw, group, oh, ow, act;
 };
 
+// Activation of the convolution kernels.  Swish goes through one MUFU.EX2 and one MUFU.RCP (relative error about
+// 1e-6, against the 1e-4 the fp32 configurations allow): the libm expf + division cost more instructions than the
+// nine multiply-adds of a depthwise tap.  No NaN for any finite input: exp2 saturates to +inf or 0, 1 / inf = 0.
+__device__ __forceinline__ float conv_act(float v, int act) {
+    if (act & B200ML_EPI_RELU) return fmaxf(v, 0.0f);
+    if (act & B200ML_EPI_SWISH) {
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.44269504088896340736f * v));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        return v * r;
+    }
+    if (act & B200ML_EPI_GELU) return gelu_erf(v);
+    return v;
+}
+
 // ---------------------------------------------------------------------------------------------
 // direct convolution: one thread = one output pixel x MT consecutive output channels
 // ---------------------------------------------------------------------------------------------
 constexpr int MT = 8;
 
-template <typename T>
+// K = 3: 3x3 taps known at compile time, so the nine loads of a channel are issued together instead of one
+// dependent L2 round trip per tap; K = 0: any kernel size.  The MT x (C/group) x kh x kw weights of the block's
+// output channels are staged in shared memory when they fit (WSM floats).
+constexpr int WSM = 2048;
+
+template <typename T, int K>
 __global__ void __launch_bounds__(256) conv_direct_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                           const T* __restrict__ bias, const T* __restrict__ gate,
                                                           const T* __restrict__ residual, T* __restrict__ y,
                                                           const ConvGeom g) {
+    __shared__ float wsm[WSM];
     const int cg = g.c / g.group;   // input channels per group
     const int mg = g.m / g.group;   // output channels per group
     const int mblocks = (mg + MT - 1) / MT;
     const int grp = blockIdx.y / mblocks;
     const int m0 = grp * mg + (blockIdx.y % mblocks) * MT;
     const int mend = (grp + 1) * mg;
+    const int kh = K ? K : g.kh, kw = K ? K : g.kw;
+    const int wstride = cg * kh * kw;  // weights per output channel
+    const bool w_in_smem = MT * wstride <= WSM;
+    if (w_in_smem) {
+        for (int i = threadIdx.x; i < MT * wstride; i += blockDim.x) {
+            const int t = i / wstride;
+            wsm[i] = m0 + t < mend ? ldv(w + static_cast<int64_t>(m0 + t) * wstride + (i - t * wstride)) : 0.0f;
+        }
+        __syncthreads();
+    }
     const int64_t pix = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t npix = static_cast<int64_t>(g.n) * g.oh * g.ow;
     if (pix >= npix) return;
@@ -50,22 +81,47 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T* __restrict__ 
     float acc[MT];
 #pragma unroll
     for (int t = 0; t < MT; ++t) acc[t] = (bias && m0 + t < mend) ? ldv(bias + m0 + t) : 0.0f;
-    const int64_t wstride = static_cast<int64_t>(cg) * g.kh * g.kw;
     for (int c = 0; c < cg; ++c) {
         const int ci = grp * cg + c;
         const T* xp = x + (static_cast<int64_t>(b) * g.c + ci) * g.h * g.w;
         const float gt = gate ? ldv(gate + static_cast<int64_t>(b) * g.c + ci) : 1.0f;
-        for (int i = 0; i < g.kh; ++i) {
-            const int iy = oy * g.sh - g.pt + i * g.dh;
-            if (iy < 0 || iy >= g.h) continue;
-            for (int j = 0; j < g.kw; ++j) {
-                const int ix = ox * g.sw - g.pl + j * g.dw;
-                if (ix < 0 || ix >= g.w) continue;
-                const float xv = ldv(xp + static_cast<int64_t>(iy) * g.w + ix) * gt;
-                const T* wp = w + static_cast<int64_t>(m0) * wstride + (static_cast<int64_t>(c) * g.kh + i) * g.kw + j;
+        if (K == 3) {
+            float xv[9];
 #pragma unroll
-                for (int t = 0; t < MT; ++t)
-                    if (m0 + t < mend) acc[t] = fmaf(ldv(wp + t * wstride), xv, acc[t]);
+            for (int i = 0; i < 3; ++i) {
+                const int iy = oy * g.sh - g.pt + i * g.dh;
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    const int ix = ox * g.sw - g.pl + j * g.dw;
+                    const bool in = iy >= 0 && iy < g.h && ix >= 0 && ix < g.w;
+                    xv[i * 3 + j] = in ? ldv(xp + static_cast<int64_t>(iy) * g.w + ix) * gt : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) {
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    const float wv = w_in_smem ? wsm[t * wstride + c * 9 + tap]
+                                               : (m0 + t < mend ? ldv(w + static_cast<int64_t>(m0 + t) * wstride + c * 9 + tap) : 0.0f);
+                    acc[t] = fmaf(wv, xv[tap], acc[t]);
+                }
+            }
+        } else {
+            for (int i = 0; i < kh; ++i) {
+                const int iy = oy * g.sh - g.pt + i * g.dh;
+                if (iy < 0 || iy >= g.h) continue;
+                for (int j = 0; j < kw; ++j) {
+                    const int ix = ox * g.sw - g.pl + j * g.dw;
+                    if (ix < 0 || ix >= g.w) continue;
+                    const float xv = ldv(xp + static_cast<int64_t>(iy) * g.w + ix) * gt;
+                    const int wo = (c * kh + i) * kw + j;
+#pragma unroll
+                    for (int t = 0; t < MT; ++t) {
+                        const float wv = w_in_smem ? wsm[t * wstride + wo]
+                                                   : (m0 + t < mend ? ldv(w + static_cast<int64_t>(m0 + t) * wstride + wo) : 0.0f);
+                        acc[t] = fmaf(wv, xv, acc[t]);
+                    }
+                }
             }
         }
     }
@@ -73,7 +129,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T* __restrict__ 
     for (int t = 0; t < MT; ++t) {
         if (m0 + t < mend) {
             const int64_t o = ((static_cast<int64_t>(b) * g.m + m0 + t) * g.oh + oy) * g.ow + ox;
-            float v = apply_act(acc[t], g.act);
+            float v = conv_act(acc[t], g.act);
             if (residual) v += ldv(residual + o);
             stv(y + o, v);
         }
@@ -131,8 +187,8 @@ __global__ void __launch_bounds__(128) pointwise_x_kernel(const float* __restric
                 acc.w = fmaf(ws[t], xx.w, acc.w);
             }
         }
-        acc.x = apply_act(acc.x, act), acc.y = apply_act(acc.y, act);
-        acc.z = apply_act(acc.z, act), acc.w = apply_act(acc.w, act);
+        acc.x = conv_act(acc.x, act), acc.y = conv_act(acc.y, act);
+        acc.z = conv_act(acc.z, act), acc.w = conv_act(acc.w, act);
         if (rp) {
             const float4 r = __ldg(rp + static_cast<int64_t>(mm) * p4);
             acc.x += r.x, acc.y += r.y, acc.z += r.z, acc.w += r.w;
@@ -197,7 +253,7 @@ __global__ void __launch_bounds__(128) pointwise_acc_kernel(const float* __restr
     for (int mm = 0; mm < MP; ++mm) {
         if (m0 + mm < m) {
             float4 a = acc[mm];
-            a.x = apply_act(a.x, act), a.y = apply_act(a.y, act), a.z = apply_act(a.z, act), a.w = apply_act(a.w, act);
+            if (act) a.x = conv_act(a.x, act), a.y = conv_act(a.y, act), a.z = conv_act(a.z, act), a.w = conv_act(a.w, act);
             if (rp) {
                 const float4 r = __ldg(rp + static_cast<int64_t>(m0 + mm) * p4);
                 a.x += r.x, a.y += r.y, a.z += r.z, a.w += r.w;
@@ -210,6 +266,9 @@ __global__ void __launch_bounds__(128) pointwise_acc_kernel(const float* __restr
 // ---------------------------------------------------------------------------------------------
 // depthwise convolution, stride 1: one (image, channel) plane per block
 // ---------------------------------------------------------------------------------------------
+// K = 3: the 3x3 taps are compile-time (nine registers, unrolled); K = 0: any kernel size up to 64 taps.
+// Warps walk rows and lanes walk columns, so no index needs a division.
+template <int K>
 __global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ bias, float* __restrict__ y,
                                                               float* __restrict__ pool_mean, const ConvGeom g) {
@@ -218,36 +277,61 @@ __global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __res
     __shared__ float wk[64];
     const int ch = blockIdx.x % g.c;
     const int64_t img = blockIdx.x / g.c;
-    const int ph = g.oh + g.kh - 1, pw = g.ow + g.kw - 1;  // padded plane extents actually read
+    const int kh = K ? K : g.kh, kw = K ? K : g.kw;
+    const int ph = g.oh + kh - 1, pw = g.ow + kw - 1;  // padded plane extents actually read
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* xp = x + (img * g.c + ch) * static_cast<int64_t>(g.h) * g.w;
-    for (int i = threadIdx.x; i < ph * pw; i += blockDim.x) {
-        const int py = i / pw, px = i % pw;
-        const int iy = py - g.pt, ix = px - g.pl;
-        plane[i] = (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) ? __ldg(xp + iy * g.w + ix) : 0.0f;
+    for (int py = warp; py < ph; py += 8) {
+        const int iy = py - g.pt;
+        const bool row_in = iy >= 0 && iy < g.h;
+        for (int px = lane; px < pw; px += 32) {
+            const int ix = px - g.pl;
+            plane[py * pw + px] = (row_in && ix >= 0 && ix < g.w) ? __ldg(xp + iy * g.w + ix) : 0.0f;
+        }
     }
-    if (threadIdx.x < g.kh * g.kw) wk[threadIdx.x] = __ldg(w + ch * g.kh * g.kw + threadIdx.x);
+    if (threadIdx.x < kh * kw) wk[threadIdx.x] = __ldg(w + ch * kh * kw + threadIdx.x);
     __syncthreads();
     const float b = bias ? __ldg(bias + ch) : 0.0f;
     float* yp = y + (img * g.m + ch) * static_cast<int64_t>(g.oh) * g.ow;
     float local = 0.0f;
-    for (int o = threadIdx.x; o < g.oh * g.ow; o += blockDim.x) {
-        const int oy = o / g.ow, ox = o % g.ow;
-        float acc = b;
-        for (int i = 0; i < g.kh; ++i)
-            for (int j = 0; j < g.kw; ++j) acc = fmaf(wk[i * g.kw + j], plane[(oy + i) * pw + ox + j], acc);
-        acc = apply_act(acc, g.act);
-        yp[o] = acc;
-        local += acc;
+    if (K == 3) {
+        float t[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) t[i] = wk[i];
+        for (int oy = warp; oy < g.oh; oy += 8) {
+            const float* r0 = plane + oy * pw;
+            for (int ox = lane; ox < g.ow; ox += 32) {
+                float acc = b;
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) acc = fmaf(t[i * 3 + j], r0[i * pw + ox + j], acc);
+                acc = conv_act(acc, g.act);
+                yp[oy * g.ow + ox] = acc;
+                local += acc;
+            }
+        }
+    } else {
+        for (int oy = warp; oy < g.oh; oy += 8) {
+            for (int ox = lane; ox < g.ow; ox += 32) {
+                float acc = b;
+                for (int i = 0; i < kh; ++i)
+                    for (int j = 0; j < kw; ++j) acc = fmaf(wk[i * kw + j], plane[(oy + i) * pw + ox + j], acc);
+                acc = conv_act(acc, g.act);
+                yp[oy * g.ow + ox] = acc;
+                local += acc;
+            }
+        }
     }
     if (pool_mean) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+        if (lane == 0) red[warp] = local;
         __syncthreads();
         if (threadIdx.x == 0) {
-            float t = 0.0f;
-            for (int i = 0; i < 8; ++i) t += red[i];
-            pool_mean[img * g.m + ch] = t / (g.oh * g.ow);
+            float tot = 0.0f;
+            for (int i = 0; i < 8; ++i) tot += red[i];
+            pool_mean[img * g.m + ch] = tot / (g.oh * g.ow);
         }
     }
 }
@@ -290,8 +374,13 @@ int launch_direct(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s
     const int64_t npix = static_cast<int64_t>(g.n) * g.oh * g.ow;
     const int64_t gy = static_cast<int64_t>(g.group) * ceil_div(mg, MT);
     B200ML_REQUIRE(gy <= 65535, "conv: too many output-channel blocks");
-    conv_direct_kernel<T><<<dim3((unsigned)ceil_div(npix, 256), (unsigned)gy), 256, 0, s>>>(
-        (const T*)p->x, (const T*)p->weight, (const T*)p->bias, (const T*)p->gate, (const T*)p->residual, (T*)p->y, g);
+    const dim3 grid((unsigned)ceil_div(npix, 256), (unsigned)gy);
+    if (g.kh == 3 && g.kw == 3)
+        conv_direct_kernel<T, 3><<<grid, 256, 0, s>>>((const T*)p->x, (const T*)p->weight, (const T*)p->bias, (const T*)p->gate,
+                                                      (const T*)p->residual, (T*)p->y, g);
+    else
+        conv_direct_kernel<T, 0><<<grid, 256, 0, s>>>((const T*)p->x, (const T*)p->weight, (const T*)p->bias, (const T*)p->gate,
+                                                      (const T*)p->residual, (T*)p->y, g);
     return check_launch("conv_direct");
 }
 
@@ -349,7 +438,8 @@ static int conv2d_fast(const b200ml_conv_params* p, const ConvGeom& g, cudaStrea
     if (unit && p->group == p->c && p->m == p->c && !gt && !r && p->kh * p->kw <= 64) {
         const size_t sm = (size_t)(g.oh + p->kh - 1) * (g.ow + p->kw - 1) * sizeof(float);
         if (sm <= 40 * 1024 && p->n * p->c < (1ll << 31)) {
-            depthwise_plane_kernel<<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
+            if (p->kh == 3 && p->kw == 3) depthwise_plane_kernel<3><<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
+            else depthwise_plane_kernel<0><<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
             *launched = true;
             *pooled = true;
             return check_launch("depthwise_plane");

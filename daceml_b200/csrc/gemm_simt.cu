@@ -57,7 +57,10 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(const SimtArgs<T> g
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
-    for (int k0 = 0; k0 < g.k; k0 += SBK) {
+    // The next k-block's elements are fetched into registers while the current one is being multiplied: with one
+    // 256-thread block per SM nothing else would cover the latency of the global loads.
+    float ra[4], rb[4];
+    auto fetch = [&](int k0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int mm, kk;
@@ -69,7 +72,7 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(const SimtArgs<T> g
                 kk = (tid >> 6) + 4 * i;
             }
             const int gm = m0 + mm, gk = k0 + kk;
-            As[kk][mm] = (gm < g.m && gk < g.k) ? to_f(a[gm * g.a_rs + gk * g.a_cs]) : 0.0f;
+            ra[i] = (gm < g.m && gk < g.k) ? to_f(a[gm * g.a_rs + gk * g.a_cs]) : 0.0f;
             int nn, kb;
             if (b_n_contig) {
                 nn = tid & 63;
@@ -79,9 +82,23 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(const SimtArgs<T> g
                 nn = (tid >> 4) + 16 * i;
             }
             const int gn = n0 + nn, gkb = k0 + kb;
-            Bs[kb][nn] = (gn < g.n && gkb < g.k) ? to_f(b[gkb * g.b_rs + gn * g.b_cs]) : 0.0f;
+            rb[i] = (gn < g.n && gkb < g.k) ? to_f(b[gkb * g.b_rs + gn * g.b_cs]) : 0.0f;
         }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (a_k_contig) As[tid & 15][(tid >> 4) + 16 * i] = ra[i];
+            else As[(tid >> 6) + 4 * i][tid & 63] = ra[i];
+            if (b_n_contig) Bs[(tid >> 6) + 4 * i][tid & 63] = rb[i];
+            else Bs[tid & 15][(tid >> 4) + 16 * i] = rb[i];
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < g.k; k0 += SBK) {
+        stash();
         __syncthreads();
+        if (k0 + SBK < g.k) fetch(k0 + SBK);
 #pragma unroll
         for (int kk = 0; kk < SBK; ++kk) {
             const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
