@@ -183,7 +183,14 @@ int launch_simt(const b200ml_gemm_params* p, cudaStream_t stream) {
 
 }  // namespace
 
-int gemm_f32(const b200ml_ctx*, const b200ml_gemm_params* p, cudaStream_t stream) { return launch_simt<float>(p, stream); }
+bool gemm_f32_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_gemm_params* p);
+int gemm_f32_tensor_core(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream);
+
+// Large K-major fp32 products run on the tensor cores as three TF32 passes (fp32-grade accuracy); the rest here.
+int gemm_f32(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t stream) {
+    if (gemm_f32_tensor_core_applies(ctx, p)) return gemm_f32_tensor_core(ctx, p, stream);
+    return launch_simt<float>(p, stream);
+}
 int gemm_f16_simt(const b200ml_ctx*, const b200ml_gemm_params* p, cudaStream_t stream) {
     return launch_simt<__half>(p, stream);
 }

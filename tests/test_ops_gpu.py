@@ -107,6 +107,27 @@ def test_matmul_pair_kernel_ragged_rows(m, n, k, rng):
     status_ok()
 
 
+@pytest.mark.parametrize("m, n, k", [(1000, 200, 360), (4096, 120, 784), (300, 256, 1024)])
+def test_gemm_fp32_tensor_core_path(m, n, k, rng):
+    """fp32 Gemm(transB=1) large enough for the three-pass TF32 tensor-core kernel: ragged M, N and K, bias + ReLU.
+    The result must meet the fp32 tolerance (rtol 1e-4), which a single TF32 pass would not."""
+    a, w, c = (rng.standard_normal((m, k)).astype(np.float32), (rng.standard_normal((n, k)) * 0.1).astype(np.float32),
+               rng.standard_normal(n).astype(np.float32))
+    ref = np.maximum(a.astype(np.float64) @ w.astype(np.float64).T + c, 0.0)
+    y = empty((m, n), torch.float32)
+    donnx.ONNXFusedMatMul(A=dev(a), B=dev(w), Bias=dev(c), Y=y, transB=1, activation="Relu")
+    # sums of K products cancel down to values near zero, so the operator tolerance gets the absolute floor of an
+    # fp32 dot product of this length ...
+    assert_close(y, ref, torch.float32, atol=3e-5, what=f"fp32 gemm {m}x{n}x{k}")
+    # ... and the forward error is checked against what it scales with: |error| <= 2e-6 * sum_k |a_ik| |w_jk|
+    # (the split keeps about 21 bits of each operand; a single TF32 pass would sit near 5e-4)
+    scale = np.abs(a).astype(np.float64) @ np.abs(w).astype(np.float64).T + np.abs(c)
+    ratio = (np.abs(y.cpu().numpy().astype(np.float64) - ref) / scale).max()
+    print(f"3xTF32 {m}x{n}x{k}: forward error {ratio:.2e} of sum |a||w|, max abs {np.abs(y.cpu().numpy() - ref).max():.2e}")
+    assert ratio < 2e-6, f"3xTF32 forward error {ratio:.2e} of sum |a||w|"
+    status_ok()
+
+
 def test_gemm_golden_and_rules():
     g = gold("gemm")
     y = empty((7, 5), torch.float32)
