@@ -144,10 +144,13 @@ __global__ void __launch_bounds__(128) pointwise_x_kernel(const float* __restric
                                                           const float* __restrict__ bias, const float* __restrict__ gate,
                                                           const float* __restrict__ residual, float* __restrict__ y,
                                                           int64_t total4, int p4, int c, int m, int act) {
-    extern __shared__ float wsm[];  // [m][CP], zero-padded
-    for (int i = threadIdx.x; i < m * CP; i += blockDim.x) {
+    extern __shared__ float wsm[];  // [m_part][CP], zero-padded: this block's share of the output channels
+    const int m_part = (m + gridDim.y - 1) / gridDim.y;
+    const int m_begin = blockIdx.y * m_part;
+    const int m_end = m_begin + m_part < m ? m_begin + m_part : m;
+    for (int i = threadIdx.x; i < (m_end - m_begin) * CP; i += blockDim.x) {
         const int mm = i / CP, cc = i % CP;
-        wsm[i] = cc < c ? __ldg(w + mm * c + cc) : 0.0f;
+        wsm[i] = cc < c ? __ldg(w + (m_begin + mm) * c + cc) : 0.0f;
     }
     __syncthreads();
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -170,10 +173,10 @@ __global__ void __launch_bounds__(128) pointwise_x_kernel(const float* __restric
     }
     float4* yp = reinterpret_cast<float4*>(y) + img * m * p4 + q;
     const float4* rp = residual ? reinterpret_cast<const float4*>(residual) + img * m * p4 + q : nullptr;
-    for (int mm = 0; mm < m; ++mm) {
+    for (int mm = m_begin; mm < m_end; ++mm) {
         const float b = bias ? __ldg(bias + mm) : 0.0f;
         float4 acc = make_float4(b, b, b, b);
-        const float4* wr = reinterpret_cast<const float4*>(wsm + mm * CP);
+        const float4* wr = reinterpret_cast<const float4*>(wsm + (mm - m_begin) * CP);
 #pragma unroll
         for (int c4 = 0; c4 < CP / 4; ++c4) {
             const float4 wv = wr[c4];
@@ -266,9 +269,77 @@ __global__ void __launch_bounds__(128) pointwise_acc_kernel(const float* __restr
 // ---------------------------------------------------------------------------------------------
 // depthwise convolution, stride 1: one (image, channel) plane per block
 // ---------------------------------------------------------------------------------------------
-// K = 3: the 3x3 taps are compile-time (nine registers, unrolled); K = 0: any kernel size up to 64 taps.
-// Warps walk rows and lanes walk columns, so no index needs a division.
-template <int K>
+// 3x3, unit stride and dilation, planes up to 64 pixels wide: no shared memory.  A lane owns one output column of a
+// strip of rows and slides a 3x3 window down it - three (L1-served) loads, nine multiply-adds, one store per output,
+// against the 130 instructions per output of the staged kernel below (index arithmetic and shared-memory traffic).
+__global__ void __launch_bounds__(256) depthwise3x3_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           const float* __restrict__ bias, float* __restrict__ y,
+                                                           float* __restrict__ pool_mean, const ConvGeom g) {
+    __shared__ float red[8];
+    const int ch = blockIdx.x % g.c;
+    const int64_t img = blockIdx.x / g.c;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* xp = x + (img * g.c + ch) * static_cast<int64_t>(g.h) * g.w;
+    float* yp = y + (img * g.m + ch) * static_cast<int64_t>(g.oh) * g.ow;
+    float t[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) t[i] = __ldg(w + ch * 9 + i);
+    const float b = bias ? __ldg(bias + ch) : 0.0f;
+    const int ox = lane + 32 * (warp & 1);
+    const bool col_ok = ox < g.ow;
+    const int rows_per = (g.oh + 3) >> 2;  // four strips of rows
+    const int oy0 = (warp >> 1) * rows_per;
+    const int oy1 = oy0 + rows_per < g.oh ? oy0 + rows_per : g.oh;
+    const int ix0 = ox - g.pl;
+    auto load_row = [&](int iy, float (&v)[3]) {
+        const bool row_in = col_ok && iy >= 0 && iy < g.h;
+        const float* rp = xp + static_cast<int64_t>(iy) * g.w;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const int ix = ix0 + j;
+            v[j] = (row_in && ix >= 0 && ix < g.w) ? __ldg(rp + ix) : 0.0f;
+        }
+    };
+    // four output rows per step: the twelve loads of the next four input rows are issued before the first
+    // multiply, so that each thread keeps enough bytes in flight to cover the HBM latency
+    float r[6][3];
+    load_row(oy0 - g.pt, r[0]);
+    load_row(oy0 - g.pt + 1, r[1]);
+    float local = 0.0f;
+    for (int oy = oy0; oy < oy1; oy += 4) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) load_row(oy + k - g.pt + 2, r[2 + k]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float acc = b;
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+#pragma unroll
+                for (int j = 0; j < 3; ++j) acc = fmaf(t[i * 3 + j], r[k + i][j], acc);
+            acc = conv_act(acc, g.act);
+            if (col_ok && oy + k < oy1) {
+                yp[(oy + k) * g.ow + ox] = acc;
+                local += acc;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 3; ++j) r[0][j] = r[4][j], r[1][j] = r[5][j];
+    }
+    if (pool_mean) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if (lane == 0) red[warp] = local;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float tot = 0.0f;
+            for (int i = 0; i < 8; ++i) tot += red[i];
+            pool_mean[img * g.m + ch] = tot / (g.oh * g.ow);
+        }
+    }
+}
+
+// Any kernel size up to 64 taps: the plane and its halo staged in shared memory.  Warps walk rows and lanes walk
+// columns, so no index needs a division.
 __global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ bias, float* __restrict__ y,
                                                               float* __restrict__ pool_mean, const ConvGeom g) {
@@ -277,7 +348,7 @@ __global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __res
     __shared__ float wk[64];
     const int ch = blockIdx.x % g.c;
     const int64_t img = blockIdx.x / g.c;
-    const int kh = K ? K : g.kh, kw = K ? K : g.kw;
+    const int kh = g.kh, kw = g.kw;
     const int ph = g.oh + kh - 1, pw = g.ow + kw - 1;  // padded plane extents actually read
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* xp = x + (img * g.c + ch) * static_cast<int64_t>(g.h) * g.w;
@@ -294,33 +365,14 @@ __global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __res
     const float b = bias ? __ldg(bias + ch) : 0.0f;
     float* yp = y + (img * g.m + ch) * static_cast<int64_t>(g.oh) * g.ow;
     float local = 0.0f;
-    if (K == 3) {
-        float t[9];
-#pragma unroll
-        for (int i = 0; i < 9; ++i) t[i] = wk[i];
-        for (int oy = warp; oy < g.oh; oy += 8) {
-            const float* r0 = plane + oy * pw;
-            for (int ox = lane; ox < g.ow; ox += 32) {
-                float acc = b;
-#pragma unroll
-                for (int i = 0; i < 3; ++i)
-#pragma unroll
-                    for (int j = 0; j < 3; ++j) acc = fmaf(t[i * 3 + j], r0[i * pw + ox + j], acc);
-                acc = conv_act(acc, g.act);
-                yp[oy * g.ow + ox] = acc;
-                local += acc;
-            }
-        }
-    } else {
-        for (int oy = warp; oy < g.oh; oy += 8) {
-            for (int ox = lane; ox < g.ow; ox += 32) {
-                float acc = b;
-                for (int i = 0; i < kh; ++i)
-                    for (int j = 0; j < kw; ++j) acc = fmaf(wk[i * kw + j], plane[(oy + i) * pw + ox + j], acc);
-                acc = conv_act(acc, g.act);
-                yp[oy * g.ow + ox] = acc;
-                local += acc;
-            }
+    for (int oy = warp; oy < g.oh; oy += 8) {
+        for (int ox = lane; ox < g.ow; ox += 32) {
+            float acc = b;
+            for (int i = 0; i < kh; ++i)
+                for (int j = 0; j < kw; ++j) acc = fmaf(wk[i * kw + j], plane[(oy + i) * pw + ox + j], acc);
+            acc = conv_act(acc, g.act);
+            yp[oy * g.ow + ox] = acc;
+            local += acc;
         }
     }
     if (pool_mean) {
@@ -387,7 +439,8 @@ int launch_direct(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s
 }  // namespace
 
 // Tries the specialised kernels; *launched says whether one ran, *pooled whether it also wrote the pool.
-static int conv2d_fast(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched, bool* pooled) {
+static int conv2d_fast(const b200ml_ctx* ctx, const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched,
+                       bool* pooled) {
     *launched = false;
     *pooled = false;
     if (p->dtype != B200ML_F32) return B200ML_OK;
@@ -409,12 +462,18 @@ static int conv2d_fast(const b200ml_conv_params* p, const ConvGeom& g, cudaStrea
                 const int cp = c <= 4 ? 4 : (c <= 8 ? 8 : (c <= 16 ? 16 : (c <= 24 ? 24 : 32)));
                 const size_t sm = (size_t)m * cp * sizeof(float);
                 if (sm <= 48 * 1024) {
+                    // X is small next to Y here (C <= 32): when the pixel blocks alone would leave a ragged last wave,
+                    // the output channels are shared out over blockIdx.y and X is simply read once per share
+                    const int64_t slots = static_cast<int64_t>(ctx->sm_count) * 4;
+                    const unsigned parts = 1u;  // sharing out the channels was measured: slower (145.8 vs 132.3 us for 24 -> 144)
+                    (void)slots;
+                    const dim3 gxy(gx, parts);
                     switch (cp) {
-                        case 4: pointwise_x_kernel<4><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
-                        case 8: pointwise_x_kernel<8><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
-                        case 16: pointwise_x_kernel<16><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
-                        case 24: pointwise_x_kernel<24><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
-                        default: pointwise_x_kernel<32><<<gx, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 4: pointwise_x_kernel<4><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 8: pointwise_x_kernel<8><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 16: pointwise_x_kernel<16><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        case 24: pointwise_x_kernel<24><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
+                        default: pointwise_x_kernel<32><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
                     }
                     *launched = true;
                     return check_launch("pointwise_x");
@@ -438,8 +497,8 @@ static int conv2d_fast(const b200ml_conv_params* p, const ConvGeom& g, cudaStrea
     if (unit && p->group == p->c && p->m == p->c && !gt && !r && p->kh * p->kw <= 64) {
         const size_t sm = (size_t)(g.oh + p->kh - 1) * (g.ow + p->kw - 1) * sizeof(float);
         if (sm <= 40 * 1024 && p->n * p->c < (1ll << 31)) {
-            if (p->kh == 3 && p->kw == 3) depthwise_plane_kernel<3><<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
-            else depthwise_plane_kernel<0><<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
+            if (p->kh == 3 && p->kw == 3 && g.ow <= 64) depthwise3x3_kernel<<<(unsigned)(p->n * p->c), 256, 0, s>>>(x, w, b, y, p->pool_sum, g);
+            else depthwise_plane_kernel<<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
             *launched = true;
             *pooled = true;
             return check_launch("depthwise_plane");
@@ -461,7 +520,7 @@ int conv2d(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t s) {
                (int32_t)p->kw, (int32_t)p->stride_h, (int32_t)p->stride_w, (int32_t)p->pad_top, (int32_t)p->pad_left,
                (int32_t)p->dil_h, (int32_t)p->dil_w, (int32_t)p->group, (int32_t)oh, (int32_t)ow, p->act};
     bool launched = false, pooled = false;
-    int rc = conv2d_fast(p, g, s, &launched, &pooled);
+    int rc = conv2d_fast(ctx, p, g, s, &launched, &pooled);
     if (rc) return rc;
     if (!launched) {
         rc = p->dtype == B200ML_F32 ? launch_direct<float>(p, g, s) : launch_direct<__half>(p, g, s);
