@@ -366,7 +366,7 @@ def main():
 
     # ---- device-timed region ----
     sampler = ClockSampler(local_rank)
-    if rank == 0 and not os.environ.get("BENCH_NO_CLOCK_SAMPLER"):
+    if rank == 0:
         sampler.start()
     if world > 1:
         D.gather_outputs(final_buf, out=gathered)  # warms NCCL

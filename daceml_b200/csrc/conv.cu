@@ -439,7 +439,7 @@ int launch_direct(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s
 }  // namespace
 
 // Tries the specialised kernels; *launched says whether one ran, *pooled whether it also wrote the pool.
-static int conv2d_fast(const b200ml_ctx* ctx, const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched,
+static int conv2d_fast(const b200ml_ctx*, const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched,
                        bool* pooled) {
     *launched = false;
     *pooled = false;
@@ -462,12 +462,9 @@ static int conv2d_fast(const b200ml_ctx* ctx, const b200ml_conv_params* p, const
                 const int cp = c <= 4 ? 4 : (c <= 8 ? 8 : (c <= 16 ? 16 : (c <= 24 ? 24 : 32)));
                 const size_t sm = (size_t)m * cp * sizeof(float);
                 if (sm <= 48 * 1024) {
-                    // X is small next to Y here (C <= 32): when the pixel blocks alone would leave a ragged last wave,
-                    // the output channels are shared out over blockIdx.y and X is simply read once per share
-                    const int64_t slots = static_cast<int64_t>(ctx->sm_count) * 4;
-                    const unsigned parts = 1u;  // sharing out the channels was measured: slower (145.8 vs 132.3 us for 24 -> 144)
-                    (void)slots;
-                    const dim3 gxy(gx, parts);
+                    // One share of output channels (gridDim.y == 1): sharing them out over blockIdx.y, which the kernel
+                    // supports, was measured slower (145.8 vs 132.3 us for 24 -> 144 channels at 112 x 112 x 64 images)
+                    const dim3 gxy(gx, 1u);
                     switch (cp) {
                         case 4: pointwise_x_kernel<4><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
                         case 8: pointwise_x_kernel<8><<<gxy, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;

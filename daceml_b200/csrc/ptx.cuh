@@ -108,20 +108,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return true;
 }
 
-// Same contract as mbar_wait, but polls with the non-blocking test instead of the potentially
-// suspending try_wait: for the waits on a kernel's critical path, where the wake-up latency counts.
-__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity) {
-    if (mbar_test_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t spins = 0;
-    while (!mbar_test_wait(bar, parity)) {
-        if ((++spins & 0x3ffu) == 0) {
-            if (global_timer_ns() - t0 > kWaitLimitNs) return false;
-        }
-    }
-    return true;
-}
-
 // ---------------------------------------------------------------------------------------------
 // TMA: tiled bulk tensor loads into shared memory, completion on an mbarrier.  No multicast.
 // ---------------------------------------------------------------------------------------------
