@@ -18,12 +18,13 @@ Param = namedtuple("Param", ["name", "kind"])
 
 
 class ONNXSchema:
-    def __init__(self, name, inputs, outputs, attributes=None, fused=False, doc=""):
+    def __init__(self, name, inputs, outputs, attributes=None, fused=False, host_only=False, doc=""):
         self.name = name
         self.inputs = [Param(*p) if isinstance(p, tuple) else Param(p, SINGLE) for p in inputs]
         self.outputs = [Param(*p) if isinstance(p, tuple) else Param(p, SINGLE) for p in outputs]
         self.attributes = dict(attributes or {})
         self.fused = fused
+        self.host_only = host_only
         self.doc = doc
 
     def non_variadic_inputs(self):
@@ -73,6 +74,14 @@ _S = [
     ONNXSchema("Conv", ["X", "W", ("B", OPTIONAL)], ["Y"],
                dict(auto_pad="NOTSET", dilations=None, group=1, kernel_shape=None, pads=None, strides=None)),
     ONNXSchema("GlobalAveragePool", ["X"], ["Y"]),
+    # shape arithmetic of exported graphs: always constant for statically shaped models, so these only
+    # ever run on the host inside the constant-folding pass and have no kernel
+    ONNXSchema("Shape", ["data"], ["shape"], host_only=True),
+    ONNXSchema("Gather", ["data", "indices"], ["output"], dict(axis=0), host_only=True),
+    ONNXSchema("Concat", [("inputs", VARIADIC)], ["concat_result"], dict(axis=None), host_only=True),
+    ONNXSchema("Slice", ["data", "starts", "ends", ("axes", OPTIONAL), ("steps", OPTIONAL)], ["output"], host_only=True),
+    ONNXSchema("ConstantOfShape", ["input"], ["output"], dict(value=None), host_only=True),
+    ONNXSchema("Neg", ["X"], ["Y"], host_only=True),
     # fused operators (targets of the fusion pass)
     ONNXSchema("LayerNormalization", ["X", ("Scale", OPTIONAL), ("B", OPTIONAL), ("Residual", OPTIONAL)], ["Y"],
                dict(axis=-1, epsilon=1e-5), fused=True),

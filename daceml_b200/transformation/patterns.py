@@ -177,7 +177,8 @@ def fuse_swish(sdfg, state):
 
 @_each_state
 def fuse_layernorm(sdfg, state):
-    """ReduceMean -> Sub -> Pow(2) -> ReduceMean -> Add(eps) -> Sqrt -> Div -> Mul(gamma) -> Add(beta)  =>  LayerNormalization."""
+    """ReduceMean -> Sub [-> Cast] -> Pow(2) -> ReduceMean -> Add(eps) -> Sqrt -> Div [-> Cast] -> Mul(gamma) -> Add(beta)
+    =>  LayerNormalization (statistics in fp32 whatever the storage type)."""
     count = 0
     for mean in _nodes(state, "ReduceMean"):
         x = _in(state, mean, "data")
@@ -188,6 +189,10 @@ def fuse_layernorm(sdfg, state):
         if sub is None or conn != "B" or _in(state, sub, "A") != x:
             continue
         d = _out(state, sub)
+        # half-precision exports widen the centred values for the variance: Sub -> Cast(wide) ... Div -> Cast(back)
+        cast_up, _ = _only_consumer(sdfg, state, d, "Cast")
+        if cast_up is not None:
+            d = _out(state, cast_up)
         users = _consumers(state, d)
         if len(users) != 2 or not sdfg.arrays[d].transient:
             continue
@@ -206,6 +211,12 @@ def fuse_layernorm(sdfg, state):
         if sq is None or _only_consumer(sdfg, state, _out(state, sq), "Div")[0] is not dv:
             continue
         chain, y, gamma, beta = [mean, sub, pw, var, add, sq, dv], _out(state, dv), None, None
+        if cast_up is not None:
+            cast_dn, _ = _only_consumer(sdfg, state, y, "Cast")
+            if cast_dn is None or sdfg.arrays[_out(state, cast_dn)].dtype != sdfg.arrays[x].dtype:
+                continue
+            chain += [cast_up, cast_dn]
+            y = _out(state, cast_dn)
         mul, _ = _only_consumer(sdfg, state, y, "Mul")
         if mul is not None:
             g = _other_input(state, mul, "A", "B", y)
@@ -230,7 +241,7 @@ def fuse_layernorm(sdfg, state):
 # ---------------------------------------------------------------------------------------------
 @_each_state
 def fuse_linear(sdfg, state):
-    """Transpose(W) -> MatMul -> Add(bias), MatMul -> Add(bias), MatMul alone and Gemm  =>  FusedMatMul."""
+    """Transpose(W) -> MatMul -> Add(bias), MatMul(x, W^T constant) -> Add(bias), MatMul alone and Gemm  =>  FusedMatMul."""
     count = 0
     for mm in _nodes(state, "MatMul"):
         a, b = _in(state, mm, "A"), _in(state, mm, "B")
@@ -242,6 +253,12 @@ def fuse_linear(sdfg, state):
                 and _only_consumer(sdfg, state, b)[0] is mm and _const(sdfg, _in(state, tr, "data")) is not None):
             weight, trans_b = _in(state, tr, "data"), 1
             remove.append(tr)
+        elif _const(sdfg, b) is not None:
+            # a weight stored [in, out] (the exporter folded its Transpose): keep a [out, in] copy, the K-major
+            # operand layout of the fast matrix-product kernels
+            weight, trans_b = b + "_T", 1
+            if weight not in sdfg.constants:
+                sdfg.add_constant(weight, _const(sdfg, b).t().contiguous())
         y, bias = _out(state, mm), None
         add, _ = _only_consumer(sdfg, state, y, "Add")
         if add is not None:

@@ -70,7 +70,7 @@ def expand_onnx_nodes(sdfg, predicate: Optional[Callable[[sd.Node], bool]] = Non
 
 def auto_optimize(sdfg, cuda=True, simplify=False, fold_constants=True, fuse=True):
     """ Automatically optimize ``sdfg``: fuse exported sub-graphs into the fused operators this
-        library has kernels for, then expand every ONNX node.
+        library has kernels for (after folding nodes with constant inputs), then expand every ONNX node.
 
         The reference's function of the same name folds constants, expands the nodes and picks
         fast BLAS implementations (``daceml/util/utils.py:205-235``); the fusion step takes the
@@ -78,6 +78,9 @@ def auto_optimize(sdfg, cuda=True, simplify=False, fold_constants=True, fuse=Tru
     """
     if not cuda:
         raise ValueError("daceml_b200 has no CPU path")
+    if fold_constants:
+        from daceml_b200.transformation.constant_folding import fold_constants as fold
+        fold(sdfg)
     if fuse:
         from daceml_b200.transformation import fuse_subgraphs
         fuse_subgraphs(sdfg)

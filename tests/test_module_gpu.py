@@ -1,0 +1,130 @@
+"""``DaceModule`` / ``ONNXModel`` on the B200: real ``nn.Module`` objects in, results against PyTorch.
+
+The reference's tests of the same shape are ``tests/torch/test_bert_encoder.py:11-33`` (HF BertLayer against
+PyTorch), ``tests/torch/test_conv2d.py:14-42`` and the README network; tolerances are the configured ones
+(rtol 1e-4 fp32, 2e-2 fp16)."""
+import copy
+import warnings
+
+import pytest
+import torch
+import torch.nn as nn
+
+from daceml_b200 import lib as L
+from daceml_b200.onnx.onnx_importer import ONNXModel
+from daceml_b200.torch import DaceModule, dace_module
+from conftest import assert_close
+from models import MLP, MBConv, bert_layer
+
+pytestmark = pytest.mark.gpu
+warnings.filterwarnings("ignore")
+
+
+def status_ok():
+    torch.cuda.synchronize()
+    assert L.get_context(0).device_status() == 0
+
+
+@pytest.mark.parametrize("cuda_graph", [False, True])
+def test_hf_bert_layer_through_dace_module(cuda_graph):
+    layer = bert_layer(256, 4, 512).half()
+    ref_layer = copy.deepcopy(layer).float()  # fp32 arithmetic on the fp16-rounded weights
+    torch.manual_seed(1)
+    x = torch.randn(2, 128, 256).half()
+    module = DaceModule(layer.cuda(), cuda_graph=cuda_graph)
+    y = module(x.cuda())
+    assert module.compiled_function.kernel_names() == ["gemm", "attention", "gemm_layernorm", "gemm", "gemm_layernorm"]
+    with torch.no_grad():
+        ref = ref_layer(x.float())
+    ref = ref[0] if isinstance(ref, tuple) else ref
+    assert y.dtype == torch.float16 and y.is_cuda
+    assert_close(y, ref, dtype=torch.float16, what="BertLayer")
+    # a second call with other data reuses the compiled plan
+    x2 = torch.randn(2, 128, 256).half()
+    y2 = module(x2.cuda())
+    with torch.no_grad():
+        ref2 = ref_layer(x2.float())
+    ref2 = ref2[0] if isinstance(ref2, tuple) else ref2
+    assert_close(y2, ref2, dtype=torch.float16, what="BertLayer, second call")
+    status_ok()
+
+
+def test_bert_large_layer_full_size_through_dace_module():
+    """The benchmark layer (1024 / 16 / 4096, batch 8, sequence 512) from the HF module: same launches as the
+    hand-built runner, result against PyTorch's fp16 CUDA layer within the fp16 tolerance."""
+    layer = bert_layer(1024, 16, 4096).half().cuda()
+    torch.manual_seed(2)
+    x = torch.randn(8, 512, 1024).half().cuda()
+    module = DaceModule(layer, cuda_graph=True)
+    y = module(x)
+    assert module.compiled_function.kernel_names() == ["gemm", "attention", "gemm_layernorm", "gemm", "gemm_layernorm"]
+    with torch.no_grad():
+        ref = layer.float()(x.float())
+    ref = ref[0] if isinstance(ref, tuple) else ref
+    assert_close(y, ref, dtype=torch.float16, what="BERT-large layer")
+    status_ok()
+
+
+def test_mlp_module_matches_pytorch():
+    torch.manual_seed(0)
+    net = MLP()
+    x = torch.randn(4096, 784)
+    module = DaceModule(copy.deepcopy(net).cuda())
+    y = module(x.cuda())
+    with torch.no_grad():
+        ref = net(x)
+    assert_close(y, ref, what="MLP module")
+    status_ok()
+
+
+def test_mbconv_module_matches_pytorch():
+    torch.manual_seed(0)
+    net = MBConv()
+    for p in net.parameters():
+        nn.init.normal_(p, 0.0, 0.05)
+    x = torch.randn(8, 24, 56, 56)
+    module = DaceModule(copy.deepcopy(net).cuda())
+    y = module(x.cuda())
+    assert module.compiled_function.kernel_names() == ["conv2d", "conv2d", "se_gate", "conv2d"]
+    with torch.no_grad():
+        ref = net(x)
+    assert_close(y, ref, what="MBConv module", atol=2e-5)
+    status_ok()
+
+
+def test_strided_conv_module_and_decorator():
+    torch.manual_seed(0)
+    conv = nn.Conv2d(3, 16, 3, stride=2, bias=False)
+    x = torch.randn(32, 3, 64, 64)
+    y = DaceModule(copy.deepcopy(conv).cuda())(x.cuda())
+    with torch.no_grad():
+        assert_close(y, conv(x), what="strided conv module")
+
+    @dace_module
+    class LogSqrt(nn.Module):
+        def forward(self, x):
+            return torch.sqrt(torch.log(x))
+
+    out = LogSqrt()(torch.ones(2, device="cuda"))
+    assert out.tolist() == [0.0, 0.0]
+    status_ok()
+
+
+def test_onnx_model_multiple_outputs_keywords_and_saved_transients():
+    class Two(nn.Module):
+        def forward(self, x, y):
+            s = x + y
+            return torch.relu(s).reshape(x.shape[0], -1), torch.exp(s)
+
+    a, b = torch.randn(4, 3, 5), torch.randn(4, 3, 5)
+    saved = {}
+    model = ONNXModel.from_torch("two", Two(), (a, b), save_transients=saved)
+    assert model.outputs == ["__return_0", "__return_1"] and len(model.inputs) == 2
+    r0, r1 = model(a.cuda(), **{model.inputs[1]: b.cuda()})
+    assert_close(r0, torch.relu(a + b).reshape(4, -1), what="output 0")
+    assert_close(r1, torch.exp(a + b), what="output 1")
+    assert len(saved) >= 1 and all(t.is_cuda for t in saved.values())
+    # host tensors are staged through the device
+    h0, h1 = model(a, b)
+    assert_close(h0, r0, what="host inputs")
+    status_ok()
