@@ -148,7 +148,8 @@ int b200ml_ctx_device_status(b200ml_ctx* ctx, int32_t* status) {
     B200ML_CUDA(cudaMemcpy(status, ctx->status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost));
     if (*status != 0) {
         B200ML_CUDA(cudaMemset(ctx->status_dev, 0, sizeof(int32_t)));
-        return fail(B200ML_ERR_DEVICE, "a kernel gave up a bounded wait (device status %d)", *status);
+        return fail(B200ML_ERR_DEVICE, "%s (device status %d)",
+                    *status == DEV_BAD_INDEX ? "Gather met an index outside its axis" : "a kernel gave up a bounded wait", *status);
     }
     return B200ML_OK;
 }

@@ -18,6 +18,7 @@ enum : int32_t {
     DEV_TIMEOUT_MMA = 2,       // MMA issuer gave up waiting for operands or a free accumulator
     DEV_TIMEOUT_EPILOGUE = 3,  // epilogue gave up waiting for an accumulator
     DEV_TIMEOUT_ATTN = 4,
+    DEV_BAD_INDEX = 5,  // Gather met an index outside its axis
 };
 
 struct b200ml_ctx {

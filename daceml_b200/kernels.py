@@ -176,6 +176,87 @@ def cast(x, out):
     return out
 
 
+def strided_copy(src, dst):
+    """``dst[...] = src`` for two views of the same shape (torch views carry offset and strides: ``narrow`` gives the
+    sub-ranges of Slice / Split / Concat, ``expand`` the stride-0 axes of Expand)."""
+    ctx = _ctx(dst)
+    if tuple(src.shape) != tuple(dst.shape) or src.dtype != dst.dtype:
+        raise L.B200Error(L.ERR_INVALID, f"strided_copy: {tuple(src.shape)} {src.dtype} into {tuple(dst.shape)} {dst.dtype}")
+    if src.dim() > 6:
+        raise L.Unsupported(L.ERR_UNSUPPORTED, "strided_copy: rank > 6")
+    if src.numel() == 0:
+        return dst
+    L.check(ctx.lib.b200ml_strided_copy(ctx.handle, src.element_size(), L.ptr(src), L.ptr(dst), src.dim(), _i64(src.shape),
+                                        _i64(src.stride()), _i64(dst.stride()), _stream(dst)))
+    return dst
+
+
+def gather(data, indices, out, axis=0):
+    """``out = numpy.take(data, indices, axis)`` with int64 ``indices`` of any shape."""
+    ctx = _ctx(data)
+    for t in (data, indices, out):
+        _contig(t, "gather operand")
+    if indices.dtype != torch.int64:
+        raise L.B200Error(L.ERR_INVALID, f"gather: indices must be int64, got {indices.dtype}")
+    axis %= max(data.dim(), 1)
+    outer = 1
+    for d in data.shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in data.shape[axis + 1:]:
+        inner *= d
+    if tuple(out.shape) != tuple(data.shape[:axis]) + tuple(indices.shape) + tuple(data.shape[axis + 1:]) or out.dtype != data.dtype:
+        raise L.B200Error(L.ERR_INVALID, f"gather: output is {tuple(out.shape)} {out.dtype}")
+    L.check(ctx.lib.b200ml_gather(ctx.handle, data.element_size(), L.ptr(data), L.ptr(indices), L.ptr(out), outer,
+                                  data.shape[axis], inner, indices.numel(), _stream(data)))
+    return out
+
+
+def where(condition, x, y, out):
+    """Numpy-broadcast ``out = condition ? x : y``; ``condition`` is a bool (or uint8) tensor."""
+    ctx = _ctx(out)
+    _contig(out, "where output")
+    if condition.dtype not in (torch.bool, torch.uint8) or x.dtype != out.dtype or y.dtype != out.dtype:
+        raise L.B200Error(L.ERR_INVALID, f"where: dtypes {condition.dtype}, {x.dtype}, {y.dtype} -> {out.dtype}")
+    shape = list(out.shape)
+    if len(shape) > 6 or out.element_size() not in (2, 4, 8):
+        raise L.Unsupported(L.ERR_UNSUPPORTED, "where: rank > 6 or element size not 2 / 4 / 8")
+    ce, xe, ye = condition.expand(shape), x.expand(shape), y.expand(shape)
+    L.check(ctx.lib.b200ml_where(ctx.handle, out.element_size(), L.ptr(condition), L.ptr(x), L.ptr(y), L.ptr(out), len(shape),
+                                 _i64(shape), _i64(ce.stride()), _i64(xe.stride()), _i64(ye.stride()), _stream(out)))
+    return out
+
+
+def compare(a, b, out, op):
+    """Numpy-broadcast ``out = a <op> b`` into a bool (or uint8) tensor; operands are float16, float32 or int64."""
+    ctx = _ctx(out)
+    _contig(out, "compare output")
+    if a.dtype != b.dtype or out.dtype not in (torch.bool, torch.uint8):
+        raise L.B200Error(L.ERR_INVALID, f"compare: dtypes {a.dtype}, {b.dtype} -> {out.dtype}")
+    code = L.I64 if a.dtype == torch.int64 else L.dtype_code(a.dtype)
+    shape = list(out.shape)
+    if len(shape) > 6:
+        raise L.Unsupported(L.ERR_UNSUPPORTED, "compare: rank > 6")
+    ae, be = a.expand(shape), b.expand(shape)
+    L.check(ctx.lib.b200ml_compare(ctx.handle, code, op, L.ptr(a), L.ptr(b), L.ptr(out), len(shape), _i64(shape),
+                                   _i64(ae.stride()), _i64(be.stride()), _stream(out)))
+    return out
+
+
+def maxpool2d(x, out, *, kernel, strides=(1, 1), pads=(0, 0, 0, 0)):
+    """NCHW max pooling, floor mode; ``pads`` is ONNX order (top, left, bottom, right)."""
+    ctx = _ctx(x)
+    _contig(x, "maxpool input"), _contig(out, "maxpool output")
+    n, c, h, w = x.shape
+    oh = (h + pads[0] + pads[2] - kernel[0]) // strides[0] + 1
+    ow = (w + pads[1] + pads[3] - kernel[1]) // strides[1] + 1
+    if tuple(out.shape) != (n, c, oh, ow):
+        raise L.B200Error(L.ERR_INVALID, f"maxpool2d: output is {tuple(out.shape)}, expected {(n, c, oh, ow)}")
+    L.check(ctx.lib.b200ml_maxpool2d(ctx.handle, L.dtype_code(x.dtype), L.ptr(x), L.ptr(out), n * c, h, w, kernel[0], kernel[1],
+                                     strides[0], strides[1], pads[0], pads[1], pads[2], pads[3], _stream(x)))
+    return out
+
+
 def conv2d(x, w, out, *, bias=None, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1, act=0, gate=None,
            residual=None, pool_mean=None):
     """ONNX Conv on NCHW tensors; ``pads`` is ONNX order (top, left, bottom, right)."""

@@ -17,18 +17,20 @@ LIB_PATH = os.environ.get("DACEML_B200_LIB") or os.path.join(_HERE, "lib", "libd
 
 # status codes / enums (mirrors of the header)
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
-F16, F32 = 0, 1
+F16, F32, I64 = 0, 1, 2
 EPI_BIAS, EPI_RELU, EPI_GELU, EPI_RESIDUAL, EPI_SWISH, EPI_LAYERNORM = 1, 2, 4, 8, 16, 32
 RED_SUM, RED_MEAN, RED_MAX, RED_MIN = 0, 1, 2, 3
 (UN_COPY, UN_RELU, UN_SIGMOID, UN_ERF, UN_SQRT, UN_EXP, UN_LOG, UN_TANH, UN_SWISH, UN_GELU, UN_RECIPROCAL,
  UN_LEAKYRELU, UN_AFFINE, UN_POWS, UN_SOFTPLUS, UN_CLIP, UN_NEG, UN_ABS) = range(18)
 BIN_ADD, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW, BIN_MAX, BIN_MIN = range(7)
+CMP_EQ, CMP_GT, CMP_LT, CMP_GE, CMP_LE = range(5)
 
 EXPORTED_SYMBOLS = [
     "b200ml_ctx_create", "b200ml_ctx_destroy", "b200ml_ctx_device_status", "b200ml_ctx_workspace_bytes",
     "b200ml_last_error", "b200ml_version", "b200ml_launch_count", "b200ml_gemm", "b200ml_softmax",
     "b200ml_layernorm", "b200ml_reduce", "b200ml_reduce_static", "b200ml_unary", "b200ml_binary", "b200ml_bias_act", "b200ml_transpose",
-    "b200ml_cast", "b200ml_conv2d", "b200ml_se_gate", "b200ml_attention_f16",
+    "b200ml_cast", "b200ml_conv2d", "b200ml_se_gate", "b200ml_attention_f16", "b200ml_strided_copy", "b200ml_gather",
+    "b200ml_where", "b200ml_compare", "b200ml_maxpool2d",
 ]
 
 
@@ -130,6 +132,11 @@ def load_library(path=None):
         lib.b200ml_conv2d.argtypes = [vp, ctypes.POINTER(ConvParams), vp]
         lib.b200ml_se_gate.argtypes = [vp, c_i32, vp, vp, vp, vp, vp, vp, c_i64, c_i64, c_i64, vp]
         lib.b200ml_attention_f16.argtypes = [vp, ctypes.POINTER(AttentionParams), vp]
+        lib.b200ml_strided_copy.argtypes = [vp, c_i32, vp, vp, c_i32, i64p, i64p, i64p, vp]
+        lib.b200ml_gather.argtypes = [vp, c_i32, vp, vp, vp, c_i64, c_i64, c_i64, c_i64, vp]
+        lib.b200ml_where.argtypes = [vp, c_i32, vp, vp, vp, vp, c_i32, i64p, i64p, i64p, i64p, vp]
+        lib.b200ml_compare.argtypes = [vp, c_i32, c_i32, vp, vp, vp, c_i32, i64p, i64p, i64p, vp]
+        lib.b200ml_maxpool2d.argtypes = [vp, c_i32, vp, vp, c_i64, c_i64, c_i64] + [c_i32] * 8 + [vp]
         for name in EXPORTED_SYMBOLS:
             fn = getattr(lib, name)
             if name not in ("b200ml_last_error", "b200ml_launch_count", "b200ml_ctx_workspace_bytes"):

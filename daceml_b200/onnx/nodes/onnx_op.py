@@ -270,8 +270,14 @@ def _frontend_call(cls, kwargs):
     call_args = {}
     for conn, val in itertools.chain(inputs.items(), outputs.items()):
         name = "arr_" + conn
-        g.add_array(name, val.shape, val.dtype)
-        call_args[name] = val
+        host = isinstance(val, np.ndarray) or not val.is_cuda
+        if conn in inputs and host and not torch.as_tensor(val).is_floating_point():
+            # index-like operands held on the host (Slice starts / ends, Reshape and Expand shapes, Gather indices) are
+            # values known when the node is built: constants, as an importer would bind them
+            g.add_constant(name, torch.as_tensor(val))
+        else:
+            g.add_array(name, val.shape, val.dtype)
+            call_args[name] = val
         if conn in inputs:
             st.add_edge(st.add_read(name), None, node, conn, g.make_array_memlet(name))
         else:

@@ -336,6 +336,7 @@ B200Tanh = _register_unary("Tanh", L.UN_TANH, "input", "output")
 B200Identity = _register_unary("Identity", L.UN_COPY, "input", "output")
 B200Gelu = _register_unary("Gelu", L.UN_GELU)
 B200Swish = _register_unary("Swish", L.UN_SWISH)
+B200Neg = _register_unary("Neg", L.UN_NEG)
 
 
 def _constant_value(sdfg, state, node, conn):
@@ -510,13 +511,20 @@ def _register_copy(op, i, o):
     """Reshape-like nodes copy their input into the output descriptor's shape, as the reference does."""
     def can(node, state, sdfg):
         a, b = in_desc_with_name(node, state, sdfg, i), out_desc_with_name(node, state, sdfg, o)
-        return a.dtype == b.dtype and a.dtype in FLOAT_TYPES and a.total_size() == b.total_size()
+        return a.dtype == b.dtype and a.total_size() == b.total_size() and (
+            a.dtype in FLOAT_TYPES or torch.empty((), dtype=a.dtype).element_size() in (1, 2, 4, 8))
 
     def fwd(node, state, sdfg):
-        def run(ins, outs):
-            K.unary(ins[i], outs[o], L.UN_COPY)
+        if in_desc_with_name(node, state, sdfg, i).dtype in FLOAT_TYPES:
+            def run(ins, outs):
+                K.unary(ins[i], outs[o], L.UN_COPY)
 
-        return KernelTasklet(node.label, run, kernels=("unary",))
+            return KernelTasklet(node.label, run, kernels=("unary",))
+
+        def run_bytes(ins, outs):  # index and mask tensors (int64, bool): a plain copy of the bytes
+            K.strided_copy(ins[i].reshape(-1), outs[o].reshape(-1))
+
+        return KernelTasklet(node.label, run_bytes, kernels=("strided_copy",))
 
     cls = type("B200" + op, (ONNXForward, ), dict(forward_can_be_applied=staticmethod(can), forward=staticmethod(fwd),
                                                  __doc__="{} as a flat copy.".format(op)))

@@ -74,14 +74,21 @@ _S = [
     ONNXSchema("Conv", ["X", "W", ("B", OPTIONAL)], ["Y"],
                dict(auto_pad="NOTSET", dilations=None, group=1, kernel_shape=None, pads=None, strides=None)),
     ONNXSchema("GlobalAveragePool", ["X"], ["Y"]),
-    # shape arithmetic of exported graphs: always constant for statically shaped models, so these only
-    # ever run on the host inside the constant-folding pass and have no kernel
-    ONNXSchema("Shape", ["data"], ["shape"], host_only=True),
-    ONNXSchema("Gather", ["data", "indices"], ["output"], dict(axis=0), host_only=True),
-    ONNXSchema("Concat", [("inputs", VARIADIC)], ["concat_result"], dict(axis=None), host_only=True),
-    ONNXSchema("Slice", ["data", "starts", "ends", ("axes", OPTIONAL), ("steps", OPTIONAL)], ["output"], host_only=True),
+    # data movement (one strided-copy / gather kernel each; on constant inputs they fold at build time)
+    ONNXSchema("Shape", ["data"], ["shape"]),
+    ONNXSchema("Gather", ["data", "indices"], ["output"], dict(axis=0)),
+    ONNXSchema("Concat", [("inputs", VARIADIC)], ["concat_result"], dict(axis=None)),
+    ONNXSchema("Slice", ["data", "starts", "ends", ("axes", OPTIONAL), ("steps", OPTIONAL)], ["output"]),
+    ONNXSchema("Split", ["input"], [("outputs", VARIADIC)], dict(axis=0, split=None)),
+    ONNXSchema("Expand", ["input", "shape"], ["output"]),
+    ONNXSchema("Where", ["condition", "X", "Y"], ["output"]),
+    ONNXSchema("MaxPool", ["X"], ["Y", ("Indices", OPTIONAL)],
+               dict(auto_pad="NOTSET", ceil_mode=0, dilations=None, kernel_shape=None, pads=None, storage_order=0, strides=None)),
+    _unary("Neg"),
+    ONNXSchema("Equal", ["A", "B"], ["C"]), ONNXSchema("Greater", ["A", "B"], ["C"]), ONNXSchema("Less", ["A", "B"], ["C"]),
+    ONNXSchema("GreaterOrEqual", ["A", "B"], ["C"]), ONNXSchema("LessOrEqual", ["A", "B"], ["C"]),
+    # only ever evaluated on the host by the constant-folding pass (its input is a shape)
     ONNXSchema("ConstantOfShape", ["input"], ["output"], dict(value=None), host_only=True),
-    ONNXSchema("Neg", ["X"], ["Y"], host_only=True),
     # fused operators (targets of the fusion pass)
     ONNXSchema("LayerNormalization", ["X", ("Scale", OPTIONAL), ("B", OPTIONAL), ("Residual", OPTIONAL)], ["Y"],
                dict(axis=-1, epsilon=1e-5), fused=True),

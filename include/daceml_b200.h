@@ -45,7 +45,7 @@ typedef enum {
     B200ML_ERR_WORKSPACE = -5    /* the context's scratch buffer is too small */
 } b200ml_status;
 
-typedef enum { B200ML_F16 = 0, B200ML_F32 = 1 } b200ml_dtype;
+typedef enum { B200ML_F16 = 0, B200ML_F32 = 1, B200ML_I64 = 2 /* b200ml_compare only */ } b200ml_dtype;
 
 /* ------------------------------------------------------------------------- */
 /* Context and errors                                                         */
@@ -217,6 +217,53 @@ int b200ml_transpose(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void* y
 /* Replaces Cast (pure_implementations.py:329-377) for the two floating types used here. */
 int b200ml_cast(b200ml_ctx* ctx, int32_t src_dtype, int32_t dst_dtype, const void* x, void* y,
                 int64_t n, b200ml_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* Data movement: Slice / Split / Concat / Expand, Gather, Where, MaxPool      */
+/* ------------------------------------------------------------------------- */
+
+/* y[sum_d i_d * y_strides[d]] = x[sum_d i_d * x_strides[d]] for every index i of shape (rank <= 6); strides are in
+ * elements of elem_bytes (1, 2, 4 or 8), x strides may be 0 (broadcast), and x / y already point at the first element
+ * (the caller adds a slice's offset).  One entry point for the copies the reference writes as memlet sub-ranges:
+ * Slice (pure_implementations.py:659-735, 830-904; any axes and positive steps here, axis 0 / step 1 there),
+ * Split (:781-827), Expand (:260-281; a real broadcast here, only the no-op case there) and Concat. */
+int b200ml_strided_copy(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void* y, int32_t rank,
+                        const int64_t* shape, const int64_t* x_strides, const int64_t* y_strides,
+                        b200ml_stream stream);
+
+/* numpy.take along one axis: data is [outer, axis_dim, inner], y is [outer, n_indices, inner],
+ * y[o, j, :] = data[o, indices[j], :]; negative indices count from the end.  An index outside [-axis_dim, axis_dim)
+ * writes zeros and sets the context's device status.  Replaces Gather (pure_implementations.py:949-1014). */
+int b200ml_gather(b200ml_ctx* ctx, int32_t elem_bytes, const void* data, const int64_t* indices, void* y,
+                  int64_t outer, int64_t axis_dim, int64_t inner, int64_t n_indices, b200ml_stream stream);
+
+/* out = condition ? x : y with numpy broadcasting: shape is the output shape (contiguous, rank <= 6), the strides are
+ * those of the operands in that shape (0 on broadcast axes); condition holds one byte per element.  Replaces Where
+ * (pure_implementations.py:96-98). */
+int b200ml_where(b200ml_ctx* ctx, int32_t elem_bytes, const void* condition, const void* x, const void* y, void* out,
+                 int32_t rank, const int64_t* shape, const int64_t* c_strides, const int64_t* x_strides,
+                 const int64_t* y_strides, b200ml_stream stream);
+
+typedef enum b200ml_compare_op {
+    B200ML_CMP_EQ = 0,
+    B200ML_CMP_GT = 1,
+    B200ML_CMP_LT = 2,
+    B200ML_CMP_GE = 3,
+    B200ML_CMP_LE = 4
+} b200ml_compare_op;
+
+/* out = a <op> b as one byte per element (0 / 1) with numpy broadcasting (strides as in b200ml_binary); dtype is
+ * B200ML_F16, B200ML_F32 or B200ML_I64.  Equal / Greater / Less (and the -OrEqual forms of opset 12), which produce the
+ * condition of a Where; the reference leaves these to its ONNX Runtime fallback. */
+int b200ml_compare(b200ml_ctx* ctx, int32_t dtype, int32_t op, const void* a, const void* b, void* out,
+                   int32_t rank, const int64_t* shape, const int64_t* a_strides, const int64_t* b_strides,
+                   b200ml_stream stream);
+
+/* 2-D max pooling over [planes = N*C, h, w], floor mode, no dilation; padding reads as -infinity and must be smaller
+ * than the kernel.  Replaces MaxPool (img_op_implementations.py:28-161, which has no padding). */
+int b200ml_maxpool2d(b200ml_ctx* ctx, int32_t dtype, const void* x, void* y, int64_t planes, int64_t h, int64_t w,
+                     int32_t kh, int32_t kw, int32_t stride_h, int32_t stride_w, int32_t pad_top, int32_t pad_left,
+                     int32_t pad_bottom, int32_t pad_right, b200ml_stream stream);
 
 /* ------------------------------------------------------------------------- */
 /* Convolution and squeeze-excite                                             */

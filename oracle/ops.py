@@ -215,9 +215,104 @@ def unsqueeze(x, axes):
     return out
 
 
+def shape(x):  # :907-946
+    return np.array(x.shape, dtype=np.int64)
+
+
+def gather(data, indices, axis=0):
+    """PureGather (:949-1014): "read the docs for np.take"; the output is indexed by
+    ``data.shape[:axis] + indices.shape + data.shape[axis+1:]`` and element ``[.., j.., ..]`` reads
+    ``data[.., indices[j..], ..]``.  Restated as loops over the index tensor rather than by calling np.take."""
+    data, indices = np.asarray(data), np.asarray(indices, dtype=np.int64)
+    axis %= data.ndim
+    out = np.empty(data.shape[:axis] + indices.shape + data.shape[axis + 1:], dtype=data.dtype)
+    lead = (slice(None), ) * axis
+    for j in np.ndindex(*indices.shape):
+        i = int(indices[j])
+        if i < 0:
+            i += data.shape[axis]
+        out[lead + j] = data[lead + (i, )]
+    return out
+
+
+def slice_(data, starts, ends, axes=None, steps=None):
+    """ONNX Slice-10 with constant index inputs.  The reference expansion (:659-735, 830-904) takes the
+    ``axis 0, step 1`` case, ``output = data[start:end:1, :]``, and reads an ``INT64_MAX`` end (an exporter
+    artefact) as "to the end"; this is the same rule for every axis and any positive step."""
+    axes = list(range(len(starts))) if axes is None else [int(a) % data.ndim for a in axes]
+    steps = [1] * len(starts) if steps is None else list(steps)
+    index = [slice(None)] * data.ndim
+    for s, e, a, st in zip(starts, ends, axes, steps):
+        n = data.shape[a]
+        s = max(0, min(n, int(s) + n if s < 0 else int(s)))
+        e = max(0, min(n, int(e) + n if e < 0 else int(e)))
+        index[a] = slice(s, max(s, e), int(st))
+    return np.ascontiguousarray(data[tuple(index)])
+
+
+def split(x, axis=0, sizes=None, parts=None):
+    """SplitPure (:781-827): consecutive sub-ranges of ``axis`` with the extents of the ``split`` attribute."""
+    axis %= x.ndim
+    if sizes is None:
+        sizes = [x.shape[axis] // parts] * parts
+    outs, off = [], 0
+    for n in sizes:
+        index = [slice(None)] * x.ndim
+        index[axis] = slice(off, off + n)
+        outs.append(np.ascontiguousarray(x[tuple(index)]))
+        off += n
+    return outs
+
+
+def concat(xs, axis):
+    """ONNX Concat (the inverse of Split; the reference has no pure expansion for it)."""
+    axis %= xs[0].ndim
+    out = np.empty(xs[0].shape[:axis] + (sum(x.shape[axis] for x in xs), ) + xs[0].shape[axis + 1:], dtype=xs[0].dtype)
+    off = 0
+    for x in xs:
+        index = [slice(None)] * out.ndim
+        index[axis] = slice(off, off + x.shape[axis])
+        out[tuple(index)] = x
+        off += x.shape[axis]
+    return out
+
+
+def expand(x, shape):
+    """ONNX Expand: numpy broadcasting of ``x`` against ``shape``.  PureExpand (:260-281) only takes the case
+    where nothing changes (``output[:] = input``)."""
+    return np.ascontiguousarray(np.broadcast_to(x, np.broadcast_shapes(x.shape, tuple(shape))))
+
+
+def where(condition, x, y):  # :96-98, ``output[:] = np.where(condition, X, Y)``
+    return np.where(condition, x, y).astype(np.result_type(x, y))
+
+
 # ---------------------------------------------------------------------------------------------
 # Convolution and pooling (img_op_implementations.py)
 # ---------------------------------------------------------------------------------------------
+def maxpool2d(x, kernel, strides=(1, 1), pads=(0, 0, 0, 0)):
+    """PureMaxPool2D (img_op_implementations.py:28-161): ``Y[b, c, ox, oy]`` starts at the lowest value of the type
+    and takes ``max`` over ``X[b, c, ox * stride + hx, oy * stride + hy]`` for the window.  The reference accepts no
+    padding; with ONNX padding (added here) the padded positions simply never enter the maximum."""
+    n, c, h, w = x.shape
+    kh, kw = kernel
+    oh = (h + pads[0] + pads[2] - kh) // strides[0] + 1
+    ow = (w + pads[1] + pads[3] - kw) // strides[1] + 1
+    y = np.full((n, c, oh, ow), np.finfo(x.dtype).min, dtype=x.dtype)
+    for oy in range(oh):
+        for ox in range(ow):
+            for ky in range(kh):
+                iy = oy * strides[0] - pads[0] + ky
+                if iy < 0 or iy >= h:
+                    continue
+                for kx in range(kw):
+                    ix = ox * strides[1] - pads[1] + kx
+                    if ix < 0 or ix >= w:
+                        continue
+                    y[:, :, oy, ox] = np.maximum(y[:, :, oy, ox], x[:, :, iy, ix])
+    return y
+
+
 def conv_pure_supported(x_shape, w_shape, strides, pads, dilations, group):
     """The preconditions of PureConv2D.forward_can_be_applied (img_op_implementations.py:168-214)."""
     return (len(x_shape) == 4 and len(w_shape) == 4 and group == 1 and w_shape[1] == x_shape[1]

@@ -122,3 +122,34 @@ def test_c_restatement_matches_numpy_oracle():
     p = {k: torch.from_numpy(g[k]) for k in g.files if k not in ("x", "y_fp32", "y_fp16")}
     y = cpu_baseline.CpuBertLayer(p, heads=2).forward(torch.from_numpy(g["x"]))
     np.testing.assert_allclose(y.numpy(), g["y_fp32"], rtol=1e-4, atol=1e-5)
+
+
+def test_data_movement_reference_cases():
+    # tests/pure_expansions/test_expansions.py:464-563: Shape, the two Gather examples of the ONNX operator docs, the
+    # embedding lookup and the scalar-index Gather of a BERT model -- each compared with numpy indexing, as there
+    rng = np.random.default_rng(3)
+    assert ops.shape(np.zeros((9, 5, 3))).tolist() == [9, 5, 3]
+    d = np.array([[1.0, 1.2], [2.3, 3.4], [4.5, 5.7]])
+    idx = np.array([[0, 1], [1, 2]])
+    assert np.array_equal(ops.gather(d, idx, 0), d[idx])
+    assert ops.gather(d, idx, 0).tolist() == [[[1.0, 1.2], [2.3, 3.4]], [[2.3, 3.4], [4.5, 5.7]]]
+    embs, ids = rng.random((64, 8)), rng.integers(0, 64, (8, 16))
+    assert np.array_equal(ops.gather(embs, ids, 0), embs[ids])
+    d3 = rng.random((1, 8, 32))
+    assert np.array_equal(ops.gather(d3, np.int64(5), 1), np.take(d3, 5, axis=1))
+    d2 = np.array([[1.0, 1.2, 1.9], [2.3, 3.4, 3.9], [4.5, 5.7, 5.9]])
+    assert ops.gather(d2, np.array([[0, 2]]), 1).tolist() == [[[1.0, 1.9]], [[2.3, 3.9]], [[4.5, 5.9]]]
+    # Slice as the reference expands it (axis 0, step 1, INT64_MAX end) and the general form against numpy
+    x = rng.standard_normal((6, 7, 8)).astype(np.float32)
+    assert np.array_equal(ops.slice_(x, [2], [(1 << 63) - 1], [0], [1]), x[2:])
+    assert np.array_equal(ops.slice_(x, [1, -5], [4, 100], [1, 2], [2, 3]), x[:, 1:4:2, -5::3])
+    parts = ops.split(x, 1, [3, 4])
+    assert [p.shape for p in parts] == [(6, 3, 8), (6, 4, 8)] and np.array_equal(ops.concat(parts, 1), x)
+    assert np.array_equal(ops.expand(x[:, :1], (2, 6, 7, 8)), np.broadcast_to(x[:, :1], (2, 6, 7, 8)))
+    c = rng.integers(0, 2, (6, 1, 8)).astype(bool)
+    assert np.array_equal(ops.where(c, x, np.float32(0)), np.where(c, x, 0).astype(np.float32))
+    # MaxPool against PyTorch (no padding is the reference's case; padded windows agree too)
+    img = rng.standard_normal((2, 3, 9, 8)).astype(np.float32)
+    assert np.array_equal(ops.maxpool2d(img, (2, 2), (2, 2)), F.max_pool2d(torch.from_numpy(img), 2, 2).numpy())
+    assert np.array_equal(ops.maxpool2d(img, (3, 2), (2, 1), (1, 1, 1, 1)),
+                          F.max_pool2d(torch.from_numpy(img), (3, 2), (2, 1), padding=(1, 1)).numpy())
