@@ -52,6 +52,7 @@ int bias_act(const b200ml_ctx* ctx, int dtype, const void* x, const void* bias, 
 int transpose(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int rank, const int64_t* shape,
               const int32_t* perm, cudaStream_t s);
 int cast(const b200ml_ctx* ctx, int src, int dst, const void* x, void* y, int64_t n, cudaStream_t s);
+int cast_any(const b200ml_ctx* ctx, int src, int dst, const void* x, void* y, int64_t n, cudaStream_t s);
 int conv2d(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t s);
 int se_gate(const b200ml_ctx* ctx, int dtype, const void* pooled, const void* w1, const void* b1, const void* w2,
             const void* b2, void* gate, int64_t n, int64_t c, int64_t r, cudaStream_t s);
@@ -60,18 +61,6 @@ int attention_f16(const b200ml_ctx* ctx, const b200ml_attention_params* p, cudaS
 static bool dtype_ok(int d) { return d == B200ML_F16 || d == B200ML_F32; }
 
 // Makes the context's device current for the duration of a call when it is not already.
-struct DeviceGuard {
-    int prev = -1;
-    bool switched = false;
-    explicit DeviceGuard(int dev) {
-        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) {
-            switched = cudaSetDevice(dev) == cudaSuccess;
-        }
-    }
-    ~DeviceGuard() {
-        if (switched) cudaSetDevice(prev);
-    }
-};
 
 }  // namespace b200ml
 
@@ -281,12 +270,15 @@ int b200ml_transpose(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void* y
 int b200ml_cast(b200ml_ctx* ctx, int32_t src_dtype, int32_t dst_dtype, const void* x, void* y, int64_t n,
                 b200ml_stream stream) {
     CTX_CHECK(ctx);
-    B200ML_REQUIRE(dtype_ok(src_dtype) && dtype_ok(dst_dtype), "cast: unknown dtype");
+    B200ML_REQUIRE(src_dtype >= B200ML_F16 && src_dtype <= B200ML_BOOL && dst_dtype >= B200ML_F16 && dst_dtype <= B200ML_BOOL,
+                   "cast: unknown dtype");
     B200ML_REQUIRE(n >= 0, "cast: negative extent");
     if (n == 0) return B200ML_OK;
     B200ML_REQUIRE(x && y, "cast: null tensor");
     DeviceGuard guard(ctx->device);
-    return cast(ctx, src_dtype, dst_dtype, x, y, n, static_cast<cudaStream_t>(stream));
+    if (dtype_ok(src_dtype) && dtype_ok(dst_dtype))
+        return cast(ctx, src_dtype, dst_dtype, x, y, n, static_cast<cudaStream_t>(stream));
+    return cast_any(ctx, src_dtype, dst_dtype, x, y, n, static_cast<cudaStream_t>(stream));
 }
 
 int b200ml_conv2d(b200ml_ctx* ctx, const b200ml_conv_params* p, b200ml_stream stream) {

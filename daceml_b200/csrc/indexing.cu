@@ -289,6 +289,81 @@ static int where(const b200ml_ctx* ctx, int elem_bytes, const void* cond, const 
     return check_launch("where");
 }
 
+// ---- Cast between any two of f16, f32, f64, i32, i64, u8 and bool (pure_implementations.py:329-377) -------------
+template <typename T> __device__ __forceinline__ double cast_in(T v) { return static_cast<double>(v); }
+template <> __device__ __forceinline__ double cast_in<__half>(__half v) { return static_cast<double>(__half2float(v)); }
+template <typename T> __device__ __forceinline__ long long cast_in_int(T v) { return static_cast<long long>(v); }
+template <> __device__ __forceinline__ long long cast_in_int<__half>(__half v) { return static_cast<long long>(__half2float(v)); }
+
+template <typename S> struct IsFloat { static constexpr bool value = false; };
+template <> struct IsFloat<__half> { static constexpr bool value = true; };
+template <> struct IsFloat<float> { static constexpr bool value = true; };
+template <> struct IsFloat<double> { static constexpr bool value = true; };
+
+struct BoolTag {};  // destination "bool": x != 0 as one byte
+
+template <typename D, typename S>
+__device__ __forceinline__ D cast_one(S v) {
+    if constexpr (IsFloat<D>::value) {
+        // integers go through long long so that int64 keeps every bit a double can hold; floats through double
+        if constexpr (IsFloat<S>::value) {
+            const double d = cast_in(v);
+            if constexpr (sizeof(D) == 2) return __float2half_rn(static_cast<float>(d));
+            else return static_cast<D>(d);
+        } else {
+            const long long q = static_cast<long long>(v);
+            if constexpr (sizeof(D) == 2) return __float2half_rn(static_cast<float>(q));
+            else return static_cast<D>(q);
+        }
+    } else {
+        if constexpr (IsFloat<S>::value) return static_cast<D>(cast_in_int(v));  // truncation toward zero
+        else return static_cast<D>(v);
+    }
+}
+
+template <typename S, typename D, bool TO_BOOL>
+__global__ void __launch_bounds__(256) cast_any_kernel(const S* __restrict__ x, D* __restrict__ y, uint64_t n) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const S v = x[i];
+        if constexpr (TO_BOOL) {
+            bool nz;
+            if constexpr (IsFloat<S>::value) nz = cast_in(v) != 0.0;
+            else nz = v != 0;
+            y[i] = nz ? 1 : 0;
+        } else {
+            y[i] = cast_one<D, S>(v);
+        }
+    }
+}
+
+template <typename S>
+static int cast_from(const b200ml_ctx* ctx, int dst, const S* x, void* y, uint64_t n, cudaStream_t s) {
+    const unsigned grid = grid_for(ctx, n);
+    switch (dst) {
+        case B200ML_F16: cast_any_kernel<S, __half, false><<<grid, 256, 0, s>>>(x, static_cast<__half*>(y), n); break;
+        case B200ML_F32: cast_any_kernel<S, float, false><<<grid, 256, 0, s>>>(x, static_cast<float*>(y), n); break;
+        case B200ML_F64: cast_any_kernel<S, double, false><<<grid, 256, 0, s>>>(x, static_cast<double*>(y), n); break;
+        case B200ML_I32: cast_any_kernel<S, int32_t, false><<<grid, 256, 0, s>>>(x, static_cast<int32_t*>(y), n); break;
+        case B200ML_I64: cast_any_kernel<S, long long, false><<<grid, 256, 0, s>>>(x, static_cast<long long*>(y), n); break;
+        case B200ML_U8: cast_any_kernel<S, uint8_t, false><<<grid, 256, 0, s>>>(x, static_cast<uint8_t*>(y), n); break;
+        default: cast_any_kernel<S, uint8_t, true><<<grid, 256, 0, s>>>(x, static_cast<uint8_t*>(y), n); break;
+    }
+    return check_launch("cast");
+}
+
+int cast_any(const b200ml_ctx* ctx, int src, int dst, const void* x, void* y, int64_t n, cudaStream_t s) {
+    const uint64_t un = static_cast<uint64_t>(n);
+    switch (src) {
+        case B200ML_F16: return cast_from(ctx, dst, static_cast<const __half*>(x), y, un, s);
+        case B200ML_F32: return cast_from(ctx, dst, static_cast<const float*>(x), y, un, s);
+        case B200ML_F64: return cast_from(ctx, dst, static_cast<const double*>(x), y, un, s);
+        case B200ML_I32: return cast_from(ctx, dst, static_cast<const int32_t*>(x), y, un, s);
+        case B200ML_I64: return cast_from(ctx, dst, static_cast<const long long*>(x), y, un, s);
+        default: return cast_from(ctx, dst, static_cast<const uint8_t*>(x), y, un, s);  // u8 and bool read alike
+    }
+}
+
 static int compare(const b200ml_ctx* ctx, int kind, int op, const void* a, const void* b, void* out, int rank,
                    const int64_t* shape, const int64_t* as, const int64_t* bs, cudaStream_t s) {
     CmpGeom g = {};
@@ -343,6 +418,7 @@ int b200ml_strided_copy(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void
                        (long long)shape[d]);
     }
     B200ML_REQUIRE(x && y, "strided_copy: null tensor");
+    DeviceGuard guard(ctx->device);
     return strided_copy(ctx, elem_bytes, x, y, rank, shape, x_strides, y_strides, static_cast<cudaStream_t>(stream));
 }
 
@@ -355,6 +431,7 @@ int b200ml_gather(b200ml_ctx* ctx, int32_t elem_bytes, const void* data, const i
     if (outer == 0 || inner == 0 || n_indices == 0) return B200ML_OK;
     B200ML_REQUIRE(axis_dim > 0, "gather: indices into an empty axis");
     B200ML_REQUIRE(data && indices && y, "gather: null tensor");
+    DeviceGuard guard(ctx->device);
     return gather(ctx, elem_bytes, data, indices, y, outer, axis_dim, inner, n_indices, static_cast<cudaStream_t>(stream));
 }
 
@@ -370,6 +447,7 @@ int b200ml_where(b200ml_ctx* ctx, int32_t elem_bytes, const void* condition, con
         B200ML_REQUIRE(c_strides[d] >= 0 && x_strides[d] >= 0 && y_strides[d] >= 0, "where: negative stride");
     }
     B200ML_REQUIRE(condition && x && y && out, "where: null tensor");
+    DeviceGuard guard(ctx->device);
     return where(ctx, elem_bytes, condition, x, y, out, rank, shape, c_strides, x_strides, y_strides,
                  static_cast<cudaStream_t>(stream));
 }
@@ -386,6 +464,7 @@ int b200ml_compare(b200ml_ctx* ctx, int32_t dtype, int32_t op, const void* a, co
         B200ML_REQUIRE(a_strides[d] >= 0 && b_strides[d] >= 0, "compare: negative stride");
     }
     B200ML_REQUIRE(a && b && out, "compare: null tensor");
+    DeviceGuard guard(ctx->device);
     return compare(ctx, dtype, op, a, b, out, rank, shape, a_strides, b_strides, static_cast<cudaStream_t>(stream));
 }
 
@@ -403,6 +482,7 @@ int b200ml_maxpool2d(b200ml_ctx* ctx, int32_t dtype, const void* x, void* y, int
     B200ML_REQUIRE(h + pad_top + pad_bottom >= kh && w + pad_left + pad_right >= kw, "maxpool2d: kernel larger than the padded image");
     if (planes == 0) return B200ML_OK;
     B200ML_REQUIRE(x && y, "maxpool2d: null tensor");
+    DeviceGuard guard(ctx->device);
     PoolGeom g = {(int32_t)h, (int32_t)w, (int32_t)oh, (int32_t)ow, kh, kw, stride_h, stride_w, pad_top, pad_left};
     return maxpool2d(ctx, dtype, x, y, planes, g, static_cast<cudaStream_t>(stream));
 }

@@ -171,7 +171,7 @@ def transpose(x, out, perm):
 def cast(x, out):
     ctx = _ctx(x)
     _contig(x, "cast input"), _contig(out, "cast output")
-    L.check(ctx.lib.b200ml_cast(ctx.handle, L.dtype_code(x.dtype), L.dtype_code(out.dtype), L.ptr(x), L.ptr(out),
+    L.check(ctx.lib.b200ml_cast(ctx.handle, L.cast_code(x.dtype), L.cast_code(out.dtype), L.ptr(x), L.ptr(out),
                                 x.numel(), _stream(x)))
     return out
 

@@ -17,7 +17,7 @@ LIB_PATH = os.environ.get("DACEML_B200_LIB") or os.path.join(_HERE, "lib", "libd
 
 # status codes / enums (mirrors of the header)
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
-F16, F32, I64 = 0, 1, 2
+F16, F32, I64, I32, F64, U8, BOOL = range(7)
 EPI_BIAS, EPI_RELU, EPI_GELU, EPI_RESIDUAL, EPI_SWISH, EPI_LAYERNORM = 1, 2, 4, 8, 16, 32
 RED_SUM, RED_MEAN, RED_MAX, RED_MIN = 0, 1, 2, 3
 (UN_COPY, UN_RELU, UN_SIGMOID, UN_ERF, UN_SQRT, UN_EXP, UN_LOG, UN_TANH, UN_SWISH, UN_GELU, UN_RECIPROCAL,
@@ -166,6 +166,17 @@ def dtype_code(dt):
     if dt == torch.float32:
         return F32
     raise Unsupported(ERR_UNSUPPORTED, f"dtype {dt} has no B200 kernel (float16 and float32 only)")
+
+
+CAST_CODES = {torch.float16: F16, torch.float32: F32, torch.int64: I64, torch.int32: I32, torch.float64: F64, torch.uint8: U8,
+              torch.bool: BOOL}
+
+
+def cast_code(dt):
+    """The dtype code of an operand of ``b200ml_cast`` (a wider set than the arithmetic kernels take)."""
+    if dt not in CAST_CODES:
+        raise Unsupported(ERR_UNSUPPORTED, f"dtype {dt} cannot be cast on the device")
+    return CAST_CODES[dt]
 
 
 class Context:

@@ -371,8 +371,8 @@ class B200Clip(ONNXForward):
 class B200Cast(ONNXForward):
     @staticmethod
     def forward_can_be_applied(node, state, sdfg):
-        return (in_desc_with_name(node, state, sdfg, "input").dtype in FLOAT_TYPES
-                and out_desc_with_name(node, state, sdfg, "output").dtype in FLOAT_TYPES)
+        i, o = in_desc_with_name(node, state, sdfg, "input"), out_desc_with_name(node, state, sdfg, "output")
+        return i.dtype in L.CAST_CODES and o.dtype in L.CAST_CODES and i.total_size() == o.total_size()
 
     @staticmethod
     def forward(node, state, sdfg):

@@ -368,15 +368,23 @@ def fuse_attention(sdfg, state):
         chain, mask = [sm], None
         prev = _producer(state, scores)
         if prev is not None and type(prev) is donnx.ONNXAdd and _only_consumer(sdfg, state, scores)[0] is sm:
-            # additive mask, a [B, S] constant reshaped to [B, 1, 1, S]
+            # additive mask: a [B, S] constant reshaped to [B, 1, 1, S] ...
             a, b = _in(state, prev, "A"), _in(state, prev, "B")
             cand = [t for t in (a, b) if _producer(state, t) is not None and type(_producer(state, t)) is donnx.ONNXReshape
                     and _const(sdfg, _in(state, _producer(state, t), "data")) is not None]
-            if len(cand) != 1:
-                continue
-            rs = _producer(state, cand[0])
-            mask = _in(state, rs, "data")
-            chain += [prev, rs]
+            if len(cand) == 1:
+                rs = _producer(state, cand[0])
+                mask = _in(state, rs, "data")
+                chain += [prev, rs]
+            else:
+                # a mask computed at run time (or fed in): any [B, 1, 1, S] operand of the scores' type
+                shp = sdfg.arrays[scores].shape
+                cand = [t for t in (a, b) if tuple(sdfg.arrays[t].shape) == (shp[0], 1, 1, shp[3])
+                        and sdfg.arrays[t].dtype == sdfg.arrays[scores].dtype]
+                if len(cand) != 1:
+                    continue
+                mask = cand[0]
+                chain += [prev]
             scores = a if cand[0] == b else b
             prev = _producer(state, scores)
         if prev is None or type(prev) is not donnx.ONNXMul or _only_consumer(sdfg, state, scores)[0] is None:
@@ -399,7 +407,7 @@ def fuse_attention(sdfg, state):
         rs2, _ = _only_consumer(sdfg, state, _out(state, tr), "Reshape")
         if rs2 is None or (q[2], q[3]) != (k[2], k[3]) or (q[2], q[3]) != (v[2], v[3]):
             continue
-        if mask is not None and len(sdfg.arrays[mask].shape) != 2:
+        if mask is not None and len(sdfg.arrays[mask].shape) not in (2, 4):
             continue
         out = _out(state, rs2)
         _remove(state, chain + [pv, tr, rs2] + q[1] + k[1] + v[1])

@@ -45,7 +45,16 @@ typedef enum {
     B200ML_ERR_WORKSPACE = -5    /* the context's scratch buffer is too small */
 } b200ml_status;
 
-typedef enum { B200ML_F16 = 0, B200ML_F32 = 1, B200ML_I64 = 2 /* b200ml_compare only */ } b200ml_dtype;
+typedef enum {
+    B200ML_F16 = 0,
+    B200ML_F32 = 1,
+    /* the types below are accepted by b200ml_cast (all of them) and b200ml_compare (B200ML_I64) only */
+    B200ML_I64 = 2,
+    B200ML_I32 = 3,
+    B200ML_F64 = 4,
+    B200ML_U8 = 5,
+    B200ML_BOOL = 6 /* one byte, 0 / 1; casting to it tests x != 0 */
+} b200ml_dtype;
 
 /* ------------------------------------------------------------------------- */
 /* Context and errors                                                         */
@@ -214,7 +223,8 @@ int b200ml_bias_act(b200ml_ctx* ctx, int32_t dtype, const void* x, const void* b
 int b200ml_transpose(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void* y, int32_t rank,
                      const int64_t* shape, const int32_t* perm, b200ml_stream stream);
 
-/* Replaces Cast (pure_implementations.py:329-377) for the two floating types used here. */
+/* Replaces Cast (pure_implementations.py:329-377): any pair of b200ml_dtype values; float -> integer truncates toward
+ * zero, anything -> B200ML_BOOL tests x != 0. */
 int b200ml_cast(b200ml_ctx* ctx, int32_t src_dtype, int32_t dst_dtype, const void* x, void* y,
                 int64_t n, b200ml_stream stream);
 

@@ -53,3 +53,31 @@ def bert_layer(hidden, heads, ffn, seed=0):
     cfg = BertConfig(hidden_size=hidden, num_attention_heads=heads, intermediate_size=ffn)
     cfg._attn_implementation = "eager"
     return BertLayer(cfg).eval()
+
+
+class TinyBert(nn.Module):
+    """Embeddings + HF encoder layers + pooler, with the additive attention mask computed inside the graph the way
+    BERT implementations do (``(1 - mask) * -10000`` broadcast over heads and queries).  The whole-model class of
+    ``transformers`` does not survive TorchScript tracing in this version, so the pieces are assembled here."""
+
+    def __init__(self, vocab=1000, hidden=128, heads=2, ffn=256, layers=2, max_pos=64, seed=0):
+        super().__init__()
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            from transformers import BertConfig
+            from transformers.models.bert.modeling_bert import BertLayer
+        torch.manual_seed(seed)
+        cfg = BertConfig(hidden_size=hidden, num_attention_heads=heads, intermediate_size=ffn)
+        cfg._attn_implementation = "eager"
+        self.tok, self.pos = nn.Embedding(vocab, hidden), nn.Embedding(max_pos, hidden)
+        self.norm = nn.LayerNorm(hidden, eps=1e-12)
+        self.layers = nn.ModuleList([BertLayer(cfg) for _ in range(layers)])
+        self.pooler = nn.Linear(hidden, hidden)
+
+    def forward(self, ids, mask):
+        h = self.norm(self.tok(ids) + self.pos.weight[:ids.shape[1]])
+        ext = (1.0 - mask[:, None, None, :].to(h.dtype)) * -10000.0
+        for layer in self.layers:
+            out = layer(h, attention_mask=ext)
+            h = out[0] if isinstance(out, tuple) else out
+        return h, torch.tanh(self.pooler(h[:, 0]))

@@ -213,6 +213,35 @@ def test_comparisons(dtype, rng):
     status_ok()
 
 
+CAST_TYPES = [torch.float16, torch.float32, torch.float64, torch.int32, torch.int64, torch.uint8, torch.bool]
+
+
+@pytest.mark.parametrize("src", CAST_TYPES)
+def test_cast_between_all_types(src, rng):
+    """tests/pure_expansions/test_expansions.py:85-184 (int -> float, float -> int, float -> long), widened to every
+    pair: values are small enough for every target, floats carry fractions so that truncation toward zero shows."""
+    if src == torch.bool:
+        x = rng.integers(0, 2, (37, 65)).astype(bool)
+    elif src.is_floating_point:
+        x = (rng.standard_normal((37, 65)) * 20).clip(0.0, 100.0).astype(NP[src])
+        x[0, :4] = [0.0, 0.4, 0.99, 1.5]
+    else:
+        x = rng.integers(0, 100, (37, 65)).astype({torch.int32: np.int32}.get(src, NP.get(src)))
+    for dst in CAST_TYPES:
+        np_dst = {torch.int32: np.int32, torch.bool: bool}.get(dst, NP.get(dst))
+        out = empty(x.shape, dst)
+        donnx.ONNXCast(input=dev(x), output=out, to=1)
+        same(out, x.astype(np_dst))
+    status_ok()
+
+
+def test_cast_negative_floats_truncate_toward_zero():
+    x = np.array([-2.7, -0.5, 0.5, 2.7, -100.9], dtype=np.float32)
+    out = empty(x.shape, torch.int64)
+    donnx.ONNXCast(input=dev(x), output=out, to=7)
+    assert out.tolist() == [-2, 0, 0, 2, -100]
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("shape, kernel, strides, pads", [((2, 6, 28, 28), (2, 2), (2, 2), (0, 0, 0, 0)),   # LeNet pooling
                                                            ((3, 5, 17, 23), (3, 3), (2, 2), (1, 1, 1, 1)),   # ResNet stem form, ragged
@@ -262,4 +291,28 @@ def test_embedding_graph_through_importer(rng):
         ref = net(ids)
     for g, r in zip(got, ref):
         assert torch.equal(g.cpu(), r)
+    status_ok()
+
+
+def test_tiny_bert_with_mask_through_dace_module(rng):
+    """Embeddings (Gather), position slice, LayerNorm, the run-time attention mask ((1 - mask) * -10000 broadcast over
+    heads and queries), two HF encoder layers, [CLS] Gather and the Tanh pooler, from one ``nn.Module``."""
+    import copy
+    from daceml_b200.torch import DaceModule
+    from conftest import assert_close
+    from models import TinyBert
+    net = TinyBert().half().eval()
+    ref_net = copy.deepcopy(net).float()
+    ids = torch.from_numpy(rng.integers(0, 1000, (4, 64)))
+    mask = torch.ones(4, 64, dtype=torch.int64)
+    mask[1, 40:] = 0
+    mask[3, 7:] = 0
+    module = DaceModule(net.cuda())
+    hidden, pooled = module(ids.cuda(), mask.cuda())
+    names = module.compiled_function.kernel_names()
+    assert names.count("attention") == 2 and names.count("gather") == 2 and "cast" in names
+    with torch.no_grad():
+        ref_hidden, ref_pooled = ref_net(ids, mask)
+    assert_close(hidden, ref_hidden, dtype=torch.float16, what="hidden states")
+    assert_close(pooled, ref_pooled, dtype=torch.float16, what="pooled output")
     status_ok()
