@@ -34,6 +34,8 @@ class Data:
         self.shape = tuple(int(s) for s in shape)
         self.dtype = to_torch_dtype(dtype)
         self.transient = transient
+        # name of the array whose storage this one shares (a reshape of it); the counterpart of ``dace.data.View``
+        self.view_of = None
 
     @property
     def strides(self):
@@ -158,14 +160,15 @@ class SDFGState:
     def topological_compute_nodes(self):
         """Non-access nodes ordered so that producers of an array come before its consumers."""
         compute = [n for n in self._nodes if not isinstance(n, AccessNode)]
+        root = self.parent.root_of  # a view is written by whoever writes the array it aliases
         writers = collections.defaultdict(list)
         for n in compute:
             for e in self.out_edges(n):
-                writers[e.data.data].append(n)
+                writers[root(e.data.data)].append(n)
         deps = {id(n): set() for n in compute}
         for n in compute:
             for e in self.in_edges(n):
-                for w in writers.get(e.data.data, ()):
+                for w in writers.get(root(e.data.data), ()):
                     if w is not n:
                         deps[id(n)].add(id(w))
         order, done, pending = [], set(), list(compute)
@@ -210,6 +213,14 @@ class SDFG:
         self.constants[name] = tensor
         if name not in self.arrays:
             self.add_array(name, tensor.shape, tensor.dtype)
+
+    def root_of(self, name):
+        """The array that owns the storage ``name`` refers to (``name`` itself unless it is a view)."""
+        seen = set()
+        while name in self.arrays and self.arrays[name].view_of is not None and name not in seen:
+            seen.add(name)
+            name = self.arrays[name].view_of
+        return name
 
     def add_state(self, label=None):
         st = SDFGState(self, label or f"state_{len(self._states)}")
@@ -300,8 +311,12 @@ class CompiledSDFG:
                     t = self.sdfg.constants[name] = t.to(dev).contiguous()
                 bound[name] = t
         returns = []
+        views = []
         for name, desc in self.sdfg.arrays.items():
             if name in bound:
+                continue
+            if desc.view_of is not None:
+                views.append(name)
                 continue
             if desc.transient:
                 t = self._transients.get(name)
@@ -313,6 +328,8 @@ class CompiledSDFG:
                 returns.append(name)
             else:
                 raise TypeError(f"missing argument '{name}' for SDFG '{self.sdfg.name}'")
+        for name in views:  # same storage, other shape (every tensor here is contiguous)
+            bound[name] = bound[self.sdfg.root_of(name)].view(self.sdfg.arrays[name].shape)
         for tasklet, ins, outs in self.plan:
             tasklet.fn({c: bound[a] for c, a in ins.items()}, {c: bound[a] for c, a in outs.items()})
         for host, devt in copy_back:

@@ -94,6 +94,30 @@ _EVAL = {
 }
 
 
+def _split(node, ins):
+    x = ins["input"]
+    axis = int(node.axis) % x.dim()
+    return torch.split(x, [int(n) for n in node.split] if node.split else x.shape[axis] // max(len(node.out_connectors), 1), axis)
+
+
+def _fold_split(sdfg, state, node):
+    """Split of a constant: every output becomes a constant (outputs are ``outputs__i`` in order)."""
+    x = sdfg.constants.get(P._in(state, node, "input"))
+    outs = sorted(state.out_edges(node), key=lambda e: int(e.src_conn.split("__")[1]))
+    if x is None or any(not sdfg.arrays[e.data.data].transient for e in outs):
+        return False
+    parts = _split(node, dict(input=x))
+    if len(parts) != len(outs) or any(tuple(p.shape) != tuple(sdfg.arrays[e.data.data].shape) for p, e in zip(parts, outs)):
+        return False
+    state.remove_node(node)
+    for p, e in zip(parts, outs):
+        name = e.data.data
+        dtype = sdfg.arrays[name].dtype
+        del sdfg.arrays[name]
+        sdfg.add_constant(name, p.to(dtype).contiguous())
+    return True
+
+
 def _fold_state(sdfg, state):
     count = 0
     progressed = True
@@ -103,6 +127,11 @@ def _fold_state(sdfg, state):
             if not isinstance(node, donnx.ONNXOp):
                 continue
             op = type(node).schema.name
+            if op == "Split":
+                if _fold_split(sdfg, state, node):
+                    count += 1
+                    progressed = True
+                continue
             outs = state.out_edges(node)
             if len(outs) != 1 or not sdfg.arrays[outs[0].data.data].transient:
                 continue

@@ -110,6 +110,7 @@ def prune(sdfg):
             if isinstance(n, sd.AccessNode) and n not in used:
                 state.remove_node(n)
     referenced = {e.data.data for st in sdfg.states() for e in st.edges()}
+    referenced |= {sdfg.root_of(n) for n in referenced} | {d.view_of for n, d in sdfg.arrays.items() if n in referenced and d.view_of}
     for name in [n for n, d in sdfg.arrays.items() if d.transient and n not in referenced]:
         del sdfg.arrays[name]
     for name in [n for n in sdfg.constants if n not in referenced]:
@@ -584,6 +585,39 @@ def remove_identity(sdfg, state):
         _remove(state, [ident])
         state.add_edge(prod, conn, state.add_write(y), None, sdfg.make_array_memlet(y))
         count += 1
+    return count
+
+
+@_each_state
+def alias_reshapes(sdfg, state):
+    """Reshape / Flatten / Squeeze / Unsqueeze / Identity into a transient  =>  no launch: the output becomes a view of
+    the input's storage (all arrays are contiguous, and an exported graph writes every array once); when the output is
+    a result of the model, the input becomes a view of it instead, so that its producer writes the result in place.
+    Run after the fusion patterns, which look for these nodes."""
+    count = 0
+    for op, i, o in (("Reshape", "data", "reshaped"), ("Flatten", "input", "output"), ("Squeeze", "data", "squeezed"),
+                     ("Unsqueeze", "data", "expanded"), ("Identity", "input", "output")):
+        for node in _nodes(state, op):
+            src, dst = _in(state, node, i), _out(state, node, o)
+            a, b = sdfg.arrays[src], sdfg.arrays[dst]
+            if a.dtype != b.dtype or a.total_size() != b.total_size() or src in sdfg.constants:
+                continue
+            if len([e for e in state.edges() if e.data.data == dst and isinstance(e.src, donnx.ONNXOp)]) != 1:
+                continue
+            if b.transient:
+                _remove(state, [node])
+                b.view_of = src
+            else:
+                # the reshape feeds a model output: the producer of its input writes straight into the output's storage,
+                # provided nothing else reads that storage (under any of the names that view it)
+                root = sdfg.root_of(src)
+                r = sdfg.arrays[root]
+                readers = [e.dst for e in state.edges() if isinstance(e.dst, donnx.ONNXOp) and sdfg.root_of(e.data.data) == root]
+                if not r.transient or root in sdfg.constants or _producer(state, root) is None or readers != [node]:
+                    continue
+                _remove(state, [node])
+                r.view_of = dst
+            count += 1
     return count
 
 

@@ -68,9 +68,10 @@ def expand_onnx_nodes(sdfg, predicate: Optional[Callable[[sd.Node], bool]] = Non
     expand_nodes(sdfg, (lambda n: True) if predicate is None else predicate)
 
 
-def auto_optimize(sdfg, cuda=True, simplify=False, fold_constants=True, fuse=True):
+def auto_optimize(sdfg, cuda=True, simplify=False, fold_constants=True, fuse=True, views=True):
     """ Automatically optimize ``sdfg``: fuse exported sub-graphs into the fused operators this
-        library has kernels for (after folding nodes with constant inputs), then expand every ONNX node.
+        library has kernels for (after folding nodes with constant inputs), turn the remaining reshapes
+        into views, then expand every ONNX node.
 
         The reference's function of the same name folds constants, expands the nodes and picks
         fast BLAS implementations (``daceml/util/utils.py:205-235``); the fusion step takes the
@@ -84,4 +85,7 @@ def auto_optimize(sdfg, cuda=True, simplify=False, fold_constants=True, fuse=Tru
     if fuse:
         from daceml_b200.transformation import fuse_subgraphs
         fuse_subgraphs(sdfg)
+    if views:
+        from daceml_b200.transformation.patterns import alias_reshapes
+        alias_reshapes(sdfg)
     expand_onnx_nodes(sdfg)

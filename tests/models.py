@@ -81,3 +81,20 @@ class TinyBert(nn.Module):
             out = layer(h, attention_mask=ext)
             h = out[0] if isinstance(out, tuple) else out
         return h, torch.tanh(self.pooler(h[:, 0]))
+
+
+class LeNet(nn.Module):
+    """The classic 32x32 LeNet (two 3x3 convolutions with ReLU and 2x2 max pooling, three linear layers, log-softmax):
+    the network of the reference's ``tests/torch/test_lenet.py``."""
+
+    def __init__(self):
+        super().__init__()
+        self.conv1, self.conv2 = nn.Conv2d(1, 6, 3), nn.Conv2d(6, 16, 3)
+        self.fc1, self.fc2, self.fc3 = nn.Linear(16 * 6 * 6, 120), nn.Linear(120, 84), nn.Linear(84, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.conv1(x)), 2)
+        x = F.max_pool2d(F.relu(self.conv2(x)), 2)
+        x = x.view(-1, 16 * 6 * 6)
+        x = F.relu(self.fc2(F.relu(self.fc1(x))))
+        return F.log_softmax(self.fc3(x), dim=1)

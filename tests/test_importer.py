@@ -12,7 +12,7 @@ from daceml_b200.onnx.exported_graph import ExportedGraph, GraphNode, ValueInfo,
 from daceml_b200.onnx.onnx_importer import ONNXModel
 from daceml_b200.torch import DaceModule, dace_module
 from daceml_b200.transformation.constant_folding import fold_constants
-from models import MLP, MBConv, bert_layer
+from models import LeNet, MLP, MBConv, bert_layer
 
 warnings.filterwarnings("ignore")
 
@@ -90,6 +90,29 @@ def test_module_argument_checks_and_hooks():
 def test_debug_transients_become_outputs():
     m = DaceModule(MLP(), dummy_inputs=(torch.randn(8, 784), ), auto_optimize=False, debug_transients=True)
     assert len(m.dace_model.outputs) == 6 and not any(d.transient for d in m.sdfg.arrays.values())
+
+
+def test_reshapes_become_views():
+    """After the fusion pass a Reshape into a transient is a view of its input; one that produces a model output turns
+    its input into a view of the output, so the producer writes in place; launch order still follows the data."""
+    m = DaceModule(LeNet(), dummy_inputs=(torch.rand(8, 1, 32, 32), ))
+    assert m.compiled_function.kernel_names() == ["conv2d", "maxpool2d", "conv2d", "maxpool2d", "gemm", "gemm", "gemm", "softmax"]
+    views = {n: d.view_of for n, d in m.sdfg.arrays.items() if d.view_of}
+    assert len(views) == 1
+    (flat, pooled), = views.items()
+    assert m.sdfg.arrays[flat].shape == (8, 576) and m.sdfg.arrays[pooled].shape == (8, 16, 6, 6)
+    assert m.sdfg.root_of(flat) == pooled
+
+    class Tail(nn.Module):
+        def forward(self, x):
+            return torch.relu(x).reshape(4, 6), torch.exp(x).reshape(2, 12).reshape(24)
+
+    m = DaceModule(Tail(), dummy_inputs=(torch.rand(2, 3, 4), ))
+    assert m.compiled_function.kernel_names() == ["unary", "unary"]
+    assert sorted(m.sdfg.root_of(n) for n, d in m.sdfg.arrays.items() if d.view_of) == ["__return_0", "__return_1"]
+    # without the pass every reshape is a copy
+    m = DaceModule(Tail(), dummy_inputs=(torch.rand(2, 3, 4), ), auto_optimize=False)
+    assert len(m.compiled_function.kernel_names()) == 5
 
 
 def _vi(name, shape, dtype=torch.float32):

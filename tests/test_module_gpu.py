@@ -14,7 +14,7 @@ from daceml_b200 import lib as L
 from daceml_b200.onnx.onnx_importer import ONNXModel
 from daceml_b200.torch import DaceModule, dace_module
 from conftest import assert_close
-from models import MLP, MBConv, bert_layer
+from models import LeNet, MLP, MBConv, bert_layer
 
 pytestmark = pytest.mark.gpu
 warnings.filterwarnings("ignore")
@@ -127,4 +127,55 @@ def test_onnx_model_multiple_outputs_keywords_and_saved_transients():
     # host tensors are staged through the device
     h0, h1 = model(a, b)
     assert_close(h0, r0, what="host inputs")
+    status_ok()
+
+
+def test_lenet_module():
+    """tests/torch/test_lenet.py: batch 8 of 1x32x32 images."""
+    torch.manual_seed(0)
+    net = LeNet()
+    x = torch.rand(8, 1, 32, 32)
+    module = DaceModule(copy.deepcopy(net).cuda())
+    y = module(x.cuda())
+    names = module.compiled_function.kernel_names()
+    assert names == ["conv2d", "maxpool2d", "conv2d", "maxpool2d", "gemm", "gemm", "gemm", "softmax"]  # view(): no launch
+    with torch.no_grad():
+        assert_close(y, net(x), what="LeNet")
+    status_ok()
+
+
+def test_multihead_attention_module():
+    """tests/torch/test_attn.py: ``nn.MultiheadAttention(1024, 16, bias=False)`` on [512, 2, 1024] query / key / value,
+    both outputs (the attention output and the head-averaged weights)."""
+    torch.manual_seed(0)
+    mha = torch.nn.MultiheadAttention(1024, 16, bias=False).eval()
+    q, k, v = torch.randn(512, 2, 1024), torch.randn(512, 2, 1024), torch.randn(512, 2, 1024)
+    module = DaceModule(copy.deepcopy(mha).cuda())
+    out, weights = module(q.cuda(), k.cuda(), v.cuda())
+    with torch.no_grad():
+        ref_out, ref_weights = mha(q, k, v)
+    assert_close(out, ref_out, what="attention output", atol=1e-4)
+    assert_close(weights, ref_weights, what="averaged attention weights", atol=1e-5)
+    assert "unary" not in module.compiled_function.kernel_names()  # every reshape became a view
+    status_ok()
+
+
+def test_reshape_and_multiple_output_modules():
+    """tests/torch/test_reshape.py and test_multi_output.py (``auto_optimize=False`` there as well)."""
+    class Reshape(nn.Module):
+        def forward(self, x):
+            return x.reshape([5, 5])
+
+    class TwoOutputs(nn.Module):
+        def forward(self, x):
+            return x + 1, x + 2
+
+    x = torch.rand(25)
+    y = DaceModule(Reshape(), auto_optimize=False, dummy_inputs=(x, ))(x.cuda())
+    assert torch.equal(y.cpu(), x.reshape(5, 5))
+    y = DaceModule(Reshape())(x.cuda())  # with the view pass the only node left is the copy into the output
+    assert torch.equal(y.cpu(), x.reshape(5, 5))
+    a, b = DaceModule(TwoOutputs(), auto_optimize=False)(x.cuda())
+    assert_close(a, x + 1, what="output_0")
+    assert_close(b, x + 2, what="output_1")
     status_ok()
