@@ -181,6 +181,34 @@ def run_hbm_kernels(args):
     hs, ho = [rnd(T, FFN) for _ in range(n)], [torch.empty(T, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
     cases.append(("bias_act_kernel", "bias + GELU(erf) [4096, 4096] fp16", n, 2 * T * FFN * 2,
                   lambda i: K.bias_act(hs[i], ho[i], bias=bias_f, act=L.EPI_GELU)))
+    # data movement: the packed QKV tensor split into its three parts (Slice on the last axis), the head-merge of two
+    # halves (Concat), an embedding lookup (Gather of 1024-wide rows) and a mask select (Where)
+    n = 6  # 6 x 50 MB
+    qkv = [rnd(T, 3 * HIDDEN) for _ in range(n)]
+    parts = [torch.empty(T, HIDDEN, dtype=torch.float16, device=dev) for _ in range(3)]
+
+    def split3(i):
+        for j in range(3):
+            K.strided_copy(qkv[i].narrow(1, j * HIDDEN, HIDDEN), parts[j])
+
+    cases.append(("strided_copy_kernel", "Split of [4096, 3072] fp16 into three [4096, 1024] (3 launches)", n, 2 * T * 3 * HIDDEN * 2, split3))
+    cat = [torch.empty(T, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
+    halves = [rnd(T, FFN // 2) for _ in range(2 * n)]
+
+    def concat2(i):
+        K.strided_copy(halves[2 * i], cat[i].narrow(1, 0, FFN // 2))
+        K.strided_copy(halves[2 * i + 1], cat[i].narrow(1, FFN // 2, FFN // 2))
+
+    cases.append(("strided_copy_kernel", "Concat of two [4096, 2048] fp16 along the last axis (2 launches)", n, 2 * T * FFN * 2, concat2))
+    table = rnd(30522, HIDDEN)
+    ids = [torch.randint(0, 30522, (64, SEQ), generator=g).to(dev) for _ in range(4)]
+    emb = [torch.empty(64, SEQ, HIDDEN, dtype=torch.float16, device=dev) for _ in range(4)]
+    cases.append(("gather_kernel", "embedding lookup: [30522, 1024] fp16 table, [64, 512] ids", 4, 2 * 64 * SEQ * HIDDEN * 2 + 64 * SEQ * 8,
+                  lambda i: K.gather(table, ids[i], emb[i], 0)))
+    cond = [(torch.rand(T, FFN, generator=g) > 0.5).to(dev) for _ in range(n)]
+    zero = torch.zeros((), dtype=torch.float16, device=dev)
+    cases.append(("where_kernel", "Where(mask, x, 0) [4096, 4096] fp16, bool mask", n, T * FFN * (2 + 2 + 1),
+                  lambda i: K.where(cond[i], hs[i], zero, ho[i])))
     reps = max(args.steps // 4, 12)
     for name, what, nset, nbytes, fn in cases:
         for i in range(min(nset, max(args.warmup, 3))):

@@ -100,6 +100,36 @@ __global__ void __launch_bounds__(256) where_kernel(const uint8_t* __restrict__ 
     }
 }
 
+// Same-shape contiguous condition and x, y either the same or one scalar: 16 bytes of x per thread per step.
+template <typename E>
+__global__ void __launch_bounds__(256) where_fast_kernel(const uint8_t* __restrict__ c, const E* __restrict__ x,
+                                                         const E* __restrict__ y, E* __restrict__ out, uint64_t n,
+                                                         int y_scalar) {
+    constexpr int V = 16 / sizeof(E);
+    struct alignas(16) Vec { E v[V]; };
+    struct alignas(V) Flags { uint8_t f[V]; };
+    const uint64_t nvec = n / V;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const E ys = y_scalar ? y[0] : E();
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const Flags f = reinterpret_cast<const Flags*>(c)[i];
+        const Vec xv = reinterpret_cast<const Vec*>(x)[i];
+        Vec yv;
+        if (!y_scalar) yv = reinterpret_cast<const Vec*>(y)[i];
+        Vec o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = f.f[j] ? xv.v[j] : (y_scalar ? ys : yv.v[j]);
+        reinterpret_cast<Vec*>(out)[i] = o;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (uint64_t i = nvec * V; i < n; ++i) out[i] = c[i] ? x[i] : (y_scalar ? ys : y[i]);
+}
+
+template <typename T> struct CmpVec;
+template <> struct CmpVec<__half> { static constexpr int V = 8; };
+template <> struct CmpVec<float> { static constexpr int V = 4; };
+template <> struct CmpVec<long long> { static constexpr int V = 2; };
+
 struct CmpGeom {
     int32_t rank;
     uint32_t shape[MAXR];
@@ -109,6 +139,9 @@ struct CmpGeom {
 __device__ __forceinline__ float cmp_ld(const float* p) { return __ldg(p); }
 __device__ __forceinline__ float cmp_ld(const __half* p) { return __half2float(__ldg(p)); }
 __device__ __forceinline__ long long cmp_ld(const long long* p) { return __ldg(p); }
+__device__ __forceinline__ float cmp_val(float v) { return v; }
+__device__ __forceinline__ float cmp_val(__half v) { return __half2float(v); }
+__device__ __forceinline__ long long cmp_val(long long v) { return v; }
 
 // out[i] = a <op> b as one byte (0 / 1), numpy broadcasting by strides; NaN compares false except for "not equal"
 template <typename T>
@@ -140,6 +173,40 @@ __global__ void __launch_bounds__(256) compare_kernel(const T* __restrict__ a, c
         }
         out[i] = r ? 1 : 0;
     }
+}
+
+template <typename A, typename B>
+__device__ __forceinline__ bool cmp_apply(int op, A x, B y) {
+    switch (op) {
+        case B200ML_CMP_GT: return x > y;
+        case B200ML_CMP_LT: return x < y;
+        case B200ML_CMP_GE: return x >= y;
+        case B200ML_CMP_LE: return x <= y;
+        default: return x == y;
+    }
+}
+
+// a contiguous in the output's shape, b the same or one scalar: 16 bytes of a per thread per step
+template <typename T>
+__global__ void __launch_bounds__(256) compare_fast_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                           uint8_t* __restrict__ out, uint64_t n, int op, int b_scalar) {
+    constexpr int V = CmpVec<T>::V;
+    struct alignas(16) Vec { T v[V]; };
+    struct alignas(V) Flags { uint8_t f[V]; };
+    const uint64_t nvec = n / V;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    const auto bs = cmp_ld(b);
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const Vec av = reinterpret_cast<const Vec*>(a)[i];
+        Vec bv;
+        if (!b_scalar) bv = reinterpret_cast<const Vec*>(b)[i];
+        Flags f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) f.f[j] = cmp_apply(op, cmp_val(av.v[j]), b_scalar ? bs : cmp_val(bv.v[j])) ? 1 : 0;
+        reinterpret_cast<Flags*>(out)[i] = f;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (uint64_t i = nvec * V; i < n; ++i) out[i] = cmp_apply(op, cmp_ld(a + i), b_scalar ? bs : cmp_ld(b + i)) ? 1 : 0;
 }
 
 struct PoolGeom {
@@ -189,6 +256,20 @@ int launch_copy(const b200ml_ctx* ctx, const void* x, void* y, uint64_t total, c
 }
 
 }  // namespace
+
+// 1: the strides are those of a contiguous array of this shape; 0: all zero (one element broadcast); -1: neither
+static int stride_kind(int rank, const int64_t* shape, const int64_t* st) {
+    bool contiguous = true, scalar = true;
+    int64_t acc = 1;
+    for (int d = rank - 1; d >= 0; --d) {
+        if (shape[d] != 1) {
+            contiguous = contiguous && st[d] == acc;
+            scalar = scalar && st[d] == 0;
+        }
+        acc *= shape[d];
+    }
+    return contiguous ? 1 : (scalar ? 0 : -1);
+}
 
 static int strided_copy(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int rank, const int64_t* shape,
                  const int64_t* xs, const int64_t* ys, cudaStream_t s) {
@@ -279,8 +360,19 @@ static int where(const b200ml_ctx* ctx, int elem_bytes, const void* cond, const 
         total *= static_cast<uint64_t>(shape[d]);
     }
     if (total == 0) return B200ML_OK;
-    const unsigned grid = grid_for(ctx, total);
     const uint8_t* c = static_cast<const uint8_t*>(cond);
+    const int yk = stride_kind(rank, shape, ys);
+    if (stride_kind(rank, shape, cs) == 1 && stride_kind(rank, shape, xs) == 1 && yk >= 0 && aligned16(x) && aligned16(out) &&
+        (yk == 0 || aligned16(y)) && (reinterpret_cast<uintptr_t>(cond) & 7u) == 0) {
+        const unsigned fgrid = grid_for(ctx, total / (16 / elem_bytes) + 1);
+        switch (elem_bytes) {
+            case 2: where_fast_kernel<uint16_t><<<fgrid, 256, 0, s>>>(c, (const uint16_t*)x, (const uint16_t*)y, (uint16_t*)out, total, yk == 0); break;
+            case 4: where_fast_kernel<uint32_t><<<fgrid, 256, 0, s>>>(c, (const uint32_t*)x, (const uint32_t*)y, (uint32_t*)out, total, yk == 0); break;
+            default: where_fast_kernel<uint64_t><<<fgrid, 256, 0, s>>>(c, (const uint64_t*)x, (const uint64_t*)y, (uint64_t*)out, total, yk == 0); break;
+        }
+        return check_launch("where");
+    }
+    const unsigned grid = grid_for(ctx, total);
     switch (elem_bytes) {
         case 2: where_kernel<uint16_t><<<grid, 256, 0, s>>>(c, (const uint16_t*)x, (const uint16_t*)y, (uint16_t*)out, total, g); break;
         case 4: where_kernel<uint32_t><<<grid, 256, 0, s>>>(c, (const uint32_t*)x, (const uint32_t*)y, (uint32_t*)out, total, g); break;
@@ -376,8 +468,21 @@ static int compare(const b200ml_ctx* ctx, int kind, int op, const void* a, const
         total *= static_cast<uint64_t>(shape[d]);
     }
     if (total == 0) return B200ML_OK;
-    const unsigned grid = grid_for(ctx, total);
     uint8_t* o = static_cast<uint8_t*>(out);
+    const int bk = stride_kind(rank, shape, bs);
+    if (stride_kind(rank, shape, as) == 1 && bk >= 0 && aligned16(a) && (bk == 0 || aligned16(b)) &&
+        (reinterpret_cast<uintptr_t>(out) & 7u) == 0) {
+        const int v = kind == B200ML_F16 ? 8 : (kind == B200ML_F32 ? 4 : 2);
+        const unsigned fgrid = grid_for(ctx, total / v + 1);
+        if (kind == B200ML_F16)
+            compare_fast_kernel<__half><<<fgrid, 256, 0, s>>>((const __half*)a, (const __half*)b, o, total, op, bk == 0);
+        else if (kind == B200ML_F32)
+            compare_fast_kernel<float><<<fgrid, 256, 0, s>>>((const float*)a, (const float*)b, o, total, op, bk == 0);
+        else
+            compare_fast_kernel<long long><<<fgrid, 256, 0, s>>>((const long long*)a, (const long long*)b, o, total, op, bk == 0);
+        return check_launch("compare");
+    }
+    const unsigned grid = grid_for(ctx, total);
     if (kind == B200ML_F16)
         compare_kernel<__half><<<grid, 256, 0, s>>>((const __half*)a, (const __half*)b, o, total, op, g);
     else if (kind == B200ML_F32)

@@ -210,6 +210,12 @@ def test_comparisons(dtype, rng):
         out = empty((33, 65), torch.bool)
         getattr(donnx, "ONNX" + name)(A=dev(a), B=dev(b), C=out)
         same(out, fn(a, b))
+        # the vectorised forms: a full second operand, and a scalar one
+        full = np.ascontiguousarray(np.broadcast_to(b, a.shape))
+        getattr(donnx, "ONNX" + name)(A=dev(a), B=dev(full), C=out)
+        same(out, fn(a, full))
+        getattr(donnx, "ONNX" + name)(A=dev(a), B=dev(b[4:5].reshape(())), C=out)
+        same(out, fn(a, b[4]))
     status_ok()
 
 
