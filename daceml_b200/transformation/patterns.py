@@ -410,6 +410,9 @@ def fuse_attention(sdfg, state):
             continue
         if mask is not None and len(sdfg.arrays[mask].shape) not in (2, 4):
             continue
+        # the fused kernel is fp16 with 64-wide heads; anything else stays MatMul / Softmax / MatMul
+        if sdfg.arrays[q[0]].dtype != torch.float16 or q[3] != 64:
+            continue
         out = _out(state, rs2)
         _remove(state, chain + [pv, tr, rs2] + q[1] + k[1] + v[1])
         _add_node(sdfg, state, "Attention", sm.label + "_attention", dict(Q=q[0], K=k[0], V=v[0], Mask=mask), dict(Y=out),

@@ -42,6 +42,13 @@ def test_bert_layer_export_imports_node_for_node_and_collapses():
     assert att is not None
 
 
+def test_attention_fusion_only_where_the_kernel_applies():
+    """fp32 layers and head sizes other than 64 keep MatMul / Softmax / MatMul instead of failing at expansion."""
+    for layer, x in ((bert_layer(256, 4, 512), torch.randn(2, 128, 256)), (bert_layer(96, 4, 128).half(), torch.randn(2, 16, 96).half())):
+        names = DaceModule(layer, dummy_inputs=(x, )).compiled_function.kernel_names()
+        assert "attention" not in names and names.count("softmax") == 1 and names.count("gemm") == 8
+
+
 def test_daceml_module_wraps_the_benchmark_modules():
     m = DaceModule(MLP(), dummy_inputs=(torch.randn(64, 784), ))
     assert m.compiled_function.kernel_names() == ["gemm", "gemm", "gemm", "softmax"]

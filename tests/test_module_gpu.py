@@ -179,3 +179,21 @@ def test_reshape_and_multiple_output_modules():
     assert_close(a, x + 1, what="output_0")
     assert_close(b, x + 2, what="output_1")
     status_ok()
+
+
+def test_bert_encoder_reference_test_fp32():
+    """tests/torch/test_bert_encoder.py:11-33: the default ``BertConfig`` layer (768 / 12 / 3072) in fp32 on
+    [8, 512, 768], compared with the reference's own tolerance (rtol 1e-5, atol 1e-4).  fp32 has no fused attention
+    kernel, so the graph keeps MatMul / Softmax / MatMul and the fp32 GEMM kernels."""
+    layer = bert_layer(768, 12, 3072)
+    torch.manual_seed(3)
+    x = torch.randn(8, 512, 768)
+    module = DaceModule(copy.deepcopy(layer).cuda(), training=False, simplify=True)
+    y = module(x.cuda())
+    names = module.compiled_function.kernel_names()
+    assert "attention" not in names and names.count("softmax") == 1 and "unary" not in names
+    with torch.no_grad():
+        ref = layer.double()(x.double())
+    ref = ref[0] if isinstance(ref, tuple) else ref
+    assert_close(y, ref.float(), what="fp32 BertLayer", rtol=1e-5, atol=1e-4)
+    status_ok()
