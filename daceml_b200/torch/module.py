@@ -50,8 +50,9 @@ class DaceModule(nn.Module):
     :param sdfg_name: the name to give to the sdfg (defaults to the module's class name).
     :param cuda_graph: replay the forward pass as one CUDA graph (inputs are copied into static buffers and the
                        returned tensors are reused by the next call).
-    ``inputs_to_skip``, ``onnx_simplify``, ``simplify`` and ``compile_torch_extension`` are accepted for
-    signature compatibility.
+    :param compile_torch_extension: call the compiled module through a registered torch operator
+                                    (``torch.ops.daceml_<sdfg_name>.<sdfg_name>``), as the reference's C++ extension does.
+    ``inputs_to_skip``, ``onnx_simplify`` and ``simplify`` are accepted for signature compatibility.
 
     :Example:
 
@@ -187,7 +188,7 @@ class DaceModule(nn.Module):
             return result
 
         if not self.cuda_graph:
-            return run
+            return self._as_torch_op(run, input_names, output_names)
 
         from daceml_b200.runner import GraphedCall
         dev = compiled._device()
@@ -212,7 +213,30 @@ class DaceModule(nn.Module):
             return holder["out"]
 
         self.static_inputs = static_in
-        return replay
+        return self._as_torch_op(replay, input_names, output_names)
+
+    def _as_torch_op(self, function, input_names, output_names):
+        """With ``compile_torch_extension`` (the default, as in the reference) the module is called through a registered
+        torch operator, ``torch.ops.daceml_<sdfg_name>.<sdfg_name>(handle, *inputs)``; otherwise directly."""
+        self.torch_op = None
+        if not self.compile_torch_extension or self.debug_transients:
+            return function
+        from .dispatchers import register_torch_op
+        outs = [(self.sdfg.arrays[n].shape, self.sdfg.arrays[n].dtype) for n in output_names]
+        try:
+            op, handle = register_torch_op(self.sdfg_name, input_names, outs, function)
+        except Exception as e:  # an operator schema torch rejects must not make the module unusable
+            log.warning("could not register %s as a torch operator (%s); calling it directly", self.sdfg_name, e)
+            return function
+        self.torch_op, self.torch_op_handle = op, handle
+
+        def call(*args):
+            if not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+                return function(*args)  # host tensors are staged by the compiled SDFG itself
+            result = op(handle, *args)
+            return tuple(result) if isinstance(result, list) else result
+
+        return call
 
     def forward(self, *actual_inputs):
         """ Execute the forward pass using the traced ``module``."""

@@ -94,6 +94,29 @@ def test_module_argument_checks_and_hooks():
     assert isinstance(d, DaceModule) and d.sdfg_name == "decorated"
 
 
+def test_module_is_registered_as_a_torch_operator():
+    """``compile_torch_extension`` (default): ``torch.ops.daceml_<name>.<name>(handle, *inputs)`` with a schema and a
+    shape function, as the reference's generated extension declares it (cpp_torch_extension.py:398-457)."""
+    m = DaceModule(MLP(), dummy_inputs=(torch.randn(16, 784), ), sdfg_name="mlp_as_op")
+    assert m.torch_op is torch.ops.daceml_mlp_as_op.mlp_as_op
+    assert str(m.torch_op.default._schema) == "daceml_mlp_as_op::mlp_as_op(int handle_ptr, Tensor onnxCOLONCOLONGemm_0) -> Tensor"
+    out = m.torch_op(m.torch_op_handle, torch.empty(16, 784, device="meta"))
+    assert out.shape == (16, 10) and out.dtype == torch.float32 and out.device.type == "meta"
+    again = DaceModule(MLP(), dummy_inputs=(torch.randn(16, 784), ), sdfg_name="mlp_as_op")  # same name: numbered namespace
+    assert again.torch_op is torch.ops.daceml_mlp_as_op_1.mlp_as_op
+    plain = DaceModule(MLP(), dummy_inputs=(torch.randn(16, 784), ), compile_torch_extension=False)
+    assert plain.torch_op is None
+
+    class Two(nn.Module):
+        def forward(self, x, y):
+            return x + y, x * y
+
+    two = DaceModule(Two(), dummy_inputs=(torch.randn(4), torch.randn(4)), sdfg_name="two_outputs_op")
+    assert str(two.torch_op.default._schema).endswith("-> Tensor[]")
+    a, b = two.torch_op(two.torch_op_handle, torch.empty(4, device="meta"), torch.empty(4, device="meta"))
+    assert a.shape == b.shape == (4, )
+
+
 def test_debug_transients_become_outputs():
     m = DaceModule(MLP(), dummy_inputs=(torch.randn(8, 784), ), auto_optimize=False, debug_transients=True)
     assert len(m.dace_model.outputs) == 6 and not any(d.transient for d in m.sdfg.arrays.values())
