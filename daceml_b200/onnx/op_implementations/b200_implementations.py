@@ -581,6 +581,39 @@ class B200Conv(ONNXForward):
 _ACT = {"": 0, "Relu": L.EPI_RELU, "Gelu": L.EPI_GELU, "Swish": L.EPI_SWISH}
 
 
+@op_implementation(op="BatchNormalization", name="b200")
+class B200BatchNormalization(ONNXForward):
+    """Inference BatchNormalization with constant statistics: ``Y = a * X + b`` per channel, ``a = scale / sqrt(var +
+    eps)``, ``b = B - mean * a``, run as a depthwise 1x1 convolution (one read of X, one write of Y).  The reference's
+    pure and cuDNN expansions are the training form (``img_op_implementations.py:333-393``,
+    ``cudnn_implementations.py:413-``), which this library does not implement."""
+
+    @staticmethod
+    def forward_can_be_applied(node, state, sdfg):
+        from daceml_b200.transformation.patterns import batchnorm_affine
+        x, y = in_desc_with_name(node, state, sdfg, "X"), out_desc_with_name(node, state, sdfg, "Y")
+        return (_float_descs(x, y) and 2 <= len(x.shape) <= 4 and tuple(x.shape) == tuple(y.shape)
+                and batchnorm_affine(sdfg, state, node) is not None)
+
+    @staticmethod
+    def forward(node, state, sdfg):
+        from daceml_b200.transformation.patterns import batchnorm_affine
+        a, b = batchnorm_affine(sdfg, state, node)
+        x = in_desc_with_name(node, state, sdfg, "X")
+        shape4 = tuple(x.shape) + (1, ) * (4 - len(x.shape))
+        cache = {}
+
+        def run(ins, outs):
+            t = ins["X"]
+            key = (t.device, t.dtype)
+            if key not in cache:
+                cache[key] = (a.reshape(-1, 1, 1, 1).to(t.dtype).to(t.device).contiguous(), b.to(t.dtype).to(t.device).contiguous())
+            w, bias = cache[key]
+            K.conv2d(t.view(shape4), w, outs["Y"].view(shape4), bias=bias, group=shape4[1])
+
+        return KernelTasklet(node.label, run, kernels=("conv2d",))
+
+
 @op_implementation(op="FusedConv", name="b200")
 class B200FusedConv(ONNXForward):
     """Conv + bias + activation, with a squeeze-excite gate on the input, a residual add and the

@@ -74,6 +74,8 @@ _S = [
     ONNXSchema("Conv", ["X", "W", ("B", OPTIONAL)], ["Y"],
                dict(auto_pad="NOTSET", dilations=None, group=1, kernel_shape=None, pads=None, strides=None)),
     ONNXSchema("GlobalAveragePool", ["X"], ["Y"]),
+    # inference form only: Y from the running statistics (the training-mode outputs have no kernel here)
+    ONNXSchema("BatchNormalization", ["X", "scale", "B", "mean", "var"], ["Y"], dict(epsilon=1e-5, momentum=0.9)),
     # data movement (one strided-copy / gather kernel each; on constant inputs they fold at build time)
     ONNXSchema("Shape", ["data"], ["shape"]),
     ONNXSchema("Gather", ["data", "indices"], ["output"], dict(axis=0)),

@@ -466,6 +466,44 @@ def pack_qkv(sdfg, state):
 # ---------------------------------------------------------------------------------------------
 # convolution blocks
 # ---------------------------------------------------------------------------------------------
+def batchnorm_affine(sdfg, state, bn):
+    """Inference BatchNormalization as a per-channel ``a * x + b`` (fp32 on the host); None unless the four statistics
+    tensors are constants."""
+    ts = [_const(sdfg, _in(state, bn, c)) for c in ("scale", "B", "mean", "var")]
+    if any(t is None for t in ts):
+        return None
+    scale, shift, mean, var = (t.detach().float().cpu() for t in ts)
+    a = scale / torch.sqrt(var + float(bn.epsilon))
+    return a, shift - mean * a
+
+
+@_each_state
+def fold_batchnorm_into_conv(sdfg, state):
+    """Conv(W, b) -> BatchNormalization(constants)  =>  Conv(a * W, a * b + shift): the exporter does this itself for
+    modules in eval mode; graphs from elsewhere may still carry the pair."""
+    count = 0
+    for bn in _nodes(state, "BatchNormalization"):
+        x = _in(state, bn, "X")
+        conv = _producer(state, x)
+        if conv is None or type(conv) is not donnx.ONNXConv or _only_consumer(sdfg, state, x)[0] is not bn:
+            continue
+        w, b = _const(sdfg, _in(state, conv, "W")), _in(state, conv, "B")
+        ab = batchnorm_affine(sdfg, state, bn)
+        if w is None or ab is None or (b is not None and _const(sdfg, b) is None):
+            continue
+        a, shift = ab
+        dtype, dev = w.dtype, w.device
+        wn, bnm = bn.label + "_w", bn.label + "_b"
+        sdfg.add_constant(wn, (w.float().cpu() * a.reshape(-1, 1, 1, 1)).to(dtype).to(dev).contiguous())
+        bias = _const(sdfg, b).float().cpu() if b is not None else torch.zeros_like(a)
+        sdfg.add_constant(bnm, (bias * a + shift).to(dtype).to(dev).contiguous())
+        ins, y, attrs = dict(X=_in(state, conv, "X"), W=wn, B=bnm), _out(state, bn), _attrs(conv)
+        _remove(state, [conv, bn])
+        _add_node(sdfg, state, "Conv", conv.label, ins, dict(Y=y), **attrs)
+        count += 1
+    return count
+
+
 @_each_state
 def fuse_conv(sdfg, state):
     """Conv -> Swish | Relu  =>  FusedConv(activation); a Conv left alone also becomes a FusedConv so that the gate,
@@ -624,5 +662,5 @@ def alias_reshapes(sdfg, state):
     return count
 
 
-PATTERNS = [remove_identity, fuse_gelu, fuse_swish, fuse_layernorm, fuse_linear, fuse_matmul_epilogue, fuse_attention, pack_qkv, fuse_conv,
+PATTERNS = [remove_identity, fold_batchnorm_into_conv, fuse_gelu, fuse_swish, fuse_layernorm, fuse_linear, fuse_matmul_epilogue, fuse_attention, pack_qkv, fuse_conv,
             fuse_squeeze_excite, fuse_conv_residual]

@@ -352,6 +352,16 @@ def conv2d(x, w, b=None, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), gr
     return y.astype(x.dtype)
 
 
+def batchnorm_inference(x, scale, b, mean, var, eps=1e-5):
+    """ONNX BatchNormalization, inference form: ``(x - mean) / sqrt(var + eps) * scale + b`` per channel (axis 1).
+    The reference only has the training form (img_op_implementations.py:333-393, which also updates the running
+    statistics); this is the ONNX definition, checked against ``torch.nn.functional.batch_norm`` in the tests."""
+    bshape = (1, -1) + (1, ) * (x.ndim - 2)
+    xf = np.asarray(x, dtype=np.float32)
+    y = (xf - mean.reshape(bshape)) / np.sqrt(var.reshape(bshape) + np.float32(eps)) * scale.reshape(bshape) + b.reshape(bshape)
+    return y.astype(x.dtype)
+
+
 def global_average_pool(x):
     """GlobalAveragePool (img_op_implementations.py:415-417): mean over H, W into [N, C, 1, 1]."""
     return np.mean(_f(x), axis=(2, 3), keepdims=True).astype(x.dtype)

@@ -145,6 +145,27 @@ def test_reshapes_become_views():
     assert len(m.compiled_function.kernel_names()) == 5
 
 
+def test_batchnorm_folds_into_conv_or_becomes_one_launch():
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv, self.bn, self.bn2 = nn.Conv2d(3, 8, 3, padding=1, bias=False), nn.BatchNorm2d(8), nn.BatchNorm2d(8)
+
+        def forward(self, x):
+            return self.bn2(torch.relu(self.bn(self.conv(x))))
+
+    net = Net().eval()
+    graph = export_module(net, (torch.randn(2, 3, 8, 8), ), do_constant_folding=False)  # keeps Conv -> BatchNormalization
+    assert [n.op_type for n in graph.nodes] == ["Conv", "BatchNormalization", "Relu", "BatchNormalization"]
+    model = ONNXModel("bn", graph)
+    model.auto_optimize()
+    # Conv+BN+Relu is one convolution, the free-standing BN one depthwise launch
+    assert model.compile_and_init().kernel_names() == ["conv2d", "conv2d"]
+    folded = next(t for n, t in model.sdfg.constants.items() if n.endswith("_w"))
+    a = net.bn.weight / torch.sqrt(net.bn.running_var + net.bn.eps)
+    assert torch.allclose(folded, net.conv.weight * a.reshape(-1, 1, 1, 1), atol=1e-6)
+
+
 def _vi(name, shape, dtype=torch.float32):
     return ValueInfo(name, tuple(shape), dtype)
 

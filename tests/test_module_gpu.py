@@ -224,3 +224,42 @@ def test_module_runs_through_its_torch_operator_and_under_torch_compile():
         assert_close(torch.compile(around_op, backend="eager", fullgraph=True)(x.cuda()), ref, what="operator under torch.compile")
         assert_close(torch.compile(around_module, backend="eager")(x.cuda()), ref, what="module under torch.compile")
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_batchnorm_inference_modules(dtype):
+    """BatchNorm in eval mode (running statistics): free-standing in 2-D, 3-D and 4-D, and after a convolution from a
+    graph exported without the exporter's own Conv+BN folding.  Checked against the oracle and PyTorch."""
+    import numpy as np
+    from oracle import ops
+    from daceml_b200.onnx.exported_graph import export_module
+    torch.manual_seed(0)
+    for bn, shape in ((nn.BatchNorm2d(24), (8, 24, 28, 28)), (nn.BatchNorm1d(40), (64, 40)), (nn.BatchNorm1d(16), (4, 16, 50))):
+        bn.running_mean.normal_(), bn.running_var.uniform_(0.5, 2.0), bn.weight.data.normal_(), bn.bias.data.normal_()
+        bn = bn.eval().to(dtype)
+        x = torch.randn(*shape).to(dtype)
+        y = DaceModule(copy.deepcopy(bn).cuda())(x.cuda())
+        ref = ops.batchnorm_inference(x.float().numpy(), *(t.detach().float().numpy() for t in (bn.weight, bn.bias, bn.running_mean, bn.running_var)),
+                                      eps=bn.eps)
+        assert_close(y, ref, dtype=dtype, what="BatchNorm %s" % (shape, ))
+        with torch.no_grad():
+            assert_close(y, bn.float()(x.float()), dtype=dtype, what="BatchNorm vs torch")
+
+    class ConvBn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv, self.bn = nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8)
+
+        def forward(self, x):
+            return torch.relu(self.bn(self.conv(x)))
+
+    net = ConvBn().eval()
+    net.bn.running_mean.normal_(), net.bn.running_var.uniform_(0.5, 2.0)
+    net = net.to(dtype)
+    x = torch.randn(4, 3, 16, 16).to(dtype)
+    model = ONNXModel("convbn", export_module(net, (x, ), do_constant_folding=False))
+    y = model(x.cuda())
+    assert model.compile_and_init().kernel_names() == ["conv2d"]
+    with torch.no_grad():
+        assert_close(y, net.float()(x.float()), dtype=dtype, what="Conv + BatchNorm + Relu")
+    status_ok()
