@@ -317,6 +317,81 @@ def run_other_configs(args):
                           "dtype": "f32", "data": "synthetic"}), flush=True)
 
 
+def run_via_module(args):
+    """The same metric with the layers coming from real modules: 24 HuggingFace ``BertLayer`` objects (BERT-large
+    sizes, their own initialisation: normal(0, 0.02) weights, zero biases) wrapped in one ``DaceModule``.  A step is one
+    layer; the 24-layer module is called ``steps / 24`` times, each call feeding the next, all in one CUDA graph timed
+    with CUDA events.  Prints one JSON line (N = 1 only; no roofline probe, the kernels are those of the main run)."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the product path has no CPU fallback")
+    import warnings
+    from daceml_b200 import lib as L
+    from daceml_b200.runner import upload_graph
+    from daceml_b200.torch import DaceModule
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        from transformers import BertConfig
+        from transformers.models.bert.modeling_bert import BertLayer
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    torch.manual_seed(11)
+    cfg = BertConfig(hidden_size=HIDDEN, num_attention_heads=HEADS, intermediate_size=FFN)
+    cfg._attn_implementation = "eager"
+
+    class Stack(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList([BertLayer(cfg) for _ in range(LAYERS)])
+
+        def forward(self, x):
+            for layer in self.layers:
+                out = layer(x)
+                x = out[0] if isinstance(out, tuple) else out
+            return x
+
+    t0 = time.perf_counter()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        module = DaceModule(Stack().half().to(dev).eval(), compile_torch_extension=False)
+        x = torch.randn(BATCH, SEQ, HIDDEN, generator=torch.Generator().manual_seed(7)).half().to(dev)
+        module(x)
+    build_s = time.perf_counter() - t0
+    compiled = module.compiled_function
+    names = compiled.kernel_names()
+    arg = module.sdfg.arg_names[0]
+    bufs = [x.clone(), torch.empty_like(x)]
+    calls = max(1, (args.steps + LAYERS - 1) // LAYERS)
+    steps = calls * LAYERS
+
+    def run(n):
+        for i in range(n):
+            compiled(**{arg: bufs[i % 2], "__return": bufs[(i + 1) % 2]})
+
+    run(max(2, (args.warmup + LAYERS - 1) // LAYERS))
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run(calls)
+    upload_graph(graph)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    assert L.get_context(dev).device_status() == 0 and torch.isfinite(bufs[calls % 2]).all()
+    print(json.dumps({"metric": "bert_large_fp16_encoder_layer_samples_per_s", "value": BATCH * steps / (ms * 1e-3), "unit": "samples/s",
+                      "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+                      "dtype": "f16", "data": "synthetic",
+                      "config": {"workload": "bert-large encoder layer fp16, B=8, S=512, through DaceModule(24 x transformers BertLayer)",
+                                 "api": "daceml_b200.torch.DaceModule", "launches_per_layer": len(names) / LAYERS,
+                                 "kernels": sorted(set(names)), "export_import_optimize_s": round(build_s, 2),
+                                 "l2": "24 distinct layer weight sets (604 MB): weights come from HBM every step"},
+                      "gpu_launches": len(names) * calls}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -330,8 +405,14 @@ def main():
     ap.add_argument("--other-configs", action="store_true",
                     help="instead of the layer: time the fp32 configurations 1 (strided conv), 2 (MLP) and 4 (MBConv block) "
                          "at their full sizes and print one JSON line each")
+    ap.add_argument("--via-module", action="store_true",
+                    help="instead of the hand-built layer graphs: 24 transformers BertLayer modules wrapped in one DaceModule "
+                         "(export, import, fusion), timed the same way; one JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.via_module:
+        run_via_module(args)
+        return
     if args.hbm_kernels:
         run_hbm_kernels(args)
         return
