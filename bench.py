@@ -181,6 +181,17 @@ def run_hbm_kernels(args):
     hs, ho = [rnd(T, FFN) for _ in range(n)], [torch.empty(T, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
     cases.append(("bias_act_kernel", "bias + GELU(erf) [4096, 4096] fp16", n, 2 * T * FFN * 2,
                   lambda i: K.bias_act(hs[i], ho[i], bias=bias_f, act=L.EPI_GELU)))
+    # the same three kernels on 8 x the rows (a batch of 64 sequences): launches long enough for the launch ramp not to count
+    n, big = 3, 8 * T
+    xb, rb, yb = ([rnd(big, HIDDEN) for _ in range(n)], [rnd(big, HIDDEN) for _ in range(n)],
+                  [torch.empty(big, HIDDEN, dtype=torch.float16, device=dev) for _ in range(n)])
+    cases.append(("layernorm_warp_kernel", "LayerNorm(x + bias + residual) [32768, 1024] fp16", n, 3 * big * HIDDEN * 2,
+                  lambda i: K.layernorm(xb[i], yb[i], gamma=gamma, beta=beta, residual=rb[i], bias=bias_h, eps=1e-12)))
+    cases.append(("binary_fast_kernel", "residual add [32768, 1024] fp16", n, 3 * big * HIDDEN * 2,
+                  lambda i: K.binary(xb[i], rb[i], yb[i], L.BIN_ADD)))
+    hb, hob = [rnd(big // 2, FFN) for _ in range(n)], [torch.empty(big // 2, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
+    cases.append(("bias_act_kernel", "bias + GELU(erf) [16384, 4096] fp16", n, 2 * (big // 2) * FFN * 2,
+                  lambda i: K.bias_act(hb[i], hob[i], bias=bias_f, act=L.EPI_GELU)))
     # data movement: the packed QKV tensor split into its three parts (Slice on the last axis), the head-merge of two
     # halves (Concat), an embedding lookup (Gather of 1024-wide rows) and a mask select (Where)
     n = 6  # 6 x 50 MB
