@@ -24,26 +24,36 @@ template <typename E>
 __global__ void __launch_bounds__(256) strided_copy_kernel(const E* __restrict__ x, E* __restrict__ y, uint64_t total,
                                                            const CopyGeom g) {
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        uint64_t rem = i;
-        int64_t xo = 0, yo = 0;
+    // two units per thread and step: both loads are issued before the first store
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 2 * stride) {
+        int64_t xo[2], yo[2];
+        const bool second = i + stride < total;
 #pragma unroll
-        for (int d = MAXR - 1; d >= 0; --d) {
-            if (d < g.rank) {
-                uint64_t c;
-                if (rem < (1ull << 32)) {  // 32-bit division once the remainder fits (always, after the first step or two)
-                    const uint32_t r32 = static_cast<uint32_t>(rem);
-                    c = r32 % g.shape[d];
-                    rem = r32 / g.shape[d];
-                } else {
-                    c = rem % g.shape[d];
-                    rem = rem / g.shape[d];
+        for (int u = 0; u < 2; ++u) {
+            uint64_t rem = i + u * stride;
+            xo[u] = 0, yo[u] = 0;
+#pragma unroll
+            for (int d = MAXR - 1; d >= 0; --d) {
+                if (d < g.rank) {
+                    uint64_t c;
+                    if (rem < (1ull << 32)) {  // 32-bit division once the remainder fits (always, after the first step or two)
+                        const uint32_t r32 = static_cast<uint32_t>(rem);
+                        c = r32 % g.shape[d];
+                        rem = r32 / g.shape[d];
+                    } else {
+                        c = rem % g.shape[d];
+                        rem = rem / g.shape[d];
+                    }
+                    xo[u] += static_cast<int64_t>(c) * g.xs[d];
+                    yo[u] += static_cast<int64_t>(c) * g.ys[d];
                 }
-                xo += static_cast<int64_t>(c) * g.xs[d];
-                yo += static_cast<int64_t>(c) * g.ys[d];
             }
         }
-        y[yo] = x[xo];
+        const E v0 = x[xo[0]];
+        E v1 = E();
+        if (second) v1 = x[xo[1]];
+        y[yo[0]] = v0;
+        if (second) y[yo[1]] = v1;
     }
 }
 
@@ -251,7 +261,7 @@ unsigned grid_for(const b200ml_ctx* ctx, uint64_t total) {
 
 template <typename E>
 int launch_copy(const b200ml_ctx* ctx, const void* x, void* y, uint64_t total, const CopyGeom& g, cudaStream_t s) {
-    strided_copy_kernel<E><<<grid_for(ctx, total), 256, 0, s>>>(static_cast<const E*>(x), static_cast<E*>(y), total, g);
+    strided_copy_kernel<E><<<grid_for(ctx, (total + 1) / 2), 256, 0, s>>>(static_cast<const E*>(x), static_cast<E*>(y), total, g);
     return check_launch("strided_copy");
 }
 
