@@ -338,6 +338,91 @@ __global__ void __launch_bounds__(256) depthwise3x3_kernel(const float* __restri
     }
 }
 
+// 3x3, unit stride, pad 1 on every side, width a multiple of 4 up to 64: a lane owns FOUR adjacent output columns of a
+// strip of rows.  Per input row it issues one 16-byte load; the two halo columns come from the neighbouring lanes by
+// shuffle (zero at the plane's edges), so four outputs cost one load, two shuffles, 36 multiply-adds and one 16-byte
+// store - a quarter of the instructions of the column-per-lane kernel above, which is bound by instruction issue.
+// One warp per plane: LPR = w / 4 lanes cover a row, 32 / LPR strips of rows share the warp.
+__global__ void __launch_bounds__(128) depthwise3x3_quad_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                const float* __restrict__ bias, float* __restrict__ y,
+                                                                float* __restrict__ pool_mean, const ConvGeom g,
+                                                                int64_t planes) {
+    const int lane = threadIdx.x & 31;
+    const int64_t plane = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    if (plane >= planes) return;  // whole warps leave; no block-wide barrier below
+    const int ch = static_cast<int>(plane % g.c);
+    const int64_t img = plane / g.c;
+    const int lpr = g.w >> 2;            // lanes per row
+    const int strips = 32 / lpr;         // row strips per warp
+    const int strip = lane / lpr, q = lane - strip * lpr;
+    const bool active = strip < strips;
+    const int rows_per = (g.h + strips - 1) / strips;
+    const int oy0 = strip * rows_per;
+    const int oy1 = active ? (oy0 + rows_per < g.h ? oy0 + rows_per : g.h) : oy0;
+    const float4* xp = reinterpret_cast<const float4*>(x + (img * g.c + ch) * static_cast<int64_t>(g.h) * g.w) + q;
+    float4* yp = reinterpret_cast<float4*>(y + (img * g.m + ch) * static_cast<int64_t>(g.h) * g.w) + q;
+    float t[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) t[i] = __ldg(w + ch * 9 + i);
+    const float b = bias ? __ldg(bias + ch) : 0.0f;
+
+    // a row as this lane sees it: left halo, four own columns, right halo
+    struct Row { float v[6]; };
+    auto fetch = [&](int iy) -> float4 {
+        return (active && iy >= 0 && iy < g.h) ? __ldg(xp + static_cast<int64_t>(iy) * lpr) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto finish = [&](const float4& c) -> Row {
+        Row r;
+        // every lane takes part in the shuffles (inactive lanes hold zeros); edges of the plane read the padding
+        const float left = __shfl_up_sync(0xffffffffu, c.w, 1);
+        const float right = __shfl_down_sync(0xffffffffu, c.x, 1);
+        r.v[0] = q == 0 ? 0.0f : left;
+        r.v[1] = c.x, r.v[2] = c.y, r.v[3] = c.z, r.v[4] = c.w;
+        r.v[5] = q == lpr - 1 ? 0.0f : right;
+        return r;
+    };
+    auto output = [&](const Row& r0, const Row& r1, const Row& r2) -> float4 {
+        float o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float acc = b;
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                acc = fmaf(t[j], r0.v[k + j], acc);
+                acc = fmaf(t[3 + j], r1.v[k + j], acc);
+                acc = fmaf(t[6 + j], r2.v[k + j], acc);
+            }
+            o[k] = conv_act(acc, g.act);
+        }
+        return make_float4(o[0], o[1], o[2], o[3]);
+    };
+
+    // the strips of a warp have the same number of steps (rows_per), so the shuffles stay warp-uniform
+    Row ra = finish(fetch(oy0 - 1)), rb = finish(fetch(oy0));
+    float local = 0.0f;
+    for (int k = 0; k < rows_per; k += 2) {
+        const int oy = oy0 + k;
+        const float4 c0 = fetch(oy + 1), c1 = fetch(oy + 2);  // both loads in flight before the first multiply
+        const Row rc = finish(c0), rd = finish(c1);
+        if (oy < oy1) {
+            const float4 o = output(ra, rb, rc);
+            yp[static_cast<int64_t>(oy) * lpr] = o;
+            local += (o.x + o.y) + (o.z + o.w);
+        }
+        if (oy + 1 < oy1) {
+            const float4 o = output(rb, rc, rd);
+            yp[static_cast<int64_t>(oy + 1) * lpr] = o;
+            local += (o.x + o.y) + (o.z + o.w);
+        }
+        ra = rc, rb = rd;
+    }
+    if (pool_mean) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if (lane == 0) pool_mean[img * g.m + ch] = local / (g.h * g.w);
+    }
+}
+
 // Any kernel size up to 64 taps: the plane and its halo staged in shared memory.  Warps walk rows and lanes walk
 // columns, so no index needs a division.
 __global__ void __launch_bounds__(256) depthwise_plane_kernel(const float* __restrict__ x, const float* __restrict__ w,
@@ -494,7 +579,11 @@ static int conv2d_fast(const b200ml_ctx*, const b200ml_conv_params* p, const Con
     if (unit && p->group == p->c && p->m == p->c && !gt && !r && p->kh * p->kw <= 64) {
         const size_t sm = (size_t)(g.oh + p->kh - 1) * (g.ow + p->kw - 1) * sizeof(float);
         if (sm <= 40 * 1024 && p->n * p->c < (1ll << 31)) {
-            if (p->kh == 3 && p->kw == 3 && g.ow <= 64) depthwise3x3_kernel<<<(unsigned)(p->n * p->c), 256, 0, s>>>(x, w, b, y, p->pool_sum, g);
+            const bool pad1 = p->pad_top == 1 && p->pad_left == 1 && p->pad_bottom == 1 && p->pad_right == 1;
+            if (p->kh == 3 && p->kw == 3 && pad1 && p->w % 4 == 0 && p->w >= 8 && p->w <= 64 && aligned16(x) && aligned16(y)) {
+                const int64_t planes = p->n * p->c;
+                depthwise3x3_quad_kernel<<<(unsigned)ceil_div(planes, 4), 128, 0, s>>>(x, w, b, y, p->pool_sum, g, planes);
+            } else if (p->kh == 3 && p->kw == 3 && g.ow <= 64) depthwise3x3_kernel<<<(unsigned)(p->n * p->c), 256, 0, s>>>(x, w, b, y, p->pool_sum, g);
             else depthwise_plane_kernel<<<(unsigned)(p->n * p->c), 256, sm, s>>>(x, w, b, y, p->pool_sum, g);
             *launched = true;
             *pooled = true;

@@ -413,6 +413,26 @@ def test_conv_pointwise(cin, cout, hw, rng):
     assert_close(y, ops.conv2d(x, w, b), what=f"1x1 conv {cin}->{cout}")
 
 
+@pytest.mark.parametrize("c, hw, pads", [(144, (56, 56), (1, 1, 1, 1)), (5, (7, 8), (1, 1, 1, 1)), (3, (13, 12), (1, 1, 1, 1)), (6, (33, 64), (1, 1, 1, 1)),
+                                         (4, (1, 16), (1, 1, 1, 1)), (5, (9, 10), (1, 1, 1, 1)), (4, (12, 12), (0, 1, 1, 0)), (2, (70, 72), (1, 1, 1, 1))])
+@pytest.mark.parametrize("act", ["", "Swish"])
+def test_depthwise_3x3_forms(c, hw, pads, act, rng):
+    """Depthwise 3x3 on the four-columns-per-lane kernel (pad 1, width a multiple of 4 up to 64), on the
+    column-per-lane kernel (other widths and pads) and on the staged kernel (wide planes), with the pooled mean."""
+    x = rng.standard_normal((3, c) + hw).astype(np.float32)
+    w = (rng.standard_normal((c, 1, 3, 3)) * 0.3).astype(np.float32)
+    b = rng.standard_normal(c).astype(np.float32)
+    ref = ops.conv2d(x, w, b, pads=pads, group=c)
+    if act:
+        ref = ops.swish(ref)
+    y = empty(ref.shape, torch.float32)
+    pool = empty((3, c, 1, 1), torch.float32)
+    donnx.ONNXFusedConv(X=dev(x), W=dev(w), B=dev(b), Y=y, Pool=pool, pads=list(pads), group=c, activation=act)
+    assert_close(y, ref, what=f"depthwise {hw} {pads} {act}", atol=2e-5)
+    assert_close(pool, ref.mean(axis=(2, 3), keepdims=True), what="pooled mean", atol=2e-5)
+    status_ok()
+
+
 # ------------------------------------------------------------------------------------------------
 # Edge cases of the C ABI
 # ------------------------------------------------------------------------------------------------
