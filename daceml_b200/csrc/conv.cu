@@ -203,6 +203,11 @@ __global__ void __launch_bounds__(128) pointwise_x_kernel(const float* __restric
 // ---------------------------------------------------------------------------------------------
 // 1x1 convolution, few output channels per pass (MP <= 32): accumulators in registers, loop over C
 // ---------------------------------------------------------------------------------------------
+constexpr int ACC_CH = 4;      // input channels per ring stage
+constexpr int ACC_STAGES = 4;  // ring depth: 3 x 4 loads of 16 bytes in flight per thread
+constexpr size_t ACC_SMEM_LIMIT = 96 * 1024;  // weights of one pass (c x MP floats) + the rings
+constexpr size_t ACC_RING_BYTES = static_cast<size_t>(ACC_STAGES) * ACC_CH * 128 * sizeof(float4);
+
 template <int MP>  // output channels per pass, multiple of 4
 __global__ void __launch_bounds__(128) pointwise_acc_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                             const float* __restrict__ bias,
@@ -228,25 +233,51 @@ __global__ void __launch_bounds__(128) pointwise_acc_kernel(const float* __restr
         const float b = (bias && m0 + mm < m) ? __ldg(bias + m0 + mm) : 0.0f;
         acc[mm] = make_float4(b, b, b, b);
     }
-#pragma unroll 2
-    for (int cc = 0; cc < c; ++cc) {
-        float4 xx = __ldg(xp + static_cast<int64_t>(cc) * p4);
-        if (gp) {
-            const float gt = __ldg(gp + cc);
-            xx.x *= gt, xx.y *= gt, xx.z *= gt, xx.w *= gt;
+    // The accumulators take the registers, so the loads of X run ahead through shared memory instead: every thread owns
+    // a ring of ACC_STAGES x ACC_CH 16-byte slots that it fills with cp.async and reads back itself (no barrier), which
+    // keeps (ACC_STAGES - 1) * ACC_CH loads per thread in flight whatever the occupancy.
+    float4* ring = reinterpret_cast<float4*>(wsm + ((c * MP + 3) & ~3)) + threadIdx.x;
+    auto issue = [&](int chunk) {
+        const int slot = (chunk % ACC_STAGES) * ACC_CH;
+#pragma unroll
+        for (int k = 0; k < ACC_CH; ++k) {
+            const int cc = chunk * ACC_CH + k;
+            if (cc < c) {
+                const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(ring + (slot + k) * 128));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xp + static_cast<int64_t>(cc) * p4) : "memory");
+            }
         }
-        const float4* wr = reinterpret_cast<const float4*>(wsm + cc * MP);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int chunks = (c + ACC_CH - 1) / ACC_CH;
 #pragma unroll
-        for (int m4 = 0; m4 < MP / 4; ++m4) {
-            const float4 wv = wr[m4];
-            const float ws[4] = {wv.x, wv.y, wv.z, wv.w};
+    for (int pre = 0; pre < ACC_STAGES - 1; ++pre) issue(pre);  // chunks beyond the end commit empty groups
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        issue(chunk + ACC_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(ACC_STAGES - 1) : "memory");
+        const int slot = (chunk % ACC_STAGES) * ACC_CH;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                float4& a = acc[m4 * 4 + t];
-                a.x = fmaf(ws[t], xx.x, a.x);
-                a.y = fmaf(ws[t], xx.y, a.y);
-                a.z = fmaf(ws[t], xx.z, a.z);
-                a.w = fmaf(ws[t], xx.w, a.w);
+        for (int k = 0; k < ACC_CH; ++k) {
+            const int cc = chunk * ACC_CH + k;
+            if (cc >= c) break;
+            float4 xx = ring[(slot + k) * 128];
+            if (gp) {
+                const float gt = __ldg(gp + cc);
+                xx.x *= gt, xx.y *= gt, xx.z *= gt, xx.w *= gt;
+            }
+            const float4* wr = reinterpret_cast<const float4*>(wsm + cc * MP);
+#pragma unroll
+            for (int m4 = 0; m4 < MP / 4; ++m4) {
+                const float4 wv = wr[m4];
+                const float ws[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    float4& a = acc[m4 * 4 + t];
+                    a.x = fmaf(ws[t], xx.x, a.x);
+                    a.y = fmaf(ws[t], xx.y, a.y);
+                    a.z = fmaf(ws[t], xx.z, a.z);
+                    a.w = fmaf(ws[t], xx.w, a.w);
+                }
             }
         }
     }
@@ -562,8 +593,17 @@ static int conv2d_fast(const b200ml_ctx*, const b200ml_conv_params* p, const Con
                 }
             }
             const int mp = m <= 8 ? 8 : (m <= 16 ? 16 : (m <= 24 ? 24 : 32));
-            const size_t sm = (size_t)c * mp * sizeof(float);
-            if (sm <= 48 * 1024) {
+            const size_t sm = (((size_t)c * mp + 3) & ~(size_t)3) * sizeof(float) + ACC_RING_BYTES;  // weights + the X rings
+            if (sm <= ACC_SMEM_LIMIT) {
+                static const bool opted_in = [] {  // dynamic shared memory above 48 KB has to be asked for, once per kernel
+                    bool ok = true;
+                    ok &= cudaFuncSetAttribute(pointwise_acc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ACC_SMEM_LIMIT) == cudaSuccess;
+                    ok &= cudaFuncSetAttribute(pointwise_acc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ACC_SMEM_LIMIT) == cudaSuccess;
+                    ok &= cudaFuncSetAttribute(pointwise_acc_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ACC_SMEM_LIMIT) == cudaSuccess;
+                    ok &= cudaFuncSetAttribute(pointwise_acc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ACC_SMEM_LIMIT) == cudaSuccess;
+                    return ok;
+                }();
+                if (!opted_in && sm > 48 * 1024) return fail(B200ML_ERR_CUDA, "conv: cannot reserve %zu bytes of shared memory", sm);
                 const dim3 grid(gx, (unsigned)ceil_div(m, mp));
                 switch (mp) {
                     case 8: pointwise_acc_kernel<8><<<grid, 128, sm, s>>>(x, w, b, gt, r, y, total4, p4, c, m, p->act); break;
