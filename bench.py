@@ -608,57 +608,10 @@ def main():
                 ev_out[j] = torch.cuda.Event()
                 ev_out[j].record(s_out)
 
-    # The whole pipeline (copies from and to pinned host memory included) is captured in one CUDA graph, so that the host's
-    # own work per step (a dozen Python calls) is not what gets timed; if the capture is refused, the steps are issued one
-    # by one as above.
-    def e2e_eager_layers(n):
-        ev_in, ev_cmp, ev_out = [None] * depth, [None] * depth, [None] * depth
-        for i in range(n):
-            j = i % depth
-            with torch.cuda.stream(s_in):
-                if ev_cmp[j] is not None:
-                    s_in.wait_event(ev_cmp[j])
-                din[j].copy_(hin[j], non_blocking=True)
-                ev_in[j] = torch.cuda.Event()
-                ev_in[j].record(s_in)
-            with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in[j])
-                if ev_out[j] is not None:
-                    s_cmp.wait_event(ev_out[j])
-                layers[j % LAYERS](**{"input": din[j], "__return": dout[j]})
-                ev_cmp[j] = torch.cuda.Event()
-                ev_cmp[j].record(s_cmp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[j])
-                hout[j].copy_(dout[j], non_blocking=True)
-                ev_out[j] = torch.cuda.Event()
-                ev_out[j].record(s_out)
-
     e2e_pass(depth * 2)
-    torch.cuda.synchronize()
-    e2e_graph = None
-    try:
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=s_cmp):
-            fork = torch.cuda.Event()
-            fork.record(s_cmp)
-            s_in.wait_event(fork)   # the copy streams join the capture
-            s_out.wait_event(fork)
-            e2e_eager_layers(n_e2e)
-            s_cmp.wait_stream(s_in)
-            s_cmp.wait_stream(s_out)
-        g.replay()
-        torch.cuda.synchronize()
-        e2e_graph = g
-    except Exception as exc:  # capture of host copies on side streams refused: time the eager pipeline
-        sys.stderr.write("e2e: CUDA graph capture of the pipeline failed (%s); timing the eager pipeline\n" % exc)
-        torch.cuda.synchronize()
     barrier()
     t0 = time.perf_counter()
-    if e2e_graph is not None:
-        e2e_graph.replay()
-    else:
-        e2e_pass(n_e2e)
+    e2e_pass(n_e2e)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     if world > 1:
@@ -667,8 +620,7 @@ def main():
         e2e_s = float(te)
     nbytes = BATCH * SEQ * HIDDEN * 2
     e2e = {"value": world * BATCH * n_e2e / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-           "steps": n_e2e, "pipeline": "3 buffers; copy-in, layer and copy-out on separate streams" +
-           ("; the n steps captured in one CUDA graph" if e2e_graph is not None else "; issued step by step")}
+           "steps": n_e2e, "pipeline": "3 buffers; copy-in, layer and copy-out on separate streams"}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only) ----
     cpu = None
