@@ -608,19 +608,26 @@ def main():
                 ev_out[j] = torch.cuda.Event()
                 ev_out[j].record(s_out)
 
+    # three timed passes, the median reported: on these hosts the pipeline settles into one of two states from pass to pass
+    # (about 175 or 222 us per step; PCIe copies in both directions under the layer's HBM traffic)
     e2e_pass(depth * 2)
-    barrier()
-    t0 = time.perf_counter()
-    e2e_pass(n_e2e)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        te = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_s = float(te)
+    e2e_runs = []
+    for _ in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        e2e_pass(n_e2e)
+        torch.cuda.synchronize()
+        t = time.perf_counter() - t0
+        if world > 1:
+            te = torch.tensor([t], device=dev)
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            t = float(te)
+        e2e_runs.append(t)
+    e2e_s = sorted(e2e_runs)[1]
     nbytes = BATCH * SEQ * HIDDEN * 2
     e2e = {"value": world * BATCH * n_e2e / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-           "steps": n_e2e, "pipeline": "3 buffers; copy-in, layer and copy-out on separate streams"}
+           "steps": n_e2e, "pipeline": "3 buffers; copy-in, layer and copy-out on separate streams",
+           "passes_samples_per_s": [round(world * BATCH * n_e2e / t) for t in e2e_runs], "reported": "median of 3 passes"}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only) ----
     cpu = None
