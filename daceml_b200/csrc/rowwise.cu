@@ -215,6 +215,34 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const T* __restrict_
     }
 }
 
+// Short rows that the packet kernels cannot take (a length that is not a multiple of the packet, e.g. the 10 classes of
+// a classifier head): LPR lanes share a row and a warp takes 32 / LPR rows, scalar loads served by the L1.  One block per
+// row, the general fallback below, would launch thousands of nearly empty blocks for such a tensor.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_short_kernel(const T* __restrict__ x, const T* __restrict__ mask,
+                                                            T* __restrict__ y, int64_t rows, int cols, int64_t mask_row_div,
+                                                            float scale, int is_log, int lpr) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane / lpr, l = lane - sub * lpr;
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * 8 + warp) * (32 / lpr) + sub;
+    const bool valid = row < rows;  // lanes of rows past the end still take part in the shuffles
+    const T* xr = x + (valid ? row : 0) * cols;
+    const T* mr = mask ? mask + ((valid ? row : 0) / mask_row_div) * cols : nullptr;
+    float mx = -FLT_MAX;
+    for (int c = l; c < cols; c += lpr) mx = fmaxf(mx, ld1(xr + c) * scale + (mr ? ld1(mr + c) : 0.0f));
+    for (int o = lpr >> 1; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+    for (int c = l; c < cols; c += lpr) sum += softmax_exp<T>(ld1(xr + c) * scale + (mr ? ld1(mr + c) : 0.0f) - mx);
+    for (int o = lpr >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (!valid) return;
+    const float inv = 1.0f / sum, lse = logf(sum);
+    T* yr = y + row * cols;
+    for (int c = l; c < cols; c += lpr) {
+        const float d = ld1(xr + c) * scale + (mr ? ld1(mr + c) : 0.0f) - mx;
+        st1(yr + c, is_log ? d - lse : softmax_exp<T>(d) * inv);
+    }
+}
+
 template <typename T>
 int softmax_t(const T* x, const T* mask, T* y, int64_t rows, int64_t cols, int64_t mask_row_div, float scale,
               int is_log, cudaStream_t stream) {
@@ -237,6 +265,14 @@ int softmax_t(const T* x, const T* mask, T* y, int64_t rows, int64_t cols, int64
         else SM_LAUNCH(8, 1);
 #undef SM_LAUNCH
         return check_launch("softmax_warp");
+    }
+    if (cols <= 256) {
+        int lpr = 4;
+        while (lpr < 32 && lpr < cols) lpr <<= 1;
+        const int64_t blocks = ceil_div(rows, (int64_t)8 * (32 / lpr));
+        B200ML_REQUIRE(blocks < (1ll << 31), "softmax: too many rows");
+        softmax_short_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(x, mask, y, rows, (int)cols, mask_row_div, scale, is_log, lpr);
+        return check_launch("softmax_short");
     }
     B200ML_REQUIRE(rows < (1ll << 31), "softmax: too many rows");
     softmax_block_kernel<T><<<(unsigned)rows, 256, 0, stream>>>(x, mask, y, cols, mask_row_div, scale, is_log);

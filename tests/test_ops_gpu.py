@@ -198,6 +198,22 @@ def test_softmax_shapes(dtype, shape, axis, rng):
     assert_close(y, ops.softmax(rounded(x, dtype), axis), dtype, what=f"softmax {shape}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, cols", [(4096, 10), (37, 3), (5, 100), (33, 255), (9, 17), (64, 2)])
+def test_softmax_short_rows_with_scale_mask_and_log(dtype, rows, cols, rng):
+    """Rows the packet kernels cannot take (classifier heads): several lanes per row, several rows per warp."""
+    x = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+    m = (rng.standard_normal((rows, cols)) * 2).astype(np.float32)
+    xd, md = dev(x, dtype), dev(m, dtype)
+    xr, mr = rounded(x, dtype), rounded(m, dtype)
+    y = empty((rows, cols), dtype)
+    K.softmax(xd, y, rows=rows, cols=cols, scale=0.5, mask=md)
+    assert_close(y, ops.softmax(xr * np.float32(0.5) + mr, 1), dtype, what="short softmax with scale and mask")
+    K.softmax(xd, y, rows=rows, cols=cols, log=True)
+    assert_close(y, ops.log_softmax(xr, 1), dtype, atol=1e-2 if dtype == torch.float16 else None, what="short log-softmax")
+    status_ok()
+
+
 @pytest.mark.parametrize("kind, keep, axes", [("Sum", True, [0]), ("Sum", False, [-1]), ("Sum", True, [0, -1]), ("Max", False, [0, -1]),
                                               ("Max", True, [0]), ("Max", True, [-1]), ("Mean", True, [-1]), ("Mean", True, [0, -1]),
                                               ("Mean", False, [0]), ("Min", True, [1])])
