@@ -149,6 +149,25 @@ def test_gemm_linear_export(dtype, rng):
     assert_close(y, ref, dtype, what="gemm linear")
 
 
+@pytest.mark.parametrize("m, n, k", [(4096, 32, 120), (4096, 10, 32), (300, 1, 4), (257, 17, 64), (1000, 24, 300), (512, 8, 8)])
+@pytest.mark.parametrize("trans_b", [0, 1])
+def test_gemm_skinny_outputs(m, n, k, trans_b, rng):
+    """fp32 products with few output columns (classifier heads, the last layers of the MLP; up to 16 columns take the
+    kernel that keeps all of B in shared memory): bias, ReLU and both weight layouts, against the oracle in fp64 terms."""
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k) if trans_b else (k, n)) * 0.1).astype(np.float32)
+    c = rng.standard_normal(n).astype(np.float32)
+    ref = ops.gemm(a, w, c, trans_b=trans_b, acc_dtype=np.float64)
+    y = empty((m, n), torch.float32)
+    donnx.ONNXGemm(A=dev(a), B=dev(w), C=dev(c), Y=y, transB=trans_b)
+    assert_close(y, ref, what=f"skinny gemm {m}x{n}x{k}")
+    yr = empty((m, n), torch.float32)
+    K.gemm(dev(a), dev(w), yr, b_layout=trans_b, bias=dev(c), act=L.EPI_RELU, residual=y, alpha=0.5)
+    want = np.maximum(0.5 * (a.astype(np.float64) @ (w.T if trans_b else w).astype(np.float64)) + c, 0.0) + y.cpu().numpy()
+    assert_close(yr, want.astype(np.float32), what="skinny gemm with bias, ReLU, residual")
+    status_ok()
+
+
 def test_einsum_reference_test():
     """tests/pure_expansions/test_expansions.py:387-405 ('bij, jk -> bik')."""
     g = gold("einsum")
