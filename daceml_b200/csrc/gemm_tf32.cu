@@ -56,11 +56,26 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, ui
 }
 
 // hi = x rounded to nearest-even at 10 mantissa bits (TF32), lo = x - hi; rows of `cols` elements, source rows `ld` apart.
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
-                                                         int64_t rows, int64_t cols, int64_t ld) {
-    const int64_t n4 = rows * (cols / 4);
+// One launch splits both operands of a product: the first `a_blocks` blocks take A, the others B.
+struct SplitOperand {
+    const float* x;
+    float* hi;
+    float* lo;
+    int64_t rows, ld;
+};
+
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitOperand oa, const SplitOperand ob, int64_t cols, unsigned a_blocks) {
+    const bool first = blockIdx.x < a_blocks;
+    const SplitOperand& o = first ? oa : ob;
+    const float* __restrict__ x = o.x;
+    float* __restrict__ hi = o.hi;
+    float* __restrict__ lo = o.lo;
+    const int64_t ld = o.ld;
+    const int64_t n4 = o.rows * (cols / 4);
     const int64_t per_row = cols / 4;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t block = first ? blockIdx.x : blockIdx.x - a_blocks;
+    const int64_t nblocks = first ? a_blocks : gridDim.x - a_blocks;
+    for (int64_t i = block * blockDim.x + threadIdx.x; i < n4; i += nblocks * blockDim.x) {
         const int64_t r = i / per_row, c4 = i - r * per_row;
         const float4 v = __ldg(reinterpret_cast<const float4*>(x + r * ld) + c4);
         const float in[4] = {v.x, v.y, v.z, v.w};
@@ -338,8 +353,10 @@ int gemm_f32_tensor_core(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cud
         const int64_t cap = static_cast<int64_t>(ctx->sm_count) * 16;
         return static_cast<unsigned>(b < 1 ? 1 : (b > cap ? cap : b));
     };
-    split_tf32_kernel<<<blocks(p->m * p->k), 256, 0, stream>>>(static_cast<const float*>(p->a), a_hi, a_lo, p->m, p->k, p->lda);
-    split_tf32_kernel<<<blocks(p->n * p->k), 256, 0, stream>>>(static_cast<const float*>(p->b), b_hi, b_lo, p->n, p->k, p->ldb);
+    const unsigned ba = blocks(p->m * p->k), bb = blocks(p->n * p->k);
+    const SplitOperand oa{static_cast<const float*>(p->a), a_hi, a_lo, p->m, p->lda};
+    const SplitOperand ob{static_cast<const float*>(p->b), b_hi, b_lo, p->n, p->ldb};
+    split_tf32_kernel<<<ba + bb, 256, 0, stream>>>(oa, ob, p->k, ba);
     int rc = check_launch("split_tf32");
     if (rc) return rc;
 
