@@ -117,6 +117,22 @@ def test_module_is_registered_as_a_torch_operator():
     assert a.shape == b.shape == (4, )
 
 
+def test_parameter_to_transient_is_accepted():
+    """tests/torch/test_bert_encoder.py:26-31 registers this as a post-ONNX hook for every parameter on the GPU."""
+    from daceml_b200.transformation import parameter_to_transient
+    m = DaceModule(MLP())
+
+    def param_to_trans(model):
+        for name, _ in model.model.named_parameters():
+            parameter_to_transient(model, name)
+
+    m.append_post_onnx_hook("param_to_transient", param_to_trans)
+    m.function = m._initialize_sdfg((torch.randn(8, 784), ))
+    assert m.compiled_function.kernel_names() == ["gemm", "gemm", "gemm", "softmax"]
+    with pytest.raises(AttributeError):
+        parameter_to_transient(m, "no.such.weight")
+
+
 def test_debug_transients_become_outputs():
     m = DaceModule(MLP(), dummy_inputs=(torch.randn(8, 784), ), auto_optimize=False, debug_transients=True)
     assert len(m.dace_model.outputs) == 6 and not any(d.transient for d in m.sdfg.arrays.values())
