@@ -488,3 +488,22 @@ def test_invalid_arguments_raise():
         K.unary(torch.zeros(4), torch.zeros(4), L.UN_RELU)  # CPU tensors: no CPU path
     with pytest.raises(L.Unsupported):
         K.unary(empty((4, ), torch.float64), empty((4, ), torch.float64), L.UN_RELU)
+
+
+# ------------------------------------------------------------------------------------------------
+# Every case of tests/golden/ref_pure_expansions.*: vectors computed by the reference's own source
+# (pure_implementations.py / img_op_implementations.py executed under numpy) against the CUDA path
+# ------------------------------------------------------------------------------------------------
+import ref_cases  # noqa: E402
+
+
+@pytest.mark.parametrize("case", ref_cases.REF_CASES, ids=[c["case"] for c in ref_cases.REF_CASES])
+def test_kernels_match_reference_source(case):
+    results = ref_cases.frontend_outputs(case, ref_cases.ref_arrays(), donnx, torch)
+    for conn, (got, want) in results.items():
+        assert got.shape == want.shape and got.dtype == want.dtype, (conn, got.shape, want.shape, got.dtype, want.dtype)
+        if case["op"] in ref_cases.BIT_EXACT_OPS or not np.issubdtype(want.dtype, np.floating):
+            assert np.array_equal(got, want), f"{case['case']}:{conn} is not bit-exact"
+        else:
+            assert_close(got, want, torch.float32, what=f"{case['case']}:{conn}")
+    status_ok()

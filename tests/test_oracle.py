@@ -153,3 +153,36 @@ def test_data_movement_reference_cases():
     assert np.array_equal(ops.maxpool2d(img, (2, 2), (2, 2)), F.max_pool2d(torch.from_numpy(img), 2, 2).numpy())
     assert np.array_equal(ops.maxpool2d(img, (3, 2), (2, 1), (1, 1, 1, 1)),
                           F.max_pool2d(torch.from_numpy(img), (3, 2), (2, 1), padding=(1, 1)).numpy())
+
+
+# ------------------------------------------------------------------------------------------------
+# The oracle against outputs of the reference's own source: tests/golden/ref_pure_expansions.* hold
+# what pure_implementations.py / img_op_implementations.py compute when their bodies are executed
+# under numpy (tests/golden/generate_from_reference.py).
+# ------------------------------------------------------------------------------------------------
+import ref_cases  # noqa: E402
+from ref_cases import REF_CASES, ref_arrays, oracle_outputs  # noqa: E402
+
+
+@pytest.mark.parametrize("case", REF_CASES, ids=[c["case"] for c in REF_CASES])
+def test_oracle_matches_reference_source(case):
+    arrays = ref_arrays()
+    got = oracle_outputs(case, arrays)
+    assert set(got) == set(case["outputs"])
+    for conn, value in got.items():
+        want = arrays["%s:%s" % (case["case"], conn)]
+        assert value.shape == want.shape and value.dtype == want.dtype, (conn, value.shape, want.shape, value.dtype, want.dtype)
+        if not np.issubdtype(want.dtype, np.floating) or case["op"] in ref_cases.BIT_EXACT_OPS:
+            assert np.array_equal(value, want), conn
+        else:
+            # the same arithmetic in the same type; only the order of a reduction's additions (numpy pairwise against
+            # np.einsum / sequential) and libm-vs-numpy rounding of exp / erf / tanh may differ: a few ulp
+            np.testing.assert_allclose(value, want, rtol=2e-6, atol=1e-6 * max(1.0, float(np.abs(want).max())))
+
+
+def test_reference_chains_match_oracle_graphs():
+    """The decomposed LayerNorm and GELU sub-graphs, evaluated node by node with the reference's bodies."""
+    a = ref_arrays()
+    ln = ops.layernorm_chain(a["layernorm_chain:x"], a["layernorm_chain:gamma"], a["layernorm_chain:beta"], eps=1e-12)
+    np.testing.assert_allclose(ln, a["layernorm_chain:y"], rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(ops.gelu_chain(a["gelu_chain:x"]), a["gelu_chain:y"], rtol=2e-6, atol=1e-6)
