@@ -653,8 +653,8 @@ int conv2d(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t s) {
         if (rc) return rc;
     }
     if (p->pool_sum && !pooled) {
-        B200ML_REQUIRE(p->dtype == B200ML_F32, "conv: fused GlobalAveragePool needs fp32 tensors");
-        return reduce(ctx, B200ML_F32, B200ML_RED_MEAN, p->y, p->pool_sum, p->n * p->m, oh * ow, 1, s);
+        // no specialised kernel wrote the pool: the mean of every output plane, in the tensors' own type
+        return reduce(ctx, p->dtype, B200ML_RED_MEAN, p->y, p->pool_sum, p->n * p->m, oh * ow, 1, s);
     }
     return B200ML_OK;
 }

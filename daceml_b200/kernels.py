@@ -309,6 +309,9 @@ def attention(q, k, v, out, *, scale, mask=None):
     p.o_stride_b, p.o_stride_h, p.o_stride_s = out.stride(0), out.stride(1), out.stride(2)
     p.scale = scale
     p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    if mask is not None and (mask.dtype != torch.float16 or mask.numel() != p.batch * p.seq_kv or not mask.is_contiguous()):
+        raise L.B200Error(L.ERR_INVALID, "attention: the additive mask must be %d x %d contiguous float16 values, got %s %s"
+                          % (p.batch, p.seq_kv, tuple(mask.shape), mask.dtype))
     p.mask = mask.data_ptr() if mask is not None else None
     L.check(ctx.lib.b200ml_attention_f16(ctx.handle, ctypes.byref(p), _stream(q)))
     return out

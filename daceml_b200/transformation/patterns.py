@@ -369,17 +369,25 @@ def fuse_attention(sdfg, state):
         chain, mask = [sm], None
         prev = _producer(state, scores)
         if prev is not None and type(prev) is donnx.ONNXAdd and _only_consumer(sdfg, state, scores)[0] is sm:
-            # additive mask: a [B, S] constant reshaped to [B, 1, 1, S] ...
+            # additive mask: a [B, S_kv] constant of the scores' type reshaped to [B, 1, 1, S_kv] (the layout the kernel
+            # reads); a [1, S] row broadcast over the batch, an [S, S] causal or relative-bias constant and anything
+            # else stay an Add in front of the Softmax
             a, b = _in(state, prev, "A"), _in(state, prev, "B")
+            shp = sdfg.arrays[scores].shape
             cand = [t for t in (a, b) if _producer(state, t) is not None and type(_producer(state, t)) is donnx.ONNXReshape
                     and _const(sdfg, _in(state, _producer(state, t), "data")) is not None]
             if len(cand) == 1:
                 rs = _producer(state, cand[0])
                 mask = _in(state, rs, "data")
-                chain += [prev, rs]
+                const = _const(sdfg, mask)
+                if (tuple(const.shape) != (shp[0], shp[3]) or const.dtype != sdfg.arrays[scores].dtype
+                        or tuple(sdfg.arrays[cand[0]].shape) != (shp[0], 1, 1, shp[3])):
+                    continue
+                chain += [prev]
+                if _only_consumer(sdfg, state, cand[0])[0] is prev:
+                    chain += [rs]  # a Reshape that other layers read as well stays; prune() drops it once unused
             else:
                 # a mask computed at run time (or fed in): any [B, 1, 1, S] operand of the scores' type
-                shp = sdfg.arrays[scores].shape
                 cand = [t for t in (a, b) if tuple(sdfg.arrays[t].shape) == (shp[0], 1, 1, shp[3])
                         and sdfg.arrays[t].dtype == sdfg.arrays[scores].dtype]
                 if len(cand) != 1:
@@ -408,7 +416,7 @@ def fuse_attention(sdfg, state):
         rs2, _ = _only_consumer(sdfg, state, _out(state, tr), "Reshape")
         if rs2 is None or (q[2], q[3]) != (k[2], k[3]) or (q[2], q[3]) != (v[2], v[3]):
             continue
-        if mask is not None and len(sdfg.arrays[mask].shape) not in (2, 4):
+        if mask is not None and int(math.prod(sdfg.arrays[mask].shape)) != sdfg.arrays[q[0]].shape[0] * sdfg.arrays[k[0]].shape[1]:
             continue
         # the fused kernel is fp16 with 64-wide heads; anything else stays MatMul / Softmax / MatMul
         if sdfg.arrays[q[0]].dtype != torch.float16 or q[3] != 64:

@@ -103,3 +103,55 @@ def test_layernorm_pattern_needs_last_axis_and_constants():
     out2 = g2.output("__return", (4, 6, 8))
     g2.node("Sub", dict(A=x2, B=mean), (4, 6, 8), out=out2)
     assert fuse_subgraphs(g2.sdfg) == 0
+
+
+def _attention_block(g, x, mask4, batch, seq, heads, d, out_name):
+    """The exported attention sub-graph on one [B, S, H] input (Q = K = V = x), with an additive mask operand."""
+    hidden = heads * d
+
+    def split(perm):
+        r = g.node("Reshape", dict(data=x), (batch, seq, heads, d))
+        return g.node("Transpose", dict(data=r), tuple((batch, seq, heads, d)[i] for i in perm), perm=list(perm))
+
+    q, k, v = split((0, 2, 1, 3)), split((0, 2, 3, 1)), split((0, 2, 1, 3))
+    s = g.node("MatMul", dict(A=q, B=k), (batch, heads, seq, seq))
+    s = g.node("Mul", dict(A=s, B=g.scalar(0.125)), (batch, heads, seq, seq))
+    s = g.node("Add", dict(A=s, B=mask4), (batch, heads, seq, seq))
+    p = g.node("Softmax", dict(input=s), (batch, heads, seq, seq), axis=3)
+    c = g.node("MatMul", dict(A=p, B=v), (batch, heads, seq, d))
+    c = g.node("Transpose", dict(data=c), (batch, seq, heads, d), perm=[0, 2, 1, 3])
+    g.node("Reshape", dict(data=c), (batch, seq, hidden), out=g.output(out_name, (batch, seq, hidden)))
+
+
+@pytest.mark.parametrize("mask_shape, reshaped", [((1, 128), (1, 1, 1, 128)), ((128, 128), (1, 1, 128, 128)),
+                                                  ((2, 128), (2, 1, 1, 128))])
+def test_attention_fusion_takes_only_per_batch_key_masks(mask_shape, reshaped):
+    """The fused kernel reads its mask as [batch, keys]: a row broadcast over the batch or a [S, S] bias is not one."""
+    g = graphs.GraphBuilder("att", torch.float16)
+    x = g.input("x", (2, 128, 256))
+    m = g.constant("mask", torch.zeros(mask_shape, dtype=torch.float16))
+    m4 = g.node("Reshape", dict(data=m), reshaped)
+    _attention_block(g, x, m4, 2, 128, 4, 64, "__return")
+    fused = patterns.fuse_attention(g.sdfg)
+    if mask_shape == (2, 128):
+        assert fused == 1 and kinds(g.sdfg) == ["Attention"]
+    else:
+        assert fused == 0 and "Softmax" in kinds(g.sdfg) and "Add" in kinds(g.sdfg)
+
+
+def test_attention_fusion_keeps_a_mask_reshape_other_layers_read():
+    """One constant mask, reshaped once, added to the scores of two attention blocks: both fuse, and neither is left
+    reading an array whose producer was removed."""
+    g = graphs.GraphBuilder("att2", torch.float16)
+    x1, x2 = g.input("x1", (2, 128, 256)), g.input("x2", (2, 128, 256))
+    m = g.constant("mask", torch.zeros(2, 128, dtype=torch.float16))
+    m4 = g.node("Reshape", dict(data=m), (2, 1, 1, 128))
+    _attention_block(g, x1, m4, 2, 128, 4, 64, "__return_0")
+    _attention_block(g, x2, m4, 2, 128, 4, 64, "__return_1")
+    s = g.sdfg
+    assert fuse_subgraphs(s) > 0
+    assert sorted(kinds(s)) == ["Attention", "Attention"]
+    st = s.states()[0]
+    for att in st.topological_compute_nodes():
+        mask = next(e.data.data for e in st.in_edges_by_connector(att, "Mask"))
+        assert mask in s.constants and tuple(s.constants[mask].shape) == (2, 128)

@@ -92,6 +92,25 @@ def test_mbconv_module_matches_pytorch():
     status_ok()
 
 
+def test_mbconv_module_half_precision():
+    """The same block in fp16 (no specialised fp16 convolution kernels: the direct kernel, with the squeeze-excite
+    pool taken by the row reduction in the tensors' own type); compared with PyTorch fp32 on the rounded parameters."""
+    torch.manual_seed(0)
+    net = MBConv()
+    for p in net.parameters():
+        nn.init.normal_(p, 0.0, 0.05)
+    x = torch.randn(4, 24, 28, 28)
+    module = DaceModule(copy.deepcopy(net).half().cuda())
+    y = module(x.half().cuda())
+    assert y.dtype == torch.float16
+    assert module.compiled_function.kernel_names() == ["conv2d", "conv2d", "se_gate", "conv2d"]
+    ref_net = copy.deepcopy(net).half().float()
+    with torch.no_grad():
+        ref = ref_net(x.half().float())
+    assert_close(y, ref, torch.float16, what="MBConv module fp16", atol=1e-2)
+    status_ok()
+
+
 def test_strided_conv_module_and_decorator():
     torch.manual_seed(0)
     conv = nn.Conv2d(3, 16, 3, stride=2, bias=False)
