@@ -208,10 +208,33 @@ class Context:
 
 
 _contexts = {}
+_override = threading.local()
+
+
+class use_context:
+    """``with use_context(ctx):`` makes the calls of this thread go through ``ctx`` instead of the process-wide context
+    of its device.  A context's scratch buffer serves one call at a time on the GPU, so work that runs on several
+    streams at once gives each stream a context of its own (``Context(device)``)."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+
+    def __enter__(self):
+        self.previous = getattr(_override, "ctx", None)
+        _override.ctx = self.ctx
+        return self.ctx
+
+    def __exit__(self, *exc):
+        _override.ctx = self.previous
 
 
 def get_context(device=None):
-    """The process-wide context of a CUDA device (created on first use)."""
+    """The process-wide context of a CUDA device (created on first use), or the one ``use_context`` put in its place."""
+    over = getattr(_override, "ctx", None)
+    if over is not None:
+        index = device.index if isinstance(device, torch.device) else device
+        if index is None or index == over.device:
+            return over
     if device is None:
         if not torch.cuda.is_available():
             raise B200Error(ERR_CUDA, "no CUDA device is visible; daceml_b200 has no CPU path")

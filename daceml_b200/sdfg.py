@@ -283,6 +283,17 @@ class CompiledSDFG:
     def kernel_names(self):
         return [k for t, _, _ in self.plan for k in t.kernels]
 
+    def check_status(self, synchronize=True):
+        """Raises if a kernel on this SDFG's device recorded a problem (bad Gather index, a wait that ran out) since
+        the last check.  Kernels never stop the process; they leave a code in the context's status word."""
+        from daceml_b200 import lib as L
+        dev = self._device()
+        if synchronize:
+            torch.cuda.synchronize(dev)
+        code = L.get_context(dev).device_status()
+        if code != 0:
+            raise L.B200Error(L.ERR_DEVICE, "device status 0x%x after running SDFG '%s'" % (code & 0xffffffff, self.sdfg.name))
+
     def __call__(self, **kwargs):
         dev = self._device()
         bound: Dict[str, torch.Tensor] = {}
@@ -293,11 +304,11 @@ class CompiledSDFG:
             desc = self.sdfg.arrays[name]
             if isinstance(val, np.ndarray):
                 t = torch.from_numpy(np.ascontiguousarray(val)).to(dev)
-                copy_back.append((val, t))
+                copy_back.append((name, val, t))
             elif isinstance(val, torch.Tensor):
                 t = val if val.is_cuda else val.to(dev)
                 if not val.is_cuda:
-                    copy_back.append((val, t))
+                    copy_back.append((name, val, t))
                 if not t.is_contiguous():
                     t = t.contiguous()  # the reference's dispatchers guard inputs the same way
             else:
@@ -332,14 +343,19 @@ class CompiledSDFG:
             bound[name] = bound[self.sdfg.root_of(name)].view(self.sdfg.arrays[name].shape)
         for tasklet, ins, outs in self.plan:
             tasklet.fn({c: bound[a] for c, a in ins.items()}, {c: bound[a] for c, a in outs.items()})
-        for host, devt in copy_back:
+        written = {a for _, _, outs in self.plan for a in outs.values()}
+        written |= {self.sdfg.root_of(a) for a in written}
+        for name, host, devt in copy_back:
+            if name not in written and self.sdfg.root_of(name) not in written:
+                continue  # a pure input: nothing to bring back
             if isinstance(host, np.ndarray):
                 host[...] = devt.cpu().numpy()
             else:
                 host.copy_(devt)
         if not returns:
             return None
-        outs = [bound[n] for n in sorted(returns)]
+        # '__return', '__return_0', ... '__return_10': by number, not by string ('__return_10' < '__return_2')
+        outs = [bound[n] for n in sorted(returns, key=lambda n: (int(n.rsplit("_", 1)[1]) if n.rsplit("_", 1)[1].isdigit() else -1, n))]
         if any(isinstance(v, np.ndarray) for v in kwargs.values()):
             outs = [o.cpu().numpy() for o in outs]
         return outs[0] if len(outs) == 1 else tuple(outs)

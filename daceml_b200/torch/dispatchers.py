@@ -18,6 +18,7 @@ _HANDLES = {}  # handle_ptr -> callable(*tensors)
 _handle_ids = itertools.count(1)
 _LIBRARIES = []  # keeps the torch.library.Library objects (and with them the registrations) alive
 _used_namespaces = set()
+_LIB_OF_HANDLE = {}
 
 
 def _identifier(name: str) -> str:
@@ -59,4 +60,21 @@ def register_torch_op(sdfg_name: str, input_names: Sequence[str], outputs: List[
     lib.impl(name, run, "CUDA")
     lib.impl(name, meta, "Meta")
     _LIBRARIES.append(lib)
+    _LIB_OF_HANDLE[handle] = lib
     return getattr(getattr(torch.ops, ns), name), handle
+
+
+def release_torch_op(handle: int) -> None:
+    """Forgets the compiled function behind ``handle`` (and with it the weights and transients it keeps on the GPU)
+    and drops the operator's registration.  Called when a module is reset or collected; the namespace is not reused."""
+    _HANDLES.pop(handle, None)
+    lib = _LIB_OF_HANDLE.pop(handle, None)
+    if lib is not None:
+        if lib in _LIBRARIES:
+            _LIBRARIES.remove(lib)
+        destroy = getattr(lib, "_destroy", None)
+        if destroy is not None:
+            try:
+                destroy()
+            except Exception as e:  # pragma: no cover - torch keeps the registration; only the memory matters here
+                log.debug("could not drop operator library: %s", e)

@@ -119,6 +119,30 @@ class DaceModule(nn.Module):
     def reset_sdfg(self):
         """ Clear the sdfg so that optimizations are reapplied (and the wrapped module's weights are read again). """
         self.function = None
+        self._release_torch_op()
+
+    def _release_torch_op(self):
+        handle = getattr(self, "torch_op_handle", None)
+        if handle is not None:
+            from .dispatchers import release_torch_op
+            release_torch_op(handle)
+            self.torch_op = self.torch_op_handle = None
+
+    def __del__(self):
+        try:
+            self._release_torch_op()
+        except Exception:
+            pass
+
+    def check_status(self, synchronize=True):
+        """Raises :class:`daceml_b200.lib.B200Error` if a kernel of this module's device recorded a problem since the
+        last check: a Gather index outside its axis (the kernel wrote zeros there) or a device-side wait that gave up.
+        Kernels report through a status word instead of stopping the process, so a caller that wants to know calls
+        this after its work (``synchronize=False`` if the stream is already idle).  Clears the word."""
+        compiled = getattr(self, "compiled_function", None)
+        if compiled is None:
+            return
+        compiled.check_status(synchronize=synchronize)
 
     # -- hooks (``daceml/torch/module.py:179-235``) ------------------------------------------------
     def _add_hook(self, hooks, name, func, first):

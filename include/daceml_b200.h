@@ -14,7 +14,11 @@
  *     (daceml/onnx/onnx_importer.py:585-590, daceml/torch/dispatchers/ctypes_module.py:58-67).
  *   - One context per (process, device), the analogue of
  *     daceml::cudnn::CudnnHandle::Get(device) (daceml/onnx/include/daceml_cudnn.h:41-62).
- *     A context is not thread-safe.
+ *     A context is not thread-safe, and calls on ONE context must not overlap on
+ *     the GPU: the fp32 tensor-core GEMM (its split operands) and the long-row
+ *     reduction (its partial results) use the context's scratch buffer, so two
+ *     such calls running at once on different streams would overwrite each
+ *     other's scratch.  Work on several streams at once uses one context per stream.
  *   - Kernels are enqueued on the stream passed in and never synchronise the host
  *     (the reference sets state.nosync, daceml/torch/dispatchers/cpp_torch_extension.py:474-475).
  *   - Every function returns 0 on success or a negative b200ml_status; the message

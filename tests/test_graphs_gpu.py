@@ -189,6 +189,36 @@ def test_layer_is_deterministic_and_respects_guard_bands():
     status_ok()
 
 
+def test_two_streams_with_a_context_each_overlap_fp32_gemms():
+    """fp32 tensor-core GEMMs keep their split operands in the context's scratch buffer, so two of them running at once
+    need a context each.  Two streams, each with its own context, run different products in turns (the launches are
+    small enough to share the GPU); every result equals the one computed alone, bit for bit."""
+    rng = np.random.default_rng(11)
+    mk = lambda *s: torch.from_numpy(rng.standard_normal(s).astype(np.float32)).cuda()
+    a1, w1, a2, w2 = mk(1024, 2048), mk(512, 2048), mk(1024, 2048), mk(512, 2048)
+    alone1, alone2 = torch.empty(1024, 512, device="cuda"), torch.empty(1024, 512, device="cuda")
+    K.gemm(a1, w1, alone1, b_layout=1)
+    K.gemm(a2, w2, alone2, b_layout=1)
+    torch.cuda.synchronize()
+    ref = (a1.double() @ w1.double().T).float()
+    assert_close(alone1, ref, torch.float32, what="fp32 gemm")
+    ctx_a, ctx_b = L.Context(0), L.Context(0)
+    s_a, s_b = torch.cuda.Stream(), torch.cuda.Stream()
+    outs1 = [torch.empty_like(alone1) for _ in range(8)]
+    outs2 = [torch.empty_like(alone2) for _ in range(8)]
+    for i in range(8):
+        with torch.cuda.stream(s_a), L.use_context(ctx_a):
+            K.gemm(a1, w1, outs1[i], b_layout=1)
+        with torch.cuda.stream(s_b), L.use_context(ctx_b):
+            K.gemm(a2, w2, outs2[i], b_layout=1)
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, alone1) for o in outs1) and all(torch.equal(o, alone2) for o in outs2)
+    assert ctx_a.device_status() == 0 and ctx_b.device_status() == 0
+    ctx_a.close()
+    ctx_b.close()
+    status_ok()
+
+
 # ------------------------------------------------------------------------------------------------
 # config 5: stack of layers (the per-GPU part)
 # ------------------------------------------------------------------------------------------------
@@ -206,6 +236,54 @@ def test_encoder_stack_small():
     y2 = enc(x.cuda())
     assert torch.equal(y, y2)
     status_ok()
+
+
+def _hf_layer(p):
+    from transformers import BertConfig
+    from transformers.models.bert.modeling_bert import BertLayer
+    cfg = BertConfig(hidden_size=p["wq"].shape[0], num_attention_heads=16, intermediate_size=p["w1"].shape[0])
+    cfg._attn_implementation = "eager"
+    m = BertLayer(cfg).eval()
+    sd = m.state_dict()
+    names = {"attention.self.query": ("wq", "bq"), "attention.self.key": ("wk", "bk"), "attention.self.value": ("wv", "bv"),
+             "attention.output.dense": ("wo", "bo"), "intermediate.dense": ("w1", "b1"), "output.dense": ("w2", "b2")}
+    for k, (w, b) in names.items():
+        sd[k + ".weight"], sd[k + ".bias"] = p[w].half().float(), p[b].half().float()
+    sd["attention.output.LayerNorm.weight"], sd["attention.output.LayerNorm.bias"] = p["ln1_g"], p["ln1_b"]
+    sd["output.LayerNorm.weight"], sd["output.LayerNorm.bias"] = p["ln2_g"], p["ln2_b"]
+    m.load_state_dict(sd)
+    return m
+
+
+def test_encoder_stack_config5_full_size():
+    """The per-GPU part of the 24-layer encoder at its real sizes (hidden 1024, 16 heads, FFN 4096, S = 512, weights
+    ~ N(0, 0.02), biases 0, 24 independent weight sets) on 2 samples, through the same BertEncoder (one CUDA graph of
+    120 launches) the multi-GPU run uses.  Two witnesses: the oracle's layer chained 24 times with fp16 storage between
+    layers, and 24 HuggingFace BertLayers in fp32 end to end.  Largest deviations observed on a B200: 7.8e-3 against
+    the oracle and 1.2e-2 against the fp32 chain (outputs are O(1) after the LayerNorm; one fp16 step there is 1e-3 and
+    24 layers of fp16 storage accumulate a few of them) -- the bounds below sit a factor of two above that."""
+    rng = np.random.default_rng(55)
+    layers, batch = 24, 2
+    params = [bert_params(rng, 1024, 4096, zero_bias=True) for _ in range(layers)]
+    x = torch.from_numpy(rng.standard_normal((batch, 512, 1024)).astype(np.float32)).half()
+    enc = runner.BertEncoder(params, batch=batch, seq=512, heads=16, cuda_graph=True)
+    assert enc.launches_per_forward == 5 * layers
+    y = enc(x.cuda()).float().cpu().numpy()
+    status_ok()
+    ref = x.float().numpy()
+    hf = x.float()
+    with torch.no_grad():
+        for p in params:
+            ref = ops.bert_layer(ref, {k: v.half().float().numpy() for k, v in p.items()}, heads=16, store=np.float16).astype(np.float32)
+            out = _hf_layer(p)(hf)
+            hf = out[0] if isinstance(out, tuple) else out
+    err_oracle, err_hf = float(np.abs(y - ref).max()), float(np.abs(y - hf.numpy()).max())
+    print("config 5 stack: max |err| %.3g vs oracle chain (fp16 storage), %.3g vs HuggingFace fp32 chain" % (err_oracle, err_hf))
+    assert np.isfinite(y).all()
+    assert err_oracle <= 2e-2, err_oracle
+    assert err_hf <= 3e-2, err_hf
+    # the bulk of the elements sits far inside those bounds: rtol 2e-2 with the whole-layer atol
+    assert_close(y, ref, torch.float16, atol=1e-2, what="config 5 vs oracle chain")
 
 
 # ------------------------------------------------------------------------------------------------
