@@ -123,33 +123,35 @@ class ClockSampler:
 
 def run_reference(args, rank):
     """The reference arm: the exported layer executed node by node on the host cores (the CPU port of the
-    reference's pure expansions; its DaCe code generator is not installable here)."""
+    reference's pure expansions; its DaCe code generator is not installable here).  All 8 samples of the step, every
+    core of the process's affinity mask (a launcher's OMP_NUM_THREADS=1 is overridden), rank 0 only."""
     if rank != 0:
         return
     from oracle import cpu_baseline
-    sample_batch = 2
     params = layer_params(0)
     layer = cpu_baseline.CpuBertLayer(params, HEADS)
-    x = torch.randn(sample_batch, SEQ, HIDDEN, generator=torch.Generator().manual_seed(1))
-    for _ in range(max(1, min(args.warmup, 3))):
+    x = torch.randn(BATCH, SEQ, HIDDEN, generator=torch.Generator().manual_seed(1))
+    warmup = max(1, min(args.warmup, 3))
+    for _ in range(warmup):
         layer.forward(x)
     steps = max(1, min(args.steps, 40))
     t0 = time.perf_counter()
     for _ in range(steps):
         layer.forward(x)
     dt = time.perf_counter() - t0
-    value = sample_batch * steps / dt
+    value = BATCH * steps / dt
     out = {"impl": "reference", "metric": "bert_large_fp16_encoder_layer_samples_per_s", "value": value, "unit": "samples/s",
-           "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+           "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": WORKLOAD, "sample": "%d of 8 samples per step, fp32 on the host" % sample_batch},
+           "config": {"workload": WORKLOAD, "sample": "all 8 samples of a step, fp32 on the host; rank 0 only, the other ranks idle",
+                      "steps_asked": args.steps, "warmup_asked": args.warmup},
            "cpu_baseline": {"value": value, "unit": "samples/s", "cores": layer.threads, "kind": "port",
-                            "sample": "%d steps of the layer on %d samples (S=512), host BLAS + OpenMP loop nests" % (steps, sample_batch)},
+                            "sample": "%d steps of the layer on 8 samples (S=512), host BLAS + OpenMP loop nests" % steps},
            "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out), flush=True)
 
 
-def run_hbm_kernels(args):
+def run_hbm_kernels(args, emit=True):
     """The memory-bound kernels of the unfused BERT-large layer, each on operand sets that cycle through more than
     the 126 MB L2, timed with CUDA events over one CUDA graph: algorithmic bytes (every operand once) / time."""
     if not torch.cuda.is_available():
@@ -221,6 +223,7 @@ def run_hbm_kernels(args):
     cases.append(("where_kernel", "Where(mask, x, 0) [4096, 4096] fp16, bool mask", n, T * FFN * (2 + 2 + 1),
                   lambda i: K.where(cond[i], hs[i], zero, ho[i])))
     reps = max(args.steps // 4, 12)
+    rows = []
     for name, what, nset, nbytes, fn in cases:
         for i in range(min(nset, max(args.warmup, 3))):
             fn(i)
@@ -238,13 +241,18 @@ def run_hbm_kernels(args):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / reps
         gbs = nbytes / us / 1e3
-        print(json.dumps({"kernel": name, "workload": what, "launches": reps, "us_per_launch": us, "bytes_per_launch": nbytes,
-                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-                                       "peak_kind": "STREAM-style copy, of %s" % pk["source"]},
-                          "l2": "%d operand sets cycled (%.0f MB)" % (nset, nset * nbytes / 1e6)}), flush=True)
+        row = {"kernel": name, "workload": what, "launches": reps, "us_per_launch": us, "bytes_per_launch": nbytes,
+               "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                            "peak_kind": "STREAM-style copy, of %s" % pk["source"]},
+               "l2": "%d operand sets cycled (%.0f MB)" % (nset, nset * nbytes / 1e6)}
+        rows.append(row)
+        if emit:
+            print(json.dumps(row), flush=True)
+        del graph
+    return rows
 
 
-def run_other_configs(args):
+def run_other_configs(args, emit=True):
     """Configurations 1, 2 and 4 (fp32, parity cases of the test-suite) timed the same way as the layer: the compiled
     graph replayed from one CUDA graph, CUDA events around it.  `bytes` = every kernel's operands and results once."""
     if not torch.cuda.is_available():
@@ -276,6 +284,7 @@ def run_other_configs(args):
          2 * 128 * 56 * 56 * (24 * 144 + 9 * 144 + 144 * 24)),
     ]
     reps = max(args.steps // 8, 10)
+    rows = []
     for name, comp, inputs, out_name, out_shape, flops in cases:
         comp.device = dev
         kw = dict(inputs)
@@ -322,10 +331,42 @@ def run_other_configs(args):
             kus = a0.elapsed_time(a1) * 1e3 / reps
             per_kernel.append({"kernel": "+".join(tasklet.kernels), "us": round(kus, 2), "MB": round(kb / 1e6, 2),
                                "GB/s": round(kb / kus / 1e3, 1)})
-        print(json.dumps({"workload": name, "kernels": comp.kernel_names(), "launches_per_run": len(comp.kernel_names()),
-                          "per_kernel": per_kernel, "us_per_run": us, "samples_per_s": out_shape[0] / (us * 1e-6), "flops": flops, "tflops": flops / us / 1e6,
-                          "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / pk["hbm_gbs"],
-                          "dtype": "f32", "data": "synthetic"}), flush=True)
+        info = None
+        if name.startswith("config 1") or name.startswith("config 4"):
+            # information only: the same arithmetic through torch's library kernels (cuDNN), the reference's GPU route
+            # for convolutions (daceml/onnx/op_implementations/cudnn_implementations.py:360-379); not part of any claim
+            import torch.nn.functional as Fn
+            if name.startswith("config 1"):
+                lib_call = lambda: Fn.conv2d(inputs["X"], inputs["W"], stride=2)
+            else:
+                P = {k: v.to(dev) for k, v in mb_p.items()}
+                sw = lambda t: t * torch.sigmoid(t)
+
+                def lib_call():
+                    h = sw(Fn.conv2d(inputs["input"], P["w_exp"], P["b_exp"]))
+                    h = sw(Fn.conv2d(h, P["w_dw"], P["b_dw"], padding=1, groups=144))
+                    g_ = torch.sigmoid(Fn.conv2d(sw(Fn.conv2d(h.mean((2, 3), keepdim=True), P["w_se1"], P["b_se1"])), P["w_se2"], P["b_se2"]))
+                    return Fn.conv2d(h * g_, P["w_proj"], P["b_proj"]) + inputs["input"]
+            with torch.no_grad():
+                for _ in range(3):
+                    lib_call()
+                torch.cuda.synchronize()
+                l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                l0.record()
+                for _ in range(reps):
+                    lib_call()
+                l1.record()
+                torch.cuda.synchronize()
+            info = {"torch_library_kernels_us": round(l0.elapsed_time(l1) * 1e3 / reps, 2),
+                    "note": "cuDNN / ATen via torch eager, information only"}
+        row = {"workload": name, "info": info, "kernels": comp.kernel_names(), "launches_per_run": len(comp.kernel_names()),
+               "per_kernel": per_kernel, "us_per_run": us, "samples_per_s": out_shape[0] / (us * 1e-6), "flops": flops, "tflops": flops / us / 1e6,
+               "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / pk["hbm_gbs"],
+               "dtype": "f32", "data": "synthetic"}
+        rows.append(row)
+        if emit:
+            print(json.dumps(row), flush=True)
+    return rows
 
 
 def run_via_module(args):
@@ -403,6 +444,30 @@ def run_via_module(args):
                       "gpu_launches": len(names) * calls}), flush=True)
 
 
+def replay_timed(graph, replays, after=None):
+    """Replays ``graph`` ``replays`` times back to back on the current stream with a CUDA event between replays.
+    ``after()`` runs after each replay (work that could not be captured).  Returns the per-replay times in ms."""
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+    ev[0].record()
+    for r in range(replays):
+        graph.replay()
+        if after is not None:
+            after()
+        ev[r + 1].record()
+    torch.cuda.synchronize()
+    return [ev[r].elapsed_time(ev[r + 1]) for r in range(replays)]
+
+
+def gemm_traffic():
+    """DRAM bytes per GEMM launch from the committed ncu capture (profiles/bert_large_layer_gemm_traffic.json names the
+    commit and the command it was taken with); None if the file is missing."""
+    path = os.path.join(ROOT, "profiles", "bert_large_layer_gemm_traffic.json")
+    if not os.path.exists(path):
+        return None, None
+    rec = json.load(open(path))
+    return rec.get("traffic_bytes_per_launch"), rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -410,6 +475,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=24)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="leave the fp32 configurations and the HBM-bound kernels out of the JSON line")
+    ap.add_argument("--replays", type=int, default=0,
+                    help="how often the K-step graph is replayed inside the timed region (default: enough for 0.15 s, at least 50)")
     ap.add_argument("--hbm-kernels", action="store_true",
                     help="instead of the layer: time the HBM-bound kernels of the unfused graph (softmax, LayerNorm, bias+GELU, "
                          "residual add) at the layer's shapes and print one JSON line per kernel with its bandwidth")
@@ -441,8 +510,9 @@ def main():
     rank, world, local_rank = D.init_from_env()
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa_cores = D.bind_to_gpu_numa_node(local_rank) if world > 1 else 0
     import torch.distributed as dist
-    from daceml_b200 import graphs, kernels as K, lib as L
+    from daceml_b200 import graphs, lib as L
     from daceml_b200.runner import upload_graph
 
     # ---- build: 24 fused layer SDFGs with their own weights, two ping-pong activation buffers ----
@@ -456,12 +526,19 @@ def main():
     bufs = [torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev) for _ in range(2)]
     x0 = torch.randn(BATCH, SEQ, HIDDEN, generator=torch.Generator().manual_seed(7 + rank)).half()
     bufs[0].copy_(x0)
+    gathered = torch.empty(world * BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev) if world > 1 else None
+    final_buf = bufs[(args.warmup + args.steps) % 2]
 
     def run_steps(first, count):
         for s in range(first, first + count):
             layers[s % LAYERS](**{"input": bufs[s % 2], "__return": bufs[(s + 1) % 2]})
 
-    def capture(first, count):
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def capture(first, count, gather=False):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -469,55 +546,106 @@ def main():
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # thread_local: NCCL's watchdog thread polls events while this thread captures
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             run_steps(first, count)
+            if gather:
+                D.gather_outputs(final_buf, out=gathered)
         return g
 
+    if world > 1:
+        D.gather_outputs(final_buf, out=gathered)  # creates the NCCL communicator before any capture
+        barrier()
     warm_graph = capture(0, args.warmup)
-    timed_graph = capture(args.warmup, args.steps)
-    uploaded = upload_graph(timed_graph)  # the first replay is the timed one: the upload must not be part of it
-    gathered = torch.empty(world * BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev) if world > 1 else None
-    final_buf = bufs[(args.warmup + args.steps) % 2]
+    gather_in_graph = False
+    if world > 1:
+        # the one all-gather of the outputs rides in the same CUDA graph as the K steps, so no host launch sits between
+        # the last layer and the collective; every rank must agree on whether that worked
+        try:
+            timed_graph = capture(args.warmup, args.steps, gather=True)
+            ok = 1
+        except Exception as e:  # capture of the collective refused: issue it from the host behind each replay
+            sys.stderr.write("rank %d: all-gather not captured (%s)\n" % (rank, str(e).splitlines()[0] if str(e) else type(e).__name__))
+            torch.cuda.synchronize()
+            ok = 0
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gather_in_graph = bool(int(flag))
+        if not gather_in_graph:
+            timed_graph = capture(args.warmup, args.steps)
+    else:
+        timed_graph = capture(args.warmup, args.steps)
+    uploaded = upload_graph(timed_graph)  # the first replay is a timed one: the upload must not be part of it
+    after = None
+    if world > 1 and not gather_in_graph:
+        after = lambda: D.gather_outputs(final_buf, out=gathered)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-timed region ----
+    # ---- device-timed region: W warm-up steps, then the K-step graph R times back to back ----
+    barrier()
+    bufs[0].copy_(x0)
+    warm_graph.replay()
+    est = replay_timed(timed_graph, 2, after)[-1]
+    replays = args.replays
+    if replays <= 0:
+        replays = int(min(400, max(50, np.ceil(150.0 / max(est, 1e-3)))))
+    if world > 1:
+        rt = torch.tensor([replays], device=dev)
+        dist.all_reduce(rt, op=dist.ReduceOp.MAX)
+        replays = int(rt)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    if world > 1:
-        D.gather_outputs(final_buf, out=gathered)  # warms NCCL
-    barrier()
     bufs[0].copy_(x0)
     warm_graph.replay()  # the W untimed steps, straight before the timed ones
     barrier()
     sampler.begin()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    timed_graph.replay()
-    if world > 1:
-        D.gather_outputs(final_buf, out=gathered)
-    e1.record()
+    t_host = time.perf_counter()
+    times = replay_timed(timed_graph, replays, after)
+    host_ms = (time.perf_counter() - t_host) * 1e3
     barrier()
     sampler.end()
-    ms = e0.elapsed_time(e1)
     if world > 1:
-        tms = torch.tensor([ms], device=dev)
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms = float(tms)
+        tt = torch.tensor(times, device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)  # a replay takes as long as its slowest rank
+        times = tt.tolist()
     clocks = sampler.stop() if rank == 0 else None
     status = L.get_context(dev).device_status()
     assert torch.isfinite(final_buf).all(), "non-finite activations"
-    value = world * BATCH * args.steps / (ms * 1e-3)
+    med = float(np.median(times))
+    ms_per_step = med / args.steps
+    value = world * BATCH * args.steps / (med * 1e-3)
+
+    # ---- contents of the gathered output: own block bit for bit, every other block against its owner's checksum ----
+    gather_checked = None
+    if world > 1:
+        mine = gathered[rank * BATCH:(rank + 1) * BATCH]
+        same = bool(torch.equal(mine, final_buf))
+        sums = gathered.view(torch.int16).to(torch.int64).view(world, -1)
+        weights = torch.arange(1, sums.shape[1] + 1, device=dev, dtype=torch.int64) % 65521
+        seen = (sums * weights).sum(dim=1)  # position-weighted, so a permutation inside a block shows as well
+        own = (final_buf.view(torch.int16).to(torch.int64).view(-1) * weights).sum().view(1)
+        owners = torch.empty(world, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(owners, own)
+        ok = torch.tensor([int(same and bool(torch.equal(seen, owners)))], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        gather_checked = bool(int(ok))
+        assert gather_checked, "the gathered output does not hold every rank's block in rank order"
+        # what the collective alone costs (its own graph-free launch, events around it), for the record
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(10):
+            D.gather_outputs(final_buf, out=gathered)
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = g0.elapsed_time(g1) / 10
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM) ----
     # Events cannot sit between the kernels of the timed graph without opening gaps in it, so each GEMM of the step is
     # timed in a CUDA graph of its own: the same launch, once for each of the 24 layers (that layer's weights and
-    # buffers), events around the replay.  Launches follow one another as they do in the step (programmatic dependent
-    # launch included); what is lost is the L2 residency of the activations the previous kernel of the step wrote.
+    # buffers), replayed 20 times with events around each replay; the median replay counts.  Launches follow one another as
+    # they do in the step (programmatic dependent launch included); what is lost is the L2 residency of the activations
+    # the previous kernel of the step wrote.
     pk = peaks()
     gemm_us, per_gemm = 0.0, []
     plan0 = layers[0].plan
@@ -541,29 +669,33 @@ def main():
             run_tasklet()
         g.replay()
         torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        g.replay()
-        b.record()
-        torch.cuda.synchronize()
-        us = a.elapsed_time(b) * 1e3 / LAYERS
+        us = float(np.median(replay_timed(g, 20))) * 1e3 / LAYERS
         per_gemm.append({"tasklet": tasklet0.label, "kernel": tasklet0.kernels[0], "us": us})
         gemm_us += us
     n_gemm = len(per_gemm)
     gemm_flops = sum(GEMM_FLOPS.values())
     achieved_tf = gemm_flops / (gemm_us * 1e-6) / 1e12 if gemm_us > 0 else None
-    ev = per_gemm
-    gemm_ms = gemm_us * 1e-3
-    roofline = {"bound": "tensor", "kernel": "tcgen05 GEMM kernels (gemm_f16_pair_kernel x2, gemm_f16_ln_kernel x2 per layer)", "achieved": achieved_tf,
-                "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": achieved_tf / pk["tf_sustained"] if achieved_tf else None,
-                "peak_kind": "sustained cuBLAS bf16, of %s" % pk["source"], "launches_timed": n_gemm * LAYERS,
+    step_tf = LAYER_FLOPS / (ms_per_step * 1e-3) / 1e12
+    # which measured peak applies: the burst figure when the SM clock held (within 5 %) at its maximum through the timed
+    # region, the sustained (power-capped) figure otherwise; both fractions are printed either way
+    held = bool(clocks and clocks.get("in_timed_region") and clocks.get("sm_mhz") and clocks.get("sm_max_mhz")
+                and clocks["sm_mhz"] >= 0.95 * clocks["sm_max_mhz"]) if rank == 0 else False
+    peak_kind, peak_tf = ("burst", pk["tf_burst"]) if held else ("sustained", pk["tf_sustained"])
+    traffic, traffic_rec = gemm_traffic()
+    roofline = {"bound": "tensor", "kernel": "tcgen05 GEMM kernels (gemm_f16_pair_kernel x2, gemm_f16_ln_kernel x2 per layer)",
+                "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf if achieved_tf else None,
+                "frac_burst": achieved_tf / pk["tf_burst"] if achieved_tf else None,
+                "frac_sustained": achieved_tf / pk["tf_sustained"] if achieved_tf else None,
+                "peak_kind": "%s cuBLAS bf16, of %s (SM clock in the timed region: %s of %s MHz)" % (
+                    peak_kind, pk["source"], clocks.get("sm_mhz") if clocks else None, clocks.get("sm_max_mhz") if clocks else None),
+                "launches_timed": n_gemm * LAYERS * 20,
                 "avg_launch_us": gemm_us / max(n_gemm, 1), "flops_per_launch": gemm_flops / max(n_gemm, 1),
                 "per_launch_us": {p["tasklet"]: round(p["us"], 2) for p in per_gemm},
-                "probe": "each GEMM of the step in a CUDA graph of its own, 24 launches (one per layer), CUDA events around the replay",
-                # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch, mean of the layer's four launches, from
-                # the ncu --set full capture of one layer summarised under profiles/ (14.8 / 18.9 / 17.0 / 51.2 MB)
-                "traffic": 25.5e6, "traffic_unit": "bytes per launch (ncu, mean of the 4 GEMM launches of a layer)",
-                "layer_frac_of_tensor_peak": value / world * LAYER_FLOPS / BATCH / 1e12 / pk["tf_sustained"]}
+                "probe": "each GEMM of the step in a CUDA graph of its own, 24 launches (one per layer), median of 20 replays, CUDA events",
+                "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, mean of the 4 GEMM launches of a layer)",
+                "traffic_source": traffic_rec,
+                "whole_step": {"tflops": step_tf, "frac": step_tf / peak_tf, "frac_burst": step_tf / pk["tf_burst"],
+                               "frac_sustained": step_tf / pk["tf_sustained"], "flops_per_step": LAYER_FLOPS}}
 
     # ---- end to end through the public API with host buffers: H2D of the step's input, layer, D2H of its output ----
     n_e2e = max(24, min(args.steps, 96))
@@ -573,7 +705,52 @@ def main():
     din = [torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev) for _ in range(depth)]
     dout = [torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev) for _ in range(depth)]
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    step_graphs = []
+
+    def pipeline(step_graphs):
+        """H2D, compute and D2H on three streams over ``depth`` buffer sets; step i uses set i % depth."""
+        def run(n):
+            ev_in, ev_cmp, ev_out = [None] * depth, [None] * depth, [None] * depth
+            for i in range(n):
+                j = i % depth
+                with torch.cuda.stream(s_in):
+                    if ev_cmp[j] is not None:
+                        s_in.wait_event(ev_cmp[j])  # the step that read din[j] has finished
+                    din[j].copy_(hin[j], non_blocking=True)
+                    ev_in[j] = torch.cuda.Event()
+                    ev_in[j].record(s_in)
+                with torch.cuda.stream(s_cmp):
+                    s_cmp.wait_event(ev_in[j])
+                    if ev_out[j] is not None:
+                        s_cmp.wait_event(ev_out[j])  # dout[j] has been copied out
+                    step_graphs[j].replay()
+                    ev_cmp[j] = torch.cuda.Event()
+                    ev_cmp[j].record(s_cmp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_cmp[j])
+                    hout[j].copy_(dout[j], non_blocking=True)
+                    ev_out[j] = torch.cuda.Event()
+                    ev_out[j].record(s_out)
+        return run
+
+    def timed_passes(run, n):
+        """Three wall-clock passes of ``run(n)`` (max over ranks each); the median."""
+        run(depth * 2)
+        torch.cuda.synchronize()
+        out = []
+        for _ in range(3):
+            barrier()
+            t0 = time.perf_counter()
+            run(n)
+            torch.cuda.synchronize()
+            t = time.perf_counter() - t0
+            if world > 1:
+                te = torch.tensor([t], device=dev)
+                dist.all_reduce(te, op=dist.ReduceOp.MAX)
+                t = float(te)
+            out.append(t)
+        return sorted(out)[1], out
+
+    layer_graphs = []
     for j in range(depth):
         with torch.cuda.stream(s_cmp):
             layers[j % LAYERS](**{"input": din[j], "__return": dout[j]})
@@ -581,72 +758,91 @@ def main():
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s_cmp):
             layers[j % LAYERS](**{"input": din[j], "__return": dout[j]})
-        step_graphs.append(g)
-
-    def e2e_pass(n):
-        ev_in = [None] * depth
-        ev_cmp = [None] * depth
-        ev_out = [None] * depth
-        for i in range(n):
-            j = i % depth
-            with torch.cuda.stream(s_in):
-                if ev_cmp[j] is not None:
-                    s_in.wait_event(ev_cmp[j])  # the layer that read din[j] has finished
-                din[j].copy_(hin[j], non_blocking=True)
-                ev_in[j] = torch.cuda.Event()
-                ev_in[j].record(s_in)
-            with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in[j])
-                if ev_out[j] is not None:
-                    s_cmp.wait_event(ev_out[j])  # dout[j] has been copied out
-                step_graphs[j].replay()
-                ev_cmp[j] = torch.cuda.Event()
-                ev_cmp[j].record(s_cmp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[j])
-                hout[j].copy_(dout[j], non_blocking=True)
-                ev_out[j] = torch.cuda.Event()
-                ev_out[j].record(s_out)
-
-    # three timed passes, the median reported: on these hosts the pipeline settles into one of two states from pass to pass
-    # (about 175 or 222 us per step; PCIe copies in both directions under the layer's HBM traffic)
-    e2e_pass(depth * 2)
-    e2e_runs = []
-    for _ in range(3):
-        barrier()
-        t0 = time.perf_counter()
-        e2e_pass(n_e2e)
-        torch.cuda.synchronize()
-        t = time.perf_counter() - t0
-        if world > 1:
-            te = torch.tensor([t], device=dev)
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-            t = float(te)
-        e2e_runs.append(t)
-    e2e_s = sorted(e2e_runs)[1]
+        layer_graphs.append(g)
+    # on these hosts the pipeline settles into one of two states from pass to pass (PCIe copies in both directions
+    # under the layer's HBM traffic), hence three passes and their median
+    e2e_s, e2e_runs = timed_passes(pipeline(layer_graphs), n_e2e)
     nbytes = BATCH * SEQ * HIDDEN * 2
     e2e = {"value": world * BATCH * n_e2e / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
            "steps": n_e2e, "pipeline": "3 buffers; copy-in, layer and copy-out on separate streams",
            "passes_samples_per_s": [round(world * BATCH * n_e2e / t) for t in e2e_runs], "reported": "median of 3 passes"}
 
+    # ---- the same end to end at the granularity of the 24-layer encoder: one copy in, 24 layers, one copy out ----
+    stack_graphs = []
+    for j in range(depth):
+        tmp = torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev)
+
+        def stack(j=j, tmp=tmp):
+            src = din[j]
+            for s in range(LAYERS):
+                dst = dout[j] if s == LAYERS - 1 else (tmp if s % 2 == 0 else din[j])
+                layers[s](**{"input": src, "__return": dst})
+                src = dst
+
+        # 24 layers: even count, so the chain din -> tmp -> din ... ends in tmp before the last layer writes dout
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s_cmp):
+            stack()
+        stack_graphs.append(g)
+    n_passes = 12
+    c5_s, c5_runs = timed_passes(pipeline(stack_graphs), n_passes)
+    e2e_config5 = {"value": world * BATCH * LAYERS * n_passes / c5_s, "unit": "samples/s (layer-steps, as the headline)",
+                   "encoder_samples_per_s": world * BATCH * n_passes / c5_s, "h2d_bytes_per_pass": nbytes, "d2h_bytes_per_pass": nbytes,
+                   "passes": n_passes, "layers_per_pass": LAYERS,
+                   "what": "one pinned H2D of [8,512,1024] fp16, the 24-layer encoder, one D2H, pipelined over 3 buffer sets",
+                   "passes_samples_per_s": [round(world * BATCH * LAYERS * n_passes / t) for t in c5_runs]}
+
     # ---- CPU baseline beside it (rank 0, N = 1 only) ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import cpu_baseline
-        sps, iters, threads = cpu_baseline.time_layer(params[0], HEADS, batch=2, seq=SEQ, budget_s=12.0)
+        sps, iters, threads = cpu_baseline.time_layer(params[0], HEADS, batch=BATCH, seq=SEQ, budget_s=12.0)
         cpu = {"value": sps, "unit": "samples/s", "cores": threads, "kind": "port",
-               "sample": "%d runs of the layer on 2 of the 8 samples (S=512), fp32, host BLAS + OpenMP loop nests" % iters}
+               "sample": "%d runs of the layer on all 8 samples (S=512), fp32, host BLAS + OpenMP loop nests" % iters}
+
+    # ---- the other configurations and the HBM-bound kernels, so that one line records them (N = 1 only) ----
+    other_configs = hbm_kernels = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        del timed_graph, warm_graph, layer_graphs, stack_graphs
+        torch.cuda.empty_cache()
+        sub = argparse.Namespace(steps=96, warmup=3)
+        other_configs = [{"workload": r["workload"], "us_per_run": round(r["us_per_run"], 2), "bytes": r["bytes"],
+                          "gbs": round(r["gbs"], 1), "frac_of_hbm_peak": round(r["frac_of_hbm_peak"], 4),
+                          "tflops": round(r["tflops"], 3), "launches_per_run": r["launches_per_run"], "per_kernel": r["per_kernel"],
+                          "info": r.get("info")}
+                         for r in run_other_configs(sub, emit=False)]
+        hbm_kernels = [{"kernel": r["kernel"], "workload": r["workload"], "us_per_launch": round(r["us_per_launch"], 2),
+                        "bytes_per_launch": r["bytes_per_launch"], "gbs": round(r["roofline"]["achieved"], 1),
+                        "frac_of_hbm_peak": round(r["roofline"]["frac"], 4)} for r in run_hbm_kernels(sub, emit=False)]
 
     if rank == 0:
+        if clocks is not None and clocks.get("sm_mhz"):
+            clocks["ms_per_step_x_sm_mhz"] = ms_per_step * clocks["sm_mhz"]
         out = {"metric": "bert_large_fp16_encoder_layer_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
-               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                "config": {"workload": WORKLOAD, "global_batch": world * BATCH, "seq_len": SEQ, "parallelism": "dp%d" % world,
                           "l2": "24 distinct layer weight sets (604 MB) cycled: weights come from HBM every step",
-                          "chained": True, "graph": "the K timed steps are one CUDA graph" + (", uploaded to the device (cudaGraphUpload) before the timed region" if uploaded else ""), "gather": "one all-gather of the final outputs inside the timed region" if world > 1 else "none"},
-               "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": kernels_per_step * args.steps,
+                          "chained": True,
+                          "graph": "the K timed steps are one CUDA graph" + (", uploaded to the device (cudaGraphUpload) before the timed region" if uploaded else ""),
+                          "timed_region": "the K-step graph replayed %d times back to back, a CUDA event between replays; ms_per_step = median replay / K" % replays,
+                          "gather": ("one all-gather of the final outputs per replay, " + ("captured in the same CUDA graph as the K steps" if gather_in_graph else "issued from the host behind the replay")) if world > 1 else "none",
+                          "numa": ("process bound to the %d cores next to its GPU" % numa_cores) if numa_cores else "not bound"},
+               "replays": replays, "steps_timed_total": replays * args.steps,
+               "replay_ms": {"median": med, "min": float(np.min(times)), "max": float(np.max(times)), "mean": float(np.mean(times)),
+                             "p10": float(np.percentile(times, 10)), "p90": float(np.percentile(times, 90))},
+               "timed_region_ms": float(np.sum(times)), "timed_region_host_ms": host_ms,
+               "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_config5": e2e_config5,
+               "gpu_launches": kernels_per_step * args.steps * replays,
                "kernels_per_step": kernels_per_step, "clocks": clocks, "device_status": status,
                "peaks": pk}
+        if world > 1:
+            out["gather_checked"] = gather_checked
+            out["gather_ms"] = gather_ms
+            out["gather_bytes_per_rank"] = nbytes
+        if other_configs is not None:
+            out["other_configs"] = other_configs
+            out["hbm_kernels"] = hbm_kernels
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()

@@ -30,6 +30,32 @@ def init_from_env(backend=None, timeout_s=120):
     return rank, world, local_rank
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Restricts this process to the CPU cores next to its GPU (NVML's CPU affinity of the device, intersected with the
+    cores the process may already use), so that pinned host buffers allocated afterwards and the copy threads sit on
+    the GPU's own NUMA node.  With one process per GPU this keeps eight ranks from pulling their host traffic through
+    one socket.  Best effort: returns the number of cores bound to, or 0 if nothing was changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        index = local_rank
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if local_rank < len(ids) and ids[local_rank].isdigit():
+                index = int(ids[local_rank])
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        near = {i * 64 + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        allowed = near & set(os.sched_getaffinity(0))
+        if not allowed or allowed == set(os.sched_getaffinity(0)):
+            return 0
+        os.sched_setaffinity(0, allowed)
+        return len(allowed)
+    except Exception:
+        return 0
+
+
 def shard_bounds(global_batch, rank, world):
     """Rank r of R takes the contiguous samples [lo, hi); the batch must split evenly."""
     if global_batch % world != 0:

@@ -38,7 +38,16 @@ def load():
     lib.ew_unary.argtypes = [f32p, f32p, i64, ctypes.c_int]
     lib.transpose4d.argtypes = [f32p, f32p, ctypes.POINTER(i64), ctypes.POINTER(i64)]
     lib.oracle_num_threads.restype = ctypes.c_int
+    lib.oracle_set_num_threads.argtypes = [ctypes.c_int]
     return lib
+
+
+def host_cores():
+    """The cores this process may run on (its affinity mask), whatever OMP_NUM_THREADS says."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def _p(t):
@@ -52,6 +61,9 @@ class CpuBertLayer:
         self.lib = load()
         self.p = {k: v.detach().float().contiguous() for k, v in params.items() if v is not None}
         self.heads, self.eps = heads, eps
+        # every core of the affinity mask, for the loop nests (OpenMP) and for the BLAS calls (torch): a launcher's
+        # OMP_NUM_THREADS=1 must not shrink the baseline to one core
+        self.lib.oracle_set_num_threads(host_cores())
         self.threads = int(self.lib.oracle_num_threads())
         torch.set_num_threads(max(self.threads, 1))
 

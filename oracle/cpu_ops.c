@@ -24,6 +24,16 @@
 #include <omp.h>
 #endif
 
+/* Sets the size of the OpenMP team the loop nests below use.  A launcher may export OMP_NUM_THREADS=1 for its worker
+ * processes (torch.distributed.run does); the timed baseline asks for the host cores it is allowed to run on. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
