@@ -5,3 +5,10 @@
 There is no CPU or eager fallback: without the built library and a B200 every call raises.
 """
 __version__ = "0.1.0"
+
+import logging as _logging
+import os as _os
+
+# the reference's switch (daceml/__init__.py:9-11): DACEML_LOG_LEVEL=debug|info|... configures the root logger
+if "DACEML_LOG_LEVEL" in _os.environ:
+    _logging.basicConfig(level=getattr(_logging, _os.environ["DACEML_LOG_LEVEL"].upper(), _logging.INFO))

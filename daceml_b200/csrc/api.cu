@@ -1,5 +1,6 @@
 // extern "C" surface of libdaceml_b200: argument validation, context management, dispatch.
 #include "common.cuh"
+#include "tensormap.cuh"
 
 #include <cuda.h>
 #include <string.h>
@@ -70,6 +71,62 @@ using namespace b200ml;
     do {                                                                     \
         if (!(ctx)) return fail(B200ML_ERR_INVALID, "%s: null context", __func__); \
     } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-map table (tensormap.cuh)
+// ---------------------------------------------------------------------------------------------
+namespace b200ml {
+namespace {
+struct TmapKey {
+    uint64_t w[13];
+    bool operator==(const TmapKey& o) const { return memcmp(w, o.w, sizeof(w)) == 0; }
+};
+struct TmapEntry {
+    TmapKey key;
+    bool used = false;
+    alignas(64) CUtensorMap map;
+};
+constexpr int kTmapSlots = 1024;  // direct-mapped; a colliding key simply replaces the older entry
+thread_local TmapEntry* t_tmaps = nullptr;
+thread_local int64_t t_tmap_hits = 0, t_tmap_misses = 0;
+}  // namespace
+
+CUresult encode_tiled_cached(const b200ml_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dtype, const void* base,
+                             const cuuint64_t dims[4], const cuuint64_t strides[3], const cuuint32_t box[4]) {
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+    TmapKey key;
+    key.w[0] = reinterpret_cast<uint64_t>(base);
+    key.w[1] = static_cast<uint64_t>(dtype) | (static_cast<uint64_t>(ctx->device) << 32);
+    for (int i = 0; i < 4; ++i) key.w[2 + i] = dims[i];
+    for (int i = 0; i < 3; ++i) key.w[6 + i] = strides[i];
+    for (int i = 0; i < 4; ++i) key.w[9 + i] = box[i];
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t v : key.w) h = (h ^ v) * 1099511628211ull;
+    if (!t_tmaps) t_tmaps = new (std::nothrow) TmapEntry[kTmapSlots];
+    TmapEntry* e = t_tmaps ? &t_tmaps[(h >> 20) & (kTmapSlots - 1)] : nullptr;
+    if (e && e->used && e->key == key) {
+        ++t_tmap_hits;
+        *out = e->map;
+        return CUDA_SUCCESS;
+    }
+    ++t_tmap_misses;
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, dtype, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS && e) {
+        e->key = key;
+        e->map = *out;
+        e->used = true;
+    }
+    return r;
+}
+
+void tensormap_cache_counters(int64_t* hits, int64_t* misses) {
+    *hits = t_tmap_hits;
+    *misses = t_tmap_misses;
+}
+}  // namespace b200ml
 
 extern "C" {
 

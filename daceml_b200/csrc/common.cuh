@@ -19,6 +19,7 @@ enum : int32_t {
     DEV_TIMEOUT_EPILOGUE = 3,  // epilogue gave up waiting for an accumulator
     DEV_TIMEOUT_ATTN = 4,
     DEV_BAD_INDEX = 5,  // Gather met an index outside its axis
+    DEV_TIMEOUT_PROBE = 6,  // the wait probe's barrier was (as intended) never completed
 };
 
 struct b200ml_ctx {

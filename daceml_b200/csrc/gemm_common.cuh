@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "epilogue.cuh"
+#include "tensormap.cuh"
 
 namespace b200ml {
 namespace gemm {
@@ -42,10 +43,6 @@ struct GemmArgs {
 #define TRACE_ADD(var)
 #endif
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 // rank-4 fp16 tensor map {inner, rows, batch_inner, batch_outer} with a 128-byte-swizzled box.
 inline int make_tmap(const b200ml_ctx* ctx, CUtensorMap* out, const void* base, int64_t inner, int64_t rows, int64_t ld,
               int64_t n_inner, int64_t s_inner, int64_t n_outer, int64_t s_outer, int box_inner, int box_rows,
@@ -64,12 +61,8 @@ inline int make_tmap(const b200ml_ctx* ctx, CUtensorMap* out, const void* base, 
     cuuint64_t strides[3] = {row_bytes, use_i ? static_cast<uint64_t>(s_inner) * 2 : dummy,
                              use_o ? static_cast<uint64_t>(s_outer) * 2 : dummy};
     cuuint32_t box[4] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows), 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    if (!fn) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (!ctx->encode_tiled) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    CUresult r = encode_tiled_cached(ctx, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, dims, strides, box);
     if (r != CUDA_SUCCESS)
         return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d (dims %llu x %llu, ld %lld)", what,
                     (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (long long)ld);

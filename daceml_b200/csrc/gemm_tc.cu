@@ -417,7 +417,11 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
     args.bias = static_cast<const __half*>(p->bias);
     args.residual = static_cast<const __half*>(p->residual);
     args.status = ctx->status_dev;
-    args.trace = static_cast<long long*>(ctx->workspace);
+#ifdef B200ML_TRACE
+    args.trace = static_cast<long long*>(ctx->workspace);  // instrumented builds only: per-CTA cycle counters
+#else
+    args.trace = nullptr;
+#endif
     bool vec = aligned16(p->c) && p->ldc % 8 == 0 && p->c_stride_inner % 8 == 0 && p->c_stride_outer % 8 == 0;
     if (p->residual)
         vec = vec && aligned16(p->residual) && p->ldr % 8 == 0 && p->r_stride_inner % 8 == 0 && p->r_stride_outer % 8 == 0;

@@ -304,17 +304,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
 
 // rank-2 fp32 tensor map {K, rows} (as rank 4 with two unit dimensions), box 32 x 128, 128-byte swizzle.
 int make_tmap_f32(const b200ml_ctx* ctx, CUtensorMap* out, const float* base, int64_t k, int64_t rows, const char* what) {
-    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
-    if (!fn) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if (!ctx->encode_tiled) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const uint64_t row_bytes = static_cast<uint64_t>(k) * 4;
     const uint64_t dummy = row_bytes * static_cast<uint64_t>(rows);
     cuuint64_t dims[4] = {(cuuint64_t)k, (cuuint64_t)rows, 1, 1};
     cuuint64_t strides[3] = {row_bytes, dummy, dummy};
     cuuint32_t box[4] = {TBK, TBM, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode_tiled_cached(ctx, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box);
     if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(%s, fp32) failed with CUresult %d", what, (int)r);
     return B200ML_OK;
 }

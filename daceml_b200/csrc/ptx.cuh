@@ -92,17 +92,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Wall-clock limit of every device-side wait.
+// Wall-clock limit of every device-side wait unless the caller passes its own.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
-// Waits for the phase with the given parity to complete.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Waits for the phase with the given parity to complete.  Returns false when the limit ran out; the caller records
+// a code in the context's status word and leaves its loop, so the kernel still ends normally.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ffu) == 0) {
-            if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+            if (global_timer_ns() - t0 > limit_ns) return false;
         }
     }
     return true;

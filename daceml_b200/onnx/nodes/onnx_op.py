@@ -125,8 +125,31 @@ class ONNXOp(sd.Node, metaclass=_ONNXOpMeta):
     def iter_outputs_in_onnx_order(self, state):
         return self._ordered(state.out_edges(self), self.schema.outputs, lambda e: e.src_conn)
 
-    # -- validation (onnx_op.py:213-431, reduced to what a launch needs) -------------------------
+    # -- validation (onnx_op.py:213-431: connectors, then the schema's type constraints, then required attributes) ------
     def validate(self, sdfg, state):
+        self._validate_connectors(sdfg, state)
+        # type parameters: connectors that share one must agree, and the element type must be one it allows
+        assigned = {}
+        for edges, conn_of, what in ((state.in_edges(self), lambda e: e.dst_conn, "input"),
+                                     (state.out_edges(self), lambda e: e.src_conn, "output")):
+            for e in edges:
+                conn = conn_of(e)
+                base = parse_variadic_param(conn)[0] if "__" in conn else conn
+                tparam = self.schema.type_params[base]
+                dtype = sdfg.arrays[e.data.data].dtype
+                if tparam in assigned and assigned[tparam] != dtype:
+                    raise ValueError("Could not solve type constraints; expected type '{}' for {} '{}', got type '{}'".format(
+                        assigned[tparam], what, base, dtype))
+                possible = self.schema.type_constraints[tparam]
+                if dtype not in possible:
+                    raise ValueError("Expected type in '{}' for {} '{}', got type '{}'".format(
+                        [str(t) for t in possible], what, base, dtype))
+                assigned[tparam] = dtype
+        for attr in self.schema.required_attributes:
+            if getattr(self, attr, None) is None:
+                raise ValueError("Expected value for required attribute '{}', got None".format(attr))
+
+    def _validate_connectors(self, sdfg, state):
         for params, edges, conn_of, what in ((self.schema.inputs, state.in_edges(self), lambda e: e.dst_conn, "input"),
                                              (self.schema.outputs, state.out_edges(self), lambda e: e.src_conn,
                                               "output")):

@@ -425,6 +425,21 @@ def _reduce_groups(shape, axes):
     return list(reversed(runs))
 
 
+def _add_scratch(node, state, sdfg, tag, shape, dtype):
+    """Declares a transient of the SDFG as scratch of ``node`` and hangs it on an extra output connector, so that it is
+    allocated with the other transients when the SDFG is compiled -- never inside a launch (which may be under CUDA-graph
+    capture).  Returns the connector name under which the tasklet finds the tensor in ``outs``."""
+    base, i = "{}_{}".format(node.label, tag), 0
+    name = base
+    while name in sdfg.arrays:
+        i += 1
+        name = "{}_{}".format(base, i)
+    sdfg.add_transient(name, tuple(shape), dtype)
+    conn = "__scratch_" + tag
+    state.add_edge(node, conn, state.add_write(name), None, sdfg.make_array_memlet(name))
+    return conn
+
+
 def _register_reduce(op, code):
     def can(node, state, sdfg):
         return _float_descs(in_desc_with_name(node, state, sdfg, "data"), out_desc_with_name(node, state, sdfg, "reduced"))
@@ -437,7 +452,9 @@ def _register_reduce(op, code):
             lo, hi = run_axes[0], run_axes[-1]
             steps.append((prod(cur[:lo]), prod(cur[lo:hi + 1]), prod(cur[hi + 1:])))
             cur = cur[:lo] + cur[hi + 1:]
-        temps = {}
+        dtype = in_desc_with_name(node, state, sdfg, "data").dtype
+        temps = {i: _add_scratch(node, state, sdfg, "partial%d" % i, (outer * inner, ), dtype)
+                 for i, (outer, _, inner) in enumerate(steps[:-1])}
 
         def run(ins, outs):
             src, dst = ins["data"], outs["reduced"]
@@ -445,13 +462,7 @@ def _register_reduce(op, code):
                 K.unary(src, dst, L.UN_COPY)
                 return
             for i, (outer, red, inner) in enumerate(steps):
-                last = i == len(steps) - 1
-                if last:
-                    tgt = dst
-                else:
-                    tgt = temps.get(i)
-                    if tgt is None:
-                        tgt = temps[i] = torch.empty(outer * inner, dtype=src.dtype, device=src.device)
+                tgt = dst if i == len(steps) - 1 else outs[temps[i]]
                 K.reduce(src, tgt, op=code, outer=outer, red=red, inner=inner)
                 src = tgt
 
@@ -709,13 +720,11 @@ class B200FusedMatMul(ONNXForward):
                              residual=ins.get("Residual"), act=act, ln=(ins.get("LnScale"), ins.get("LnBias"), eps))
 
             return KernelTasklet(node.label, run_fused, kernels=("gemm_layernorm",))
-        scratch = {}
+        y_desc = out_desc_with_name(node, state, sdfg, "Y")
+        pre = _add_scratch(node, state, sdfg, "prenorm", y_desc.shape, y_desc.dtype)
 
         def run_split(ins, outs):
-            y = outs["Y"]
-            tmp = scratch.get("t")
-            if tmp is None or tmp.device != y.device:
-                tmp = scratch["t"] = torch.empty_like(y)
+            y, tmp = outs["Y"], outs[pre]
             _launch_gemm(ins["A"], ins["B"], tmp, plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
                          residual=ins.get("Residual"), act=act)
             K.layernorm(tmp, y, gamma=ins.get("LnScale"), beta=ins.get("LnBias"), eps=eps)

@@ -12,7 +12,41 @@ later opsets; ``FusedMatMul`` and ``Attention`` are the usual contrib names) are
 """
 from collections import namedtuple
 
+import torch
+
 SINGLE, OPTIONAL, VARIADIC = "single", "optional", "variadic"
+
+# type constraints, as ONNX schemas state them (``tensor(float)`` ... by type parameter): every connector has a type
+# parameter ("T" unless said otherwise); connectors with the same parameter must carry the same element type, and the
+# type must be one the parameter allows
+FLOATS = (torch.float16, torch.float32, torch.float64)
+INTS = (torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8)
+NUMERIC = FLOATS + INTS
+ANY = NUMERIC + (torch.bool, )
+INDEX = (torch.int32, torch.int64)
+_FLOAT_ONLY = {"Softmax", "LogSoftmax", "Sqrt", "Sigmoid", "Reciprocal", "Softplus", "LeakyRelu", "Erf", "Exp", "Log", "Tanh",
+               "Gemm", "Conv", "GlobalAveragePool", "BatchNormalization", "MaxPool", "LayerNormalization", "Gelu", "Swish",
+               "FusedMatMul", "Attention", "FusedConv", "SqueezeExcite", "ReduceMean", "Clip", "Relu", "Einsum"}
+# connector -> type parameter, where it is not "T"; type parameter -> allowed types, where it is not the operator default
+_TYPE_PARAMS = {
+    "Cast": ({"input": "T1", "output": "T2"}, {"T1": ANY, "T2": ANY}),
+    "Gather": ({"indices": "Tind"}, {"T": ANY, "Tind": INDEX}),
+    "Shape": ({"shape": "T1"}, {"T": ANY, "T1": (torch.int64, )}),
+    "Reshape": ({"shape": "Tshape"}, {"T": ANY, "Tshape": (torch.int64, )}),
+    "Expand": ({"shape": "Tshape"}, {"T": ANY, "Tshape": (torch.int64, )}),
+    "Slice": ({"starts": "Tind", "ends": "Tind", "axes": "Tind", "steps": "Tind"}, {"T": ANY, "Tind": INDEX}),
+    "Where": ({"condition": "B"}, {"T": ANY, "B": (torch.bool, )}),
+    "MaxPool": ({"Indices": "I"}, {"I": (torch.int64, )}),
+    "ConstantOfShape": ({"input": "T1", "output": "T2"}, {"T1": (torch.int64, ), "T2": ANY}),
+}
+_TYPE_PARAMS["Pow"] = ({"Y": "T1"}, {"T1": NUMERIC})
+_TYPE_PARAMS["LayerNormalization"] = ({"Scale": "U", "B": "U"}, {"U": FLOATS})
+_TYPE_PARAMS["FusedMatMul"] = ({"LnScale": "U", "LnBias": "U"}, {"U": FLOATS})
+for _cmp in ("Equal", "Greater", "Less", "GreaterOrEqual", "LessOrEqual"):
+    _TYPE_PARAMS[_cmp] = ({"C": "T1"}, {"T": ANY if _cmp == "Equal" else NUMERIC, "T1": (torch.bool, )})
+for _move in ("Identity", "Transpose", "Flatten", "Unsqueeze", "Squeeze", "Concat", "Split"):
+    _TYPE_PARAMS[_move] = ({}, {"T": ANY})
+_REQUIRED_ATTRIBUTES = {"Einsum": ("equation", ), "Cast": ("to", )}
 
 Param = namedtuple("Param", ["name", "kind"])
 
@@ -26,6 +60,11 @@ class ONNXSchema:
         self.fused = fused
         self.host_only = host_only
         self.doc = doc
+        params, allowed = _TYPE_PARAMS.get(name, ({}, {}))
+        self.type_params = {p.name: params.get(p.name, "T") for p in self.inputs + self.outputs}
+        self.type_constraints = {"T": FLOATS if name in _FLOAT_ONLY else NUMERIC}
+        self.type_constraints.update(allowed)
+        self.required_attributes = _REQUIRED_ATTRIBUTES.get(name, ())
 
     def non_variadic_inputs(self):
         return [p.name for p in self.inputs if p.kind != VARIADIC]

@@ -12,6 +12,8 @@ import collections
 from typing import Callable, Dict, List, Optional
 
 import numpy as np
+import os
+
 import torch
 
 _NP_TO_TORCH = {
@@ -253,6 +255,9 @@ class SDFG:
         return self.compile()(**kwargs)
 
 
+NVTX_RANGES = os.environ.get("DACEML_B200_NVTX", "0") == "1"
+
+
 class CompiledSDFG:
     """The launch plan of an expanded SDFG: tasklets in dependency order plus its transients.
 
@@ -272,6 +277,16 @@ class CompiledSDFG:
                 outs = {e.src_conn: e.data.data for e in st.out_edges(n)}
                 self.plan.append((n, ins, outs))
         self._transients = {}
+        if device is not None or torch.cuda.is_available():
+            self.allocate_transients()
+
+    def allocate_transients(self):
+        """Allocates every transient of the SDFG (intermediate tensors and the scratch of expansions) now, so that no
+        launch allocates: a first call may then run under CUDA-graph capture."""
+        dev = self._device()
+        for name, desc in self.sdfg.arrays.items():
+            if desc.transient and desc.view_of is None and name not in self._transients and name not in self.sdfg.constants:
+                self._transients[name] = torch.empty(desc.shape, dtype=desc.dtype, device=dev)
 
     def _device(self):
         if self.device is None:
@@ -341,8 +356,18 @@ class CompiledSDFG:
                 raise TypeError(f"missing argument '{name}' for SDFG '{self.sdfg.name}'")
         for name in views:  # same storage, other shape (every tensor here is contiguous)
             bound[name] = bound[self.sdfg.root_of(name)].view(self.sdfg.arrays[name].shape)
+        if NVTX_RANGES:
+            # one named range per SDFG call and per expanded node, as the reference's profiling helpers bracket their
+            # functions (daceml/testing/profiling/event_profiler.py:87-120); off unless DACEML_B200_NVTX=1
+            torch.cuda.nvtx.range_push(self.sdfg.name)
         for tasklet, ins, outs in self.plan:
+            if NVTX_RANGES:
+                torch.cuda.nvtx.range_push(tasklet.label)
             tasklet.fn({c: bound[a] for c, a in ins.items()}, {c: bound[a] for c, a in outs.items()})
+            if NVTX_RANGES:
+                torch.cuda.nvtx.range_pop()
+        if NVTX_RANGES:
+            torch.cuda.nvtx.range_pop()
         written = {a for _, _, outs in self.plan for a in outs.values()}
         written |= {self.sdfg.root_of(a) for a in written}
         for name, host, devt in copy_back:

@@ -72,6 +72,13 @@ int b200ml_ctx_destroy(b200ml_ctx* ctx);
 /* Reads (and clears) the device status word.  Call after synchronising the stream. */
 int b200ml_ctx_device_status(b200ml_ctx* ctx, int32_t* status);
 int64_t b200ml_ctx_workspace_bytes(const b200ml_ctx* ctx);
+/* Diagnostic, no counterpart in the reference (whose status helpers print and exit, dace_onnx.h:7-15): runs the
+ * give-up path of the library's bounded device-side waits on purpose.  One CTA waits, for at most limit_ns
+ * (1 ns .. 100 ms), on an mbarrier that nothing completes; when the limit runs out it records a code in the
+ * context's status word and the kernel ends normally.  After synchronising the stream,
+ * b200ml_ctx_device_status() returns B200ML_ERR_DEVICE with status 6 and clears the word; the context and the
+ * device stay usable.  waited_us (device memory, may be null) receives the time the CTA spent waiting. */
+int b200ml_wait_probe(b200ml_ctx* ctx, int64_t limit_ns, uint32_t* waited_us, b200ml_stream stream);
 /* Replaces __ort_check_status / CheckCudnnError (dace_onnx.h:7-15, daceml_cudnn.h:17-24). */
 const char* b200ml_last_error(void);
 int b200ml_version(void);

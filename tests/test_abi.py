@@ -62,3 +62,34 @@ def test_null_context_is_rejected(library):
     rc = library.b200ml_softmax(None, 0, None, None, None, 1, 1, 1, ctypes.c_float(1.0), 0, None)
     assert rc == L.ERR_INVALID
     assert b"null context" in library.b200ml_last_error()
+
+
+@pytest.mark.gpu
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
+    """The give-up path of the library's device-side waits, run on purpose: a CTA waits 2 ms on an mbarrier nothing
+    completes, records its code and returns.  The status call reports it once, clears the word, and a GEMM launched
+    afterwards on the same context is correct.  No trap, no fault, nothing left waiting."""
+    import numpy as np
+    from daceml_b200 import kernels as K
+    ctx = L.get_context(0)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    waited = torch.zeros(1, dtype=torch.int32, device="cuda")
+    L.check(ctx.lib.b200ml_wait_probe(ctx.handle, 2_000_000, ctypes.c_void_p(waited.data_ptr()), L.current_stream()))
+    torch.cuda.synchronize()
+    with pytest.raises(L.B200Error) as err:
+        ctx.device_status()
+    assert err.value.code == L.ERR_DEVICE and "status 6" in str(err.value)
+    assert 2000 <= int(waited) < 50_000, int(waited)  # it waited the 2 ms it was given, not the default second
+    assert ctx.device_status() == 0, "the status word was not cleared"
+    # limits outside 1 ns .. 100 ms are refused on the host
+    assert ctx.lib.b200ml_wait_probe(ctx.handle, 10**10, None, L.current_stream()) == L.ERR_INVALID
+    rng = np.random.default_rng(0)
+    a = torch.from_numpy(rng.standard_normal((256, 512)).astype(np.float32)).half().cuda()
+    b = torch.from_numpy(rng.standard_normal((512, 384)).astype(np.float32)).half().cuda()
+    y = torch.empty(256, 384, dtype=torch.float16, device="cuda")
+    K.gemm(a, b, y)
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float()
+    assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2)
+    assert ctx.device_status() == 0

@@ -194,3 +194,45 @@ def test_topological_order_detects_cycles():
     st.add_edge(n2, "Y", st.add_access("a"), None, g.make_array_memlet("a"))
     with pytest.raises(ValueError, match="cycle"):
         st.topological_compute_nodes()
+
+
+def test_validate_checks_the_schema_type_constraints():
+    """daceml/onnx/nodes/onnx_op.py:355-417: connectors sharing a type parameter must agree, and the element type must be
+    one the parameter allows; a wrong tensor type is a validation error, not "cannot be applied"."""
+    import torch
+    from daceml_b200 import sdfg as sd
+
+    def one_node(op, ins, outs, **attrs):
+        g = sd.SDFG("v")
+        st = g.add_state()
+        node = getattr(donnx, "ONNX" + op)(op, **attrs)
+        st.add_node(node)
+        for conn, (shape, dtype) in ins.items():
+            g.add_array("i_" + conn, shape, dtype)
+            st.add_edge(st.add_read("i_" + conn), None, node, conn, g.make_array_memlet("i_" + conn))
+        for conn, (shape, dtype) in outs.items():
+            g.add_array("o_" + conn, shape, dtype)
+            st.add_edge(node, conn, st.add_write("o_" + conn), None, g.make_array_memlet("o_" + conn))
+        return node, g, st
+
+    node, g, st = one_node("MatMul", {"A": ((2, 4), torch.float32), "B": ((4, 3), torch.float16)}, {"Y": ((2, 3), torch.float32)})
+    with pytest.raises(ValueError, match="Could not solve type constraints"):
+        node.validate(g, st)
+    node, g, st = one_node("Softmax", {"input": ((2, 4), torch.int64)}, {"output": ((2, 4), torch.int64)})
+    with pytest.raises(ValueError, match="Expected type in"):
+        node.validate(g, st)
+    node, g, st = one_node("Gather", {"data": ((5, 4), torch.float32), "indices": ((3, ), torch.float32)}, {"output": ((3, 4), torch.float32)})
+    with pytest.raises(ValueError, match="for input 'indices'"):
+        node.validate(g, st)
+    node, g, st = one_node("Where", {"condition": ((4, ), torch.float32), "X": ((4, ), torch.float32), "Y": ((4, ), torch.float32)},
+                           {"output": ((4, ), torch.float32)})
+    with pytest.raises(ValueError, match="for input 'condition'"):
+        node.validate(g, st)
+    node, g, st = one_node("Cast", {"input": ((4, ), torch.float32)}, {"output": ((4, ), torch.int64)})
+    with pytest.raises(ValueError, match="required attribute 'to'"):
+        node.validate(g, st)
+    # well-typed nodes pass: mixed types where the schema has separate parameters
+    one = one_node("Cast", {"input": ((4, ), torch.float32)}, {"output": ((4, ), torch.int64)}, to=7)
+    one[0].validate(one[1], one[2])
+    one = one_node("Gather", {"data": ((5, 4), torch.float16), "indices": ((3, ), torch.int64)}, {"output": ((3, 4), torch.float16)})
+    one[0].validate(one[1], one[2])

@@ -201,7 +201,8 @@ def test_two_streams_with_a_context_each_overlap_fp32_gemms():
     K.gemm(a2, w2, alone2, b_layout=1)
     torch.cuda.synchronize()
     ref = (a1.double() @ w1.double().T).float()
-    assert_close(alone1, ref, torch.float32, what="fp32 gemm")
+    # sums of 2048 products of N(0,1) values are O(45); an element that cancels to 0.2 still carries their rounding
+    assert_close(alone1, ref, torch.float32, atol=1e-3, what="fp32 gemm")
     ctx_a, ctx_b = L.Context(0), L.Context(0)
     s_a, s_b = torch.cuda.Stream(), torch.cuda.Stream()
     outs1 = [torch.empty_like(alone1) for _ in range(8)]
