@@ -98,6 +98,11 @@ def oracle_outputs(case, arrays):
     raise KeyError(op)
 
 
+def _contig(a):
+    """A C-contiguous copy that keeps a 0-d array 0-d (np.ascontiguousarray would make it 1-d)."""
+    return np.array(a, copy=True, order="C")
+
+
 def frontend_outputs(case, arrays, donnx, torch):
     """The case's outputs from the CUDA path: ``donnx.ONNX<Op>(connector=tensor, ..., attribute=value)`` with
     device tensors, as a user of the frontend calls it (index-like parameters stay on the host, where the frontend
@@ -125,10 +130,10 @@ def frontend_outputs(case, arrays, donnx, torch):
         call = {}
         for k, v in ins.items():
             if k in host_params:
-                g.add_constant("arr_" + k, torch.from_numpy(np.ascontiguousarray(v)))
+                g.add_constant("arr_" + k, torch.from_numpy(_contig(v)))
             else:
                 g.add_array("arr_" + k, v.shape, v.dtype)
-                call["arr_" + k] = torch.from_numpy(np.ascontiguousarray(v)).cuda()
+                call["arr_" + k] = torch.from_numpy(_contig(v)).cuda()
             st.add_edge(st.add_read("arr_" + k), None, node, k, g.make_array_memlet("arr_" + k))
         for k, o in outs.items():
             g.add_array("arr_" + k, o.shape, o.dtype)
@@ -136,7 +141,7 @@ def frontend_outputs(case, arrays, donnx, torch):
             st.add_edge(node, k, st.add_write("arr_" + k), None, g.make_array_memlet("arr_" + k))
         g.compile()(**call)
     else:
-        kw = {k: (np.ascontiguousarray(v) if k in host_params else torch.from_numpy(np.ascontiguousarray(v)).cuda()) for k, v in ins.items()}
+        kw = {k: (_contig(v) if k in host_params else torch.from_numpy(_contig(v)).cuda()) for k, v in ins.items()}
         kw.update(outs)
         getattr(donnx, "ONNX" + case["op"])(**kw, **at)
     torch.cuda.synchronize()

@@ -260,8 +260,8 @@ def test_encoder_stack_config5_full_size():
     """The per-GPU part of the 24-layer encoder at its real sizes (hidden 1024, 16 heads, FFN 4096, S = 512, weights
     ~ N(0, 0.02), biases 0, 24 independent weight sets) on 2 samples, through the same BertEncoder (one CUDA graph of
     120 launches) the multi-GPU run uses.  Two witnesses: the oracle's layer chained 24 times with fp16 storage between
-    layers, and 24 HuggingFace BertLayers in fp32 end to end.  Largest deviations observed on a B200: 7.8e-3 against
-    the oracle and 1.2e-2 against the fp32 chain (outputs are O(1) after the LayerNorm; one fp16 step there is 1e-3 and
+    layers, and 24 HuggingFace BertLayers in fp32 end to end.  Largest deviations observed on a B200: 1.17e-2 against
+    the oracle chain and 6.6e-3 against the fp32 chain (outputs are O(1) after the LayerNorm; one fp16 step there is 1e-3 and
     24 layers of fp16 storage accumulate a few of them) -- the bounds below sit a factor of two above that."""
     rng = np.random.default_rng(55)
     layers, batch = 24, 2
@@ -281,8 +281,8 @@ def test_encoder_stack_config5_full_size():
     err_oracle, err_hf = float(np.abs(y - ref).max()), float(np.abs(y - hf.numpy()).max())
     print("config 5 stack: max |err| %.3g vs oracle chain (fp16 storage), %.3g vs HuggingFace fp32 chain" % (err_oracle, err_hf))
     assert np.isfinite(y).all()
-    assert err_oracle <= 2e-2, err_oracle
-    assert err_hf <= 3e-2, err_hf
+    assert err_oracle <= 2.4e-2, err_oracle
+    assert err_hf <= 1.4e-2, err_hf
     # the bulk of the elements sits far inside those bounds: rtol 2e-2 with the whole-layer atol
     assert_close(y, ref, torch.float16, atol=1e-2, what="config 5 vs oracle chain")
 
