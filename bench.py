@@ -803,7 +803,7 @@ def main():
     # ---- the other configurations and the HBM-bound kernels, so that one line records them (N = 1 only) ----
     other_configs = hbm_kernels = None
     if rank == 0 and world == 1 and not args.no_extras:
-        del timed_graph, warm_graph, layer_graphs, stack_graphs
+        timed_graph = warm_graph = layer_graphs = stack_graphs = None
         torch.cuda.empty_cache()
         sub = argparse.Namespace(steps=96, warmup=3)
         other_configs = [{"workload": r["workload"], "us_per_run": round(r["us_per_run"], 2), "bytes": r["bytes"],
@@ -845,8 +845,18 @@ def main():
             out["hbm_kernels"] = hbm_kernels
         print(json.dumps(out), flush=True)
     if world > 1:
+        # A communicator cannot be torn down while CUDA graphs that hold its collectives are alive: drop them first.
+        # Should the teardown still stall, the line is printed already and nothing is in flight: leave after 30 s.
+        guard = threading.Timer(30.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
+        timed_graph = warm_graph = layer_graphs = stack_graphs = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
+        guard.cancel()
 
 
 if __name__ == "__main__":
