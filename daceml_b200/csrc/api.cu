@@ -92,12 +92,13 @@ thread_local int64_t t_tmap_hits = 0, t_tmap_misses = 0;
 }  // namespace
 
 CUresult encode_tiled_cached(const b200ml_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dtype, const void* base,
-                             const cuuint64_t dims[4], const cuuint64_t strides[3], const cuuint32_t box[4]) {
+                             const cuuint64_t dims[4], const cuuint64_t strides[3], const cuuint32_t box[4],
+                             CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
     if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
     TmapKey key;
     key.w[0] = reinterpret_cast<uint64_t>(base);
-    key.w[1] = static_cast<uint64_t>(dtype) | (static_cast<uint64_t>(ctx->device) << 32);
+    key.w[1] = static_cast<uint64_t>(dtype) | (static_cast<uint64_t>(swizzle) << 16) | (static_cast<uint64_t>(ctx->device) << 32);
     for (int i = 0; i < 4; ++i) key.w[2 + i] = dims[i];
     for (int i = 0; i < 3; ++i) key.w[6 + i] = strides[i];
     for (int i = 0; i < 4; ++i) key.w[9 + i] = box[i];
@@ -113,7 +114,7 @@ CUresult encode_tiled_cached(const b200ml_ctx* ctx, CUtensorMap* out, CUtensorMa
     ++t_tmap_misses;
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(out, dtype, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS && e) {
         e->key = key;
         e->map = *out;

@@ -13,6 +13,8 @@ namespace b200ml {
 
 int reduce(const b200ml_ctx* ctx, int dtype, int op, const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
            cudaStream_t s);
+bool conv1x1_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p);
+int conv1x1_tensor_core(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t stream);
 
 namespace {
 
@@ -24,21 +26,6 @@ __device__ __forceinline__ void stv(__half* p, float v) { *p = __float2half_rn(v
 struct ConvGeom {
     int32_t n, c, h, w, m, kh, kw, sh, sw, pt, pl, dh, dw, group, oh, ow, act;
 };
-
-// Activation of the convolution kernels.  Swish goes through one MUFU.EX2 and one MUFU.RCP (relative error about
-// 1e-6, against the 1e-4 the fp32 configurations allow): the libm expf + division cost more instructions than the
-// nine multiply-adds of a depthwise tap.  No NaN for any finite input: exp2 saturates to +inf or 0, 1 / inf = 0.
-__device__ __forceinline__ float conv_act(float v, int act) {
-    if (act & B200ML_EPI_RELU) return fmaxf(v, 0.0f);
-    if (act & B200ML_EPI_SWISH) {
-        float e, r;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.44269504088896340736f * v));
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-        return v * r;
-    }
-    if (act & B200ML_EPI_GELU) return gelu_erf(v);
-    return v;
-}
 
 // ---------------------------------------------------------------------------------------------
 // direct convolution: one thread = one output pixel x MT consecutive output channels
@@ -555,11 +542,15 @@ int launch_direct(const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s
 }  // namespace
 
 // Tries the specialised kernels; *launched says whether one ran, *pooled whether it also wrote the pool.
-static int conv2d_fast(const b200ml_ctx*, const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched,
+static int conv2d_fast(const b200ml_ctx* ctx, const b200ml_conv_params* p, const ConvGeom& g, cudaStream_t s, bool* launched,
                        bool* pooled) {
     *launched = false;
     *pooled = false;
     if (p->dtype != B200ML_F32) return B200ML_OK;
+    if (conv1x1_tensor_core_applies(ctx, p)) {  // 1x1, stride 1: the tensor-core kernel (3 x TF32), HBM-bound
+        *launched = true;
+        return conv1x1_tensor_core(ctx, p, s);
+    }
     const bool unit = p->stride_h == 1 && p->stride_w == 1 && p->dil_h == 1 && p->dil_w == 1;
     const bool nopad = !p->pad_top && !p->pad_left && !p->pad_bottom && !p->pad_right;
     const int64_t hw = p->h * p->w;

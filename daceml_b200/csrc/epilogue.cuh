@@ -25,6 +25,22 @@ __device__ __forceinline__ float apply_act(float v, int32_t flags) {
     return v;
 }
 
+// Activation of the convolution kernels.  Swish goes through one MUFU.EX2 and one MUFU.RCP (relative error about
+// 1e-6, against the 1e-4 the fp32 configurations allow): the libm expf + division cost more instructions than the
+// nine multiply-adds of a depthwise tap.  No NaN for any finite input: exp2 saturates to +inf or 0, 1 / inf = 0.
+__device__ __forceinline__ float conv_act(float v, int act) {
+    if (act & B200ML_EPI_RELU) return fmaxf(v, 0.0f);
+    if (act & B200ML_EPI_SWISH) {
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.44269504088896340736f * v));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        return v * r;
+    }
+    if (act & B200ML_EPI_GELU) return gelu_erf(v);
+    return v;
+}
+
+
 __device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
     const __half2* h = reinterpret_cast<const __half2*>(&q);
 #pragma unroll

@@ -109,6 +109,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
     return true;
 }
 
+// The same wait for warps that expect to wait long (whole warps of an element-wise stage waiting for their next tile):
+// try_wait is given a suspend-time hint, so the thread sleeps in hardware until the phase completes or the hint runs
+// out instead of issuing a test every few cycles, which would take issue slots from the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return done != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_suspend(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    while (!mbar_try_wait_suspend(bar, parity, 20000u)) {
+        if (global_timer_ns() - t0 > limit_ns) return false;
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA: tiled bulk tensor loads into shared memory, completion on an mbarrier.  No multicast.
 // ---------------------------------------------------------------------------------------------
@@ -212,6 +238,14 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
         : "r"(taddr)
         : "memory");
 }

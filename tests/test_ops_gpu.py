@@ -448,6 +448,37 @@ def test_conv_pointwise(cin, cout, hw, rng):
     assert_close(y, ops.conv2d(x, w, b), what=f"1x1 conv {cin}->{cout}")
 
 
+@pytest.mark.parametrize("n, cin, cout, hw", [(8, 24, 144, (56, 56)), (8, 144, 24, (56, 56)), (16, 40, 100, (36, 36)), (4, 100, 40, (64, 64)),
+                                              (3, 8, 8, (150, 152)), (24, 24, 256, (28, 28)), (6, 31, 9, (64, 60)), (6, 32, 64, (64, 60)), (2, 33, 17, (128, 64)), (16, 72, 72, (30, 40))])
+@pytest.mark.parametrize("act", ["", "Swish", "Relu"])
+def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
+    """1x1 convolutions large enough for the tensor-core kernel (3 x TF32, NCHW operand read MN-major through TMA):
+    ragged last pixel tile (H * W not a multiple of 128), channel counts that are not whole 32- or 16-blocks,
+    squeeze-excite gate on the input, bias, activation and residual add.  Against the oracle at the fp32 tolerance,
+    and against a float64 product at a bound that a single-TF32 product (relative error 5e-4) would break."""
+    x = rng.standard_normal((n, cin) + hw).astype(np.float32)
+    w = (rng.standard_normal((cout, cin, 1, 1)) * 0.1).astype(np.float32)
+    b = (rng.standard_normal(cout) * 3).astype(np.float32)
+    gate = rng.random((n, cin, 1, 1)).astype(np.float32)
+    res = rng.standard_normal((n, cout) + hw).astype(np.float32)
+    guard = torch.full((n * cout * hw[0] * hw[1] + 4096, ), 7.0, dtype=torch.float32, device="cuda")
+    y = guard[:n * cout * hw[0] * hw[1]].view((n, cout) + hw)
+    before = L.launch_count()
+    donnx.ONNXFusedConv(X=dev(x), W=dev(w), B=dev(b), Gate=dev(gate), Residual=dev(res), Y=y, activation=act)
+    assert L.launch_count() - before == 2, "expected the weight split and the tensor-core kernel"
+    xg = x.astype(np.float64) * gate.astype(np.float64)
+    pre = np.einsum("mc,nchw->nmhw", w[:, :, 0, 0].astype(np.float64), xg) + b.astype(np.float64)[None, :, None, None]
+    post = {"": pre, "Swish": pre / (1 + np.exp(-pre)), "Relu": np.maximum(pre, 0)}[act] + res
+    mag = np.einsum("mc,nchw->nmhw", np.abs(w[:, :, 0, 0]).astype(np.float64), np.abs(xg)) + np.abs(b)[None, :, None, None] + np.abs(res)
+    err = np.abs(y.double().cpu().numpy() - post)
+    assert (err <= 4e-6 * mag + 1e-6).all(), "3 x TF32 accuracy lost: worst error / magnitude %.3g" % float((err / (mag + 1e-9)).max())
+    oracle = ops.conv2d((x * gate).astype(np.float32), w, b)
+    oracle = {"": oracle, "Swish": ops.swish(oracle), "Relu": ops.relu(oracle)}[act] + res
+    assert_close(y, oracle, what=f"1x1 conv {cin}->{cout} {hw} {act}", atol=2e-5)
+    assert bool((guard[n * cout * hw[0] * hw[1]:] == 7.0).all()), "written past the end of Y"
+    status_ok()
+
+
 @pytest.mark.parametrize("c, hw, pads", [(144, (56, 56), (1, 1, 1, 1)), (5, (7, 8), (1, 1, 1, 1)), (3, (13, 12), (1, 1, 1, 1)), (6, (33, 64), (1, 1, 1, 1)),
                                          (4, (1, 16), (1, 1, 1, 1)), (5, (9, 10), (1, 1, 1, 1)), (4, (12, 12), (0, 1, 1, 0)), (2, (70, 72), (1, 1, 1, 1))])
 @pytest.mark.parametrize("act", ["", "Swish"])
