@@ -16,8 +16,8 @@
 // allow, so each operand is split into hi (its leading TF32 bits) and lo = value - hi (exact), and the tensor core
 // accumulates X_lo.W_hi + X_hi.W_lo + X_hi.W_hi in fp32 TMEM (the dropped lo.lo term is below 1e-6 of the operands'
 // product).  The weights and the bias are split once per call by a small kernel (a few KB); X is split inside this
-// kernel: eight warps read the tile the TMA delivered, apply the squeeze-excite gate, write hi over it and lo next to
-// it, and hand the stage to the MMA warp.
+// kernel: two groups of four warps, taking the pipeline stages in turn, read the tile the TMA delivered, apply the
+// squeeze-excite gate, write hi over it and lo next to it, and hand the stage to the MMA warp.
 //
 // Roles (832 threads, one persistent CTA per SM, tiles dealt round-robin): warp 0 TMA producer, warp 1 MMA issuer and
 // TMEM owner, warps 2-9 split, warps 10-25 epilogue.  Split and epilogue are element-wise work whose chain of dependent
@@ -41,7 +41,7 @@ constexpr int PW_STAGES = 4;
 constexpr int PW_BOX_BYTES = 32 * PW_KB * 4;         // 4 KB: 32 pixels x 32 channels
 constexpr int PW_TILE_BYTES = PW_BM * PW_KB * 4;     // 16 KB: X as delivered, overwritten by its hi part
 constexpr int PW_STAGE_BYTES = 2 * PW_TILE_BYTES;    // ... and the lo part next to it
-constexpr int PW_SPLIT_WARPS = 8, PW_EPI_WARPS = 16;
+constexpr int PW_SPLIT_WARPS = 8, PW_SPLIT_GROUPS = 2, PW_EPI_WARPS = 16;
 constexpr int PW_FIRST_EPI = 2 + PW_SPLIT_WARPS;
 constexpr int PW_THREADS = 32 * (2 + PW_SPLIT_WARPS + PW_EPI_WARPS);
 constexpr int PW_MAX_WEIGHT_BYTES = 64 * 1024;       // hi + lo of the padded weight matrix, resident in shared memory
@@ -168,7 +168,7 @@ conv1x1_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         if (lane == 0) {
             for (int s = 0; s < PW_STAGES; ++s) {
                 ptx::mbar_init(&raw_full[s], 1);
-                ptx::mbar_init(&ready[s], PW_SPLIT_WARPS);
+                ptx::mbar_init(&ready[s], PW_SPLIT_WARPS / PW_SPLIT_GROUPS);
                 ptx::mbar_init(&empty[s], 1);
             }
             ptx::mbar_init(w_full, 1);
@@ -269,16 +269,26 @@ conv1x1_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         }
     } else if (warp < PW_FIRST_EPI) {
         // ------------------------------ split: raw X -> hi (in place) and lo ------------------------------
-        const int t = threadIdx.x - 64;  // 0 .. 32 * PW_SPLIT_WARPS - 1
-        constexpr int NT = 32 * PW_SPLIT_WARPS;
-        constexpr int NPK = PW_TILE_BYTES / 16 / NT;  // 16-byte packets per thread and stage
-        static_assert(NT * 16 == PW_BOX_BYTES, "one packet per thread and box: every packet of a thread is in channel row t / 8");
+        // Two groups of four warps take the stages in turn (even stages group 0, odd stages group 1), so that the load ->
+        // arithmetic -> store latency of one stage passes under the work on the next.
+        constexpr int NT = 32 * PW_SPLIT_WARPS / PW_SPLIT_GROUPS;  // threads per group
+        constexpr int NPK = PW_TILE_BYTES / 16 / NT;               // 16-byte packets per thread and stage
+        static_assert(PW_STAGES % PW_SPLIT_GROUPS == 0 && NT * 32 == PW_BOX_BYTES, "packet t + NT j: box j / 2, channel row t / 8 + 16 (j & 1)");
+        const int group = (warp - 2) / (PW_SPLIT_WARPS / PW_SPLIT_GROUPS);
+        const int t = threadIdx.x - 64 - group * NT;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
             const int n = tile / args.pblocks;
             for (int kb = 0; kb < args.kblocks; ++kb) {
+                if ((stage % PW_SPLIT_GROUPS) != group) {  // the other group's stage
+                    if (++stage == PW_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                    continue;
+                }
                 ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&raw_full[stage], phase));
                 if (!ok) {
                     if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
@@ -286,36 +296,35 @@ conv1x1_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                 }
                 float4* hi = reinterpret_cast<float4*>(smem + stage * PW_STAGE_BYTES);
                 float4* lo = reinterpret_cast<float4*>(smem + stage * PW_STAGE_BYTES + PW_TILE_BYTES);
-                // packet t + NT j sits at byte 16 t + 4096 j of the stage: box j, channel row t / 8 (the swizzle moves
-                // packets only inside a row)
-                const int row = t >> 3;
-                if (kb == kb_ones && row == row_ones) {  // the row of ones that meets the bias column of W
+                // packet t + NT j sits at byte 16 t + 2048 j of the stage: box j / 2, channel row t / 8 (even j) or
+                // t / 8 + 16 (odd j); the swizzle moves packets only inside a row
+                const int row0 = t >> 3, row1 = row0 + 16;
+                float g0 = 1.0f, g1 = 1.0f;
+                if (args.gate) {
+                    const int c0 = kb * PW_KB + row0, c1 = kb * PW_KB + row1;
+                    g0 = c0 < args.c ? __ldg(args.gate + static_cast<int64_t>(n) * args.c + c0) : 0.0f;
+                    g1 = c1 < args.c ? __ldg(args.gate + static_cast<int64_t>(n) * args.c + c1) : 0.0f;
+                }
+                const bool ones0 = kb == kb_ones && row0 == row_ones, ones1 = kb == kb_ones && row1 == row_ones;
+                // every packet is read before the first is written back: the reads are independent, while a read
+                // placed after a write to the same buffer would have to wait for it
+                float4 v[NPK];
 #pragma unroll
-                    for (int j = 0; j < NPK; ++j) {
-                        hi[t + NT * j] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-                        lo[t + NT * j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    }
-                } else {
-                    float g = 1.0f;
-                    if (args.gate) {
-                        const int ch = kb * PW_KB + row;
-                        g = ch < args.c ? __ldg(args.gate + static_cast<int64_t>(n) * args.c + ch) : 0.0f;
-                    }
-                    // every packet is read before the first is written back: the reads are independent, while a read
-                    // placed after a write to the same buffer would have to wait for it
-                    float4 v[NPK];
+                for (int j = 0; j < NPK; ++j) v[j] = hi[t + NT * j];
 #pragma unroll
-                    for (int j = 0; j < NPK; ++j) v[j] = hi[t + NT * j];
-#pragma unroll
-                    for (int j = 0; j < NPK; ++j) {
-                        float4 h, l;
-                        split_tf32(v[j].x * g, h.x, l.x);
-                        split_tf32(v[j].y * g, h.y, l.y);
-                        split_tf32(v[j].z * g, h.z, l.z);
-                        split_tf32(v[j].w * g, h.w, l.w);
-                        hi[t + NT * j] = h;
-                        lo[t + NT * j] = l;
+                for (int j = 0; j < NPK; ++j) {
+                    const float g = (j & 1) ? g1 : g0;
+                    float4 h, l;
+                    split_tf32(v[j].x * g, h.x, l.x);
+                    split_tf32(v[j].y * g, h.y, l.y);
+                    split_tf32(v[j].z * g, h.z, l.z);
+                    split_tf32(v[j].w * g, h.w, l.w);
+                    if ((j & 1) ? ones1 : ones0) {  // the row of ones that meets the bias column of W
+                        h = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                        l = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     }
+                    hi[t + NT * j] = h;
+                    lo[t + NT * j] = l;
                 }
                 ptx::fence_proxy_async_smem();  // the tensor core reads shared memory through the async proxy
                 __syncwarp();
