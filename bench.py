@@ -468,6 +468,68 @@ def gemm_traffic():
     return rec.get("traffic_bytes_per_launch"), rec
 
 
+def run_profile_kernels(args):
+    """For a profiler: every kernel family of the library launched twice on operands larger than the 126 MB L2 (the
+    small fp32 products excepted), nothing timed.  Used as
+        ncu --section SpeedOfLight --section MemoryWorkloadAnalysis --clock-control none -c 120 python bench.py --profile-kernels
+    (the second launch of each kernel is the one to read)."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the product path has no CPU fallback")
+    from daceml_b200 import kernels as K, lib as L
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(5)
+    h = lambda *s: torch.randn(*s, generator=g).half().to(dev)
+    f = lambda *s: torch.randn(*s, generator=g).to(dev)
+    e16 = lambda *s: torch.empty(*s, dtype=torch.float16, device=dev)
+    e32 = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
+    T8 = 8 * BATCH * SEQ  # 32768 rows
+    jobs = []
+    sc, so = h(BATCH * HEADS * SEQ, SEQ), e16(BATCH * HEADS * SEQ, SEQ)
+    jobs.append(("softmax", lambda: K.softmax(sc, so, rows=sc.shape[0], cols=SEQ, scale=0.125)))
+    x, r, y = h(T8, HIDDEN), h(T8, HIDDEN), e16(T8, HIDDEN)
+    gam, bet, bh, bf = h(HIDDEN), h(HIDDEN), h(HIDDEN), h(FFN)
+    jobs.append(("layernorm", lambda: K.layernorm(x, y, gamma=gam, beta=bet, residual=r, bias=bh, eps=1e-12)))
+    jobs.append(("binary add", lambda: K.binary(x, r, y, L.BIN_ADD)))
+    hx, hy = h(T8 // 2, FFN), e16(T8 // 2, FFN)
+    jobs.append(("bias + gelu", lambda: K.bias_act(hx, hy, bias=bf, act=L.EPI_GELU)))
+    ux, uy = f(32 << 20), e32(32 << 20)
+    jobs.append(("unary sigmoid f32", lambda: K.unary(ux, uy, L.UN_SIGMOID)))
+    qkv, part = h(T8, 3 * HIDDEN), e16(T8, HIDDEN)
+    jobs.append(("strided copy (split)", lambda: K.strided_copy(qkv.narrow(1, HIDDEN, HIDDEN), part)))
+    table, ids, emb = h(30522, HIDDEN), torch.randint(0, 30522, (128, SEQ), generator=g).to(dev), e16(128, SEQ, HIDDEN)
+    jobs.append(("gather", lambda: K.gather(table, ids, emb, 0)))
+    cond, zero = (torch.rand(T8 // 2, FFN, generator=g) > 0.5).to(dev), torch.zeros((), dtype=torch.float16, device=dev)
+    jobs.append(("where", lambda: K.where(cond, hx, zero, hy)))
+    rx, ry = f(65536, 1024), e32(65536)
+    jobs.append(("reduce rows", lambda: K.reduce(rx, ry, op=L.RED_MEAN, outer=65536, red=1024, inner=1)))
+    tx, ty = h(64, SEQ, HEADS, 64), e16(64, HEADS, SEQ, 64)
+    jobs.append(("transpose heads", lambda: K.transpose(tx, ty, (0, 2, 1, 3))))
+    cx, cy = h(64 << 20), e32(64 << 20)
+    jobs.append(("cast f16 -> f32", lambda: K.cast(cx, cy)))
+    ga, gw, gy = f(8192, 1024), f(1024, 1024), e32(8192, 1024)
+    jobs.append(("gemm fp32 3xTF32", lambda: K.gemm(ga, gw, gy, b_layout=1)))
+    sa, sw, sy = f(262144, 120), f(32, 120), e32(262144, 32)
+    jobs.append(("gemm fp32 FMA", lambda: K.gemm(sa, sw, sy, b_layout=1)))
+    ka, kw, ky = f(262144, 32), f(10, 32), e32(262144, 10)
+    jobs.append(("gemm fp32 skinny", lambda: K.gemm(ka, kw, ky, b_layout=1)))
+    c1x, c1w, c1y = f(512, 3, 64, 64), torch.rand(16, 3, 3, 3, generator=g).to(dev), e32(512, 16, 31, 31)
+    jobs.append(("conv direct 3x3 stride 2", lambda: K.conv2d(c1x, c1w, c1y, strides=(2, 2))))
+    mx, big, pool = f(128, 24, 56, 56), e32(128, 144, 56, 56), e32(128, 144, 1, 1)
+    w_exp, b_exp = f(144, 24, 1, 1) * 0.05, f(144) * 0.05
+    jobs.append(("conv 1x1 expand (tensor core)", lambda: K.conv2d(mx, w_exp, big, bias=b_exp, act=L.EPI_SWISH)))
+    big2, w_dw, b_dw = e32(128, 144, 56, 56), f(144, 1, 3, 3) * 0.05, f(144) * 0.05
+    jobs.append(("depthwise 3x3", lambda: K.conv2d(big, w_dw, big2, bias=b_dw, pads=(1, 1, 1, 1), group=144, act=L.EPI_SWISH, pool_mean=pool)))
+    gate, w_proj, b_proj, my = torch.rand(128, 144, 1, 1, generator=g).to(dev), f(24, 144, 1, 1) * 0.05, f(24) * 0.05, e32(128, 24, 56, 56)
+    jobs.append(("conv 1x1 project (tensor core)", lambda: K.conv2d(big2, w_proj, my, bias=b_proj, gate=gate, residual=mx)))
+    for name, fn in jobs:
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        print("ran", name, flush=True)
+    assert L.get_context(dev).device_status() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -485,11 +547,17 @@ def main():
     ap.add_argument("--other-configs", action="store_true",
                     help="instead of the layer: time the fp32 configurations 1 (strided conv), 2 (MLP) and 4 (MBConv block) "
                          "at their full sizes and print one JSON line each")
+    ap.add_argument("--profile-kernels", action="store_true",
+                    help="instead of the layer: launch every kernel family twice on operands larger than L2, nothing timed "
+                         "(the workload the ncu summaries under profiles/ were taken on)")
     ap.add_argument("--via-module", action="store_true",
                     help="instead of the hand-built layer graphs: 24 transformers BertLayer modules wrapped in one DaceModule "
                          "(export, import, fusion), timed the same way; one JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.profile_kernels:
+        run_profile_kernels(args)
+        return
     if args.via_module:
         run_via_module(args)
         return

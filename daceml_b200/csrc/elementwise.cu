@@ -76,6 +76,8 @@ __device__ __forceinline__ float binary_apply(int op, float a, float b) {
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) unary_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n, int op,
                                                     float p0, float p1) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = VEC ? Pack<T>::N : 1;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
     for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
@@ -95,6 +97,8 @@ __global__ void __launch_bounds__(256) unary_kernel(const T* __restrict__ x, T* 
 // The vector form of the unary map with the operator fixed at compile time and two packets per thread and step.
 template <typename T, int OP>
 __global__ void __launch_bounds__(256) unary2_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n, float p0, float p1) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = Pack<T>::N;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
     for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += 2 * stride) {
@@ -120,14 +124,23 @@ template <typename T>
 __global__ void __launch_bounds__(256) binary_fast_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                           T* __restrict__ y, int64_t n, int op, int mode,
                                                           int64_t period, int swap) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = Pack<T>::N;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
     const float bs = mode == 1 ? ldf(b) : 0.0f;
-    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    int64_t col = mode == 2 ? first % period : 0;  // one 64-bit remainder per thread, not per packet
+    const int64_t col_step = mode == 2 ? stride % period : 0;
+    for (int64_t i = first; i < n; i += stride) {
         float fa[V], fb[V];
         Pack<T>::load(a + i, fa);
         if (mode == 0) Pack<T>::load(b + i, fb);
-        else if (mode == 2) Pack<T>::load(b + i % period, fb);
+        else if (mode == 2) {
+            Pack<T>::load(b + col, fb);
+            col += col_step;
+            if (col >= period) col -= period;
+        }
 #pragma unroll
         for (int j = 0; j < V; ++j) {
             const float bv = mode == 1 ? bs : fb[j];
@@ -142,6 +155,8 @@ __global__ void __launch_bounds__(256) binary_fast_kernel(const T* __restrict__ 
 template <typename T, int OP>
 __global__ void __launch_bounds__(256) binary_same_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                           T* __restrict__ y, int64_t n) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = Pack<T>::N;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
     for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += 2 * stride) {
@@ -175,6 +190,8 @@ struct BcastArgs {
 template <typename T>
 __global__ void __launch_bounds__(256) binary_bcast_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                            T* __restrict__ y, int64_t n, int op, const BcastArgs g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         int64_t rem = i, ao = 0, bo = 0;
@@ -200,6 +217,8 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias,
                                                        const T* __restrict__ residual, T* __restrict__ y, int64_t n,
                                                        int64_t cols, int act) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = VEC ? Pack<T>::N : 1;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
     for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
@@ -228,28 +247,54 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
     }
 }
 
+__device__ __forceinline__ void gelu_store8(__half* y, float (&f)[8], const float (&b)[8], bool has_bias) {
+    if (has_bias) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += b[j];
+    }
+    *reinterpret_cast<uint4*>(y) = gelu_pack8(f);
+}
+__device__ __forceinline__ void gelu_store8(float*, float (&)[4], const float (&)[4], bool) {}  // never taken: fp32 keeps fp32 math
+
 // The vector form with the activation fixed at compile time and two packets per thread and step: every 16-byte load of
 // both packets is issued before the first activation is evaluated.
 template <typename T, int ACT>
 __global__ void __launch_bounds__(256) bias_act2_kernel(const T* __restrict__ x, const T* __restrict__ bias,
                                                         const T* __restrict__ residual, T* __restrict__ y, int64_t n,
                                                         int64_t cols) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = Pack<T>::N;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
-    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += 2 * stride) {
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    // the bias column of a packet advances by (stride mod cols) per step: one 64-bit remainder per thread, not per packet
+    int64_t col = first % cols;
+    const int64_t col_step = stride % cols;
+    for (int64_t i = first; i < n; i += 2 * stride) {
         const int64_t idx[2] = {i, i + stride};
         const bool on[2] = {true, i + stride < n};
+        int64_t cols_of[2];
+        cols_of[0] = col;
+        col += col_step;
+        if (col >= cols) col -= cols;
+        cols_of[1] = col;
+        col += col_step;
+        if (col >= cols) col -= cols;
         float f[2][V], r[2][V], b[2][V];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             if (!on[u]) continue;
             Pack<T>::load(x + idx[u], f[u]);
             if (residual) Pack<T>::load(residual + idx[u], r[u]);
-            if (bias) Pack<T>::load(bias + idx[u] % cols, b[u]);
+            if (bias) Pack<T>::load(bias + cols_of[u], b[u]);
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             if (!on[u]) continue;
+            if (ACT == B200ML_EPI_GELU && sizeof(T) == 2 && !residual) {  // fp16 bias + GELU: pairs in half precision
+                gelu_store8(y + idx[u], f[u], b[u], bias != nullptr);
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < V; ++j) {
                 float v = f[u][j] + (bias ? b[u][j] : 0.0f);
@@ -274,6 +319,8 @@ struct PermArgs {
 template <typename E>
 __global__ void __launch_bounds__(256) permute_gather_kernel(const E* __restrict__ x, E* __restrict__ y, int64_t n,
                                                              const PermArgs g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         int64_t rem = i, off = 0;
@@ -304,6 +351,8 @@ struct TileArgs {
 template <typename E>
 __global__ void __launch_bounds__(256) permute_tiled_kernel(const E* __restrict__ x, E* __restrict__ y,
                                                             const TileArgs g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     __shared__ E tile[32][33];
     int64_t b = blockIdx.z, ioff = 0, ooff = 0;
 #pragma unroll
@@ -332,6 +381,8 @@ __global__ void __launch_bounds__(256) permute_tiled_kernel(const E* __restrict_
 
 template <typename S, typename D>
 __global__ void __launch_bounds__(256) cast_kernel(const S* __restrict__ x, D* __restrict__ y, int64_t n) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
         stf(y + i, ldf(x + i));
@@ -350,18 +401,18 @@ int unary_t(const b200ml_ctx* ctx, int op, const T* x, T* y, int64_t n, float p0
     constexpr int V = Pack<T>::N;
     if (n % V == 0 && aligned16(x) && aligned16(y)) {
         const unsigned grid = grid_for((n / V + 1) / 2, ctx->sm_count);
-#define B200ML_UNARY2(OP) case OP: unary2_kernel<T, OP><<<grid, 256, 0, s>>>(x, y, n, p0, p1); break
+#define B200ML_UNARY2(OP) case OP: launch_pdl(unary2_kernel<T, OP>, dim3(grid), dim3(256), 0, s, x, y, n, p0, p1); break
         switch (op) {  // the load-bound operators; those bound by instruction issue (GELU, Swish, ...) gain nothing from it
             B200ML_UNARY2(B200ML_UN_COPY);
             B200ML_UNARY2(B200ML_UN_RELU);
             B200ML_UNARY2(B200ML_UN_AFFINE);
             B200ML_UNARY2(B200ML_UN_CLIP);
             B200ML_UNARY2(B200ML_UN_NEG);
-            default: unary_kernel<T, true><<<grid_for(n / V, ctx->sm_count), 256, 0, s>>>(x, y, n, op, p0, p1); break;
+            default: launch_pdl(unary_kernel<T, true>, dim3(grid_for(n / V, ctx->sm_count)), dim3(256), 0, s, x, y, n, op, p0, p1); break;
         }
 #undef B200ML_UNARY2
     } else {
-        unary_kernel<T, false><<<grid_for(n, ctx->sm_count), 256, 0, s>>>(x, y, n, op, p0, p1);
+        launch_pdl(unary_kernel<T, false>, dim3(grid_for(n, ctx->sm_count)), dim3(256), 0, s, x, y, n, op, p0, p1);
     }
     return check_launch("unary");
 }
@@ -394,19 +445,19 @@ int binary_t(const b200ml_ctx* ctx, int op, const T* a, const T* b, T* y, int ra
     if (vec_ok && ca == 0 && cb == 0 && aligned16(a) && aligned16(b) && op <= B200ML_BIN_DIV) {
         const unsigned grid = grid_for((n / V + 1) / 2, ctx->sm_count);
         switch (op) {
-            case B200ML_BIN_ADD: binary_same_kernel<T, B200ML_BIN_ADD><<<grid, 256, 0, s>>>(a, b, y, n); break;
-            case B200ML_BIN_SUB: binary_same_kernel<T, B200ML_BIN_SUB><<<grid, 256, 0, s>>>(a, b, y, n); break;
-            case B200ML_BIN_MUL: binary_same_kernel<T, B200ML_BIN_MUL><<<grid, 256, 0, s>>>(a, b, y, n); break;
-            default: binary_same_kernel<T, B200ML_BIN_DIV><<<grid, 256, 0, s>>>(a, b, y, n); break;
+            case B200ML_BIN_ADD: launch_pdl(binary_same_kernel<T, B200ML_BIN_ADD>, dim3(grid), dim3(256), 0, s, a, b, y, n); break;
+            case B200ML_BIN_SUB: launch_pdl(binary_same_kernel<T, B200ML_BIN_SUB>, dim3(grid), dim3(256), 0, s, a, b, y, n); break;
+            case B200ML_BIN_MUL: launch_pdl(binary_same_kernel<T, B200ML_BIN_MUL>, dim3(grid), dim3(256), 0, s, a, b, y, n); break;
+            default: launch_pdl(binary_same_kernel<T, B200ML_BIN_DIV>, dim3(grid), dim3(256), 0, s, a, b, y, n); break;
         }
         return check_launch("binary_same");
     }
     if (vec_ok && ca == 0 && aligned16(a) && (cb == 0 ? aligned16(b) : cb == 1 ? true : (cb == 2 && last % V == 0 && aligned16(b)))) {
-        binary_fast_kernel<T><<<grid_for(n / V, ctx->sm_count), 256, 0, s>>>(a, b, y, n, op, cb, last, 0);
+        launch_pdl(binary_fast_kernel<T>, dim3(grid_for(n / V, ctx->sm_count)), dim3(256), 0, s, a, b, y, n, op, cb, last, 0);
         return check_launch("binary_fast");
     }
     if (vec_ok && cb == 0 && aligned16(b) && (ca == 1 || (ca == 2 && last % V == 0 && aligned16(a)))) {
-        binary_fast_kernel<T><<<grid_for(n / V, ctx->sm_count), 256, 0, s>>>(b, a, y, n, op, ca, last, 1);
+        launch_pdl(binary_fast_kernel<T>, dim3(grid_for(n / V, ctx->sm_count)), dim3(256), 0, s, b, a, y, n, op, ca, last, 1);
         return check_launch("binary_fast");
     }
     BcastArgs g{};
@@ -416,7 +467,7 @@ int binary_t(const b200ml_ctx* ctx, int op, const T* a, const T* b, T* y, int ra
         g.as[d] = shape[d] == 1 ? 0 : as[d];
         g.bs[d] = shape[d] == 1 ? 0 : bs[d];
     }
-    binary_bcast_kernel<T><<<grid_for(n, ctx->sm_count), 256, 0, s>>>(a, b, y, n, op, g);
+    launch_pdl(binary_bcast_kernel<T>, dim3(grid_for(n, ctx->sm_count)), dim3(256), 0, s, a, b, y, n, op, g);
     return check_launch("binary_bcast");
 }
 
@@ -431,14 +482,14 @@ int bias_act_t(const b200ml_ctx* ctx, const T* x, const T* bias, const T* residu
     if (vec) {
         const unsigned grid = grid_for((n / V + 1) / 2, ctx->sm_count);
         switch (act) {
-            case 0: bias_act2_kernel<T, 0><<<grid, 256, 0, s>>>(x, bias, residual, y, n, cols); break;
-            case B200ML_EPI_RELU: bias_act2_kernel<T, B200ML_EPI_RELU><<<grid, 256, 0, s>>>(x, bias, residual, y, n, cols); break;
+            case 0: launch_pdl(bias_act2_kernel<T, 0>, dim3(grid), dim3(256), 0, s, x, bias, residual, y, n, cols); break;
+            case B200ML_EPI_RELU: launch_pdl(bias_act2_kernel<T, B200ML_EPI_RELU>, dim3(grid), dim3(256), 0, s, x, bias, residual, y, n, cols); break;
             // GELU and Swish are bound by instruction issue, not by loads: two packets per thread made them slower
             // (17.3 -> 23.5 us for bias + GELU on [4096, 4096] fp16), so they keep one packet per thread
-            default: bias_act_kernel<T, true><<<grid_for(n / V, ctx->sm_count), 256, 0, s>>>(x, bias, residual, y, n, cols, act); break;
+            default: launch_pdl(bias_act_kernel<T, true>, dim3(grid_for(n / V, ctx->sm_count)), dim3(256), 0, s, x, bias, residual, y, n, cols, act); break;
         }
     }
-    else bias_act_kernel<T, false><<<grid_for(n, ctx->sm_count), 256, 0, s>>>(x, bias, residual, y, n, cols, act);
+    else launch_pdl(bias_act_kernel<T, false>, dim3(grid_for(n, ctx->sm_count)), dim3(256), 0, s, x, bias, residual, y, n, cols, act);
     return check_launch("bias_act");
 }
 
@@ -508,7 +559,7 @@ int transpose_t(const b200ml_ctx* ctx, const E* x, E* y, int rank, const int64_t
         g.i_ostride = ostr[ci];
         const int64_t gx = ceil_div(g.ni, 32), gy = ceil_div(g.nj, 32);
         if (gy <= 65535 && batches <= 65535) {
-            permute_tiled_kernel<E><<<dim3((unsigned)gx, (unsigned)gy, (unsigned)batches), 256, 0, s>>>(x, y, g);
+            launch_pdl(permute_tiled_kernel<E>, dim3(dim3((unsigned)gx, (unsigned)gy, (unsigned)batches)), dim3(256), 0, s, x, y, g);
             return check_launch("permute_tiled");
         }
     }
@@ -518,7 +569,7 @@ int transpose_t(const b200ml_ctx* ctx, const E* x, E* y, int rank, const int64_t
         g.oshape[d] = osh[d];
         g.istride[d] = ois[d];
     }
-    permute_gather_kernel<E><<<grid_for(n, ctx->sm_count), 256, 0, s>>>(x, y, n, g);
+    launch_pdl(permute_gather_kernel<E>, dim3(grid_for(n, ctx->sm_count)), dim3(256), 0, s, x, y, n, g);
     return check_launch("permute_gather");
 }
 
@@ -556,10 +607,10 @@ int transpose(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int
 int cast(const b200ml_ctx* ctx, int src, int dst, const void* x, void* y, int64_t n, cudaStream_t s) {
     if (n == 0) return B200ML_OK;
     const unsigned grid = grid_for(n, ctx->sm_count);
-    if (src == B200ML_F16 && dst == B200ML_F32) cast_kernel<__half, float><<<grid, 256, 0, s>>>((const __half*)x, (float*)y, n);
-    else if (src == B200ML_F32 && dst == B200ML_F16) cast_kernel<float, __half><<<grid, 256, 0, s>>>((const float*)x, (__half*)y, n);
-    else if (src == B200ML_F32) cast_kernel<float, float><<<grid, 256, 0, s>>>((const float*)x, (float*)y, n);
-    else cast_kernel<__half, __half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)y, n);
+    if (src == B200ML_F16 && dst == B200ML_F32) launch_pdl(cast_kernel<__half, float>, dim3(grid), dim3(256), 0, s, (const __half*)x, (float*)y, n);
+    else if (src == B200ML_F32 && dst == B200ML_F16) launch_pdl(cast_kernel<float, __half>, dim3(grid), dim3(256), 0, s, (const float*)x, (__half*)y, n);
+    else if (src == B200ML_F32) launch_pdl(cast_kernel<float, float>, dim3(grid), dim3(256), 0, s, (const float*)x, (float*)y, n);
+    else launch_pdl(cast_kernel<__half, __half>, dim3(grid), dim3(256), 0, s, (const __half*)x, (__half*)y, n);
     return check_launch("cast");
 }
 

@@ -23,6 +23,8 @@ struct CopyGeom {
 template <typename E>
 __global__ void __launch_bounds__(256) strided_copy_kernel(const E* __restrict__ x, E* __restrict__ y, uint64_t total,
                                                            const CopyGeom g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     // two units per thread and step: both loads are issued before the first store
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 2 * stride) {
@@ -63,6 +65,8 @@ template <typename E>
 __global__ void __launch_bounds__(256) gather_kernel(const E* __restrict__ data, const int64_t* __restrict__ idx,
                                                      E* __restrict__ y, uint64_t total, uint32_t n_idx, uint32_t inner,
                                                      int64_t dim, int32_t* status) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const uint64_t row = i / inner;
@@ -91,6 +95,8 @@ template <typename E>
 __global__ void __launch_bounds__(256) where_kernel(const uint8_t* __restrict__ c, const E* __restrict__ x,
                                                     const E* __restrict__ y, E* __restrict__ out, uint64_t total,
                                                     const WhereGeom g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         uint64_t rem = i;
@@ -115,6 +121,8 @@ template <typename E>
 __global__ void __launch_bounds__(256) where_fast_kernel(const uint8_t* __restrict__ c, const E* __restrict__ x,
                                                          const E* __restrict__ y, E* __restrict__ out, uint64_t n,
                                                          int y_scalar) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = 16 / sizeof(E);
     struct alignas(16) Vec { E v[V]; };
     struct alignas(V) Flags { uint8_t f[V]; };
@@ -157,6 +165,8 @@ __device__ __forceinline__ long long cmp_val(long long v) { return v; }
 template <typename T>
 __global__ void __launch_bounds__(256) compare_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                       uint8_t* __restrict__ out, uint64_t total, int op, const CmpGeom g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         uint64_t rem = i;
@@ -200,6 +210,8 @@ __device__ __forceinline__ bool cmp_apply(int op, A x, B y) {
 template <typename T>
 __global__ void __launch_bounds__(256) compare_fast_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                            uint8_t* __restrict__ out, uint64_t n, int op, int b_scalar) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = CmpVec<T>::V;
     struct alignas(16) Vec { T v[V]; };
     struct alignas(V) Flags { uint8_t f[V]; };
@@ -232,6 +244,8 @@ __device__ __forceinline__ void pool_st(__half* p, float v) { *p = __float2half_
 template <typename T>
 __global__ void __launch_bounds__(256) maxpool2d_kernel(const T* __restrict__ x, T* __restrict__ y, uint64_t total,
                                                         const PoolGeom g) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     const uint32_t opix = static_cast<uint32_t>(g.oh) * g.ow;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -261,7 +275,7 @@ unsigned grid_for(const b200ml_ctx* ctx, uint64_t total) {
 
 template <typename E>
 int launch_copy(const b200ml_ctx* ctx, const void* x, void* y, uint64_t total, const CopyGeom& g, cudaStream_t s) {
-    strided_copy_kernel<E><<<grid_for(ctx, (total + 1) / 2), 256, 0, s>>>(static_cast<const E*>(x), static_cast<E*>(y), total, g);
+    launch_pdl(strided_copy_kernel<E>, dim3(grid_for(ctx, (total + 1) / 2)), dim3(256), 0, s, static_cast<const E*>(x), static_cast<E*>(y), total, g);
     return check_launch("strided_copy");
 }
 
@@ -346,7 +360,7 @@ static int gather(const b200ml_ctx* ctx, int elem_bytes, const void* data, const
     const unsigned grid = grid_for(ctx, total);
     const uint32_t ni = static_cast<uint32_t>(n_idx), in = static_cast<uint32_t>(inner);
 #define B200ML_GATHER(E) \
-    gather_kernel<E><<<grid, 256, 0, s>>>(static_cast<const E*>(data), indices, static_cast<E*>(y), total, ni, in, dim, ctx->status_dev)
+    launch_pdl(gather_kernel<E>, dim3(grid), dim3(256), 0, s, static_cast<const E*>(data), indices, static_cast<E*>(y), total, ni, in, dim, ctx->status_dev)
     switch (unit) {
         case 1: B200ML_GATHER(uint8_t); break;
         case 2: B200ML_GATHER(uint16_t); break;
@@ -376,17 +390,17 @@ static int where(const b200ml_ctx* ctx, int elem_bytes, const void* cond, const 
         (yk == 0 || aligned16(y)) && (reinterpret_cast<uintptr_t>(cond) & 7u) == 0) {
         const unsigned fgrid = grid_for(ctx, total / (16 / elem_bytes) + 1);
         switch (elem_bytes) {
-            case 2: where_fast_kernel<uint16_t><<<fgrid, 256, 0, s>>>(c, (const uint16_t*)x, (const uint16_t*)y, (uint16_t*)out, total, yk == 0); break;
-            case 4: where_fast_kernel<uint32_t><<<fgrid, 256, 0, s>>>(c, (const uint32_t*)x, (const uint32_t*)y, (uint32_t*)out, total, yk == 0); break;
-            default: where_fast_kernel<uint64_t><<<fgrid, 256, 0, s>>>(c, (const uint64_t*)x, (const uint64_t*)y, (uint64_t*)out, total, yk == 0); break;
+            case 2: launch_pdl(where_fast_kernel<uint16_t>, dim3(fgrid), dim3(256), 0, s, c, (const uint16_t*)x, (const uint16_t*)y, (uint16_t*)out, total, yk == 0); break;
+            case 4: launch_pdl(where_fast_kernel<uint32_t>, dim3(fgrid), dim3(256), 0, s, c, (const uint32_t*)x, (const uint32_t*)y, (uint32_t*)out, total, yk == 0); break;
+            default: launch_pdl(where_fast_kernel<uint64_t>, dim3(fgrid), dim3(256), 0, s, c, (const uint64_t*)x, (const uint64_t*)y, (uint64_t*)out, total, yk == 0); break;
         }
         return check_launch("where");
     }
     const unsigned grid = grid_for(ctx, total);
     switch (elem_bytes) {
-        case 2: where_kernel<uint16_t><<<grid, 256, 0, s>>>(c, (const uint16_t*)x, (const uint16_t*)y, (uint16_t*)out, total, g); break;
-        case 4: where_kernel<uint32_t><<<grid, 256, 0, s>>>(c, (const uint32_t*)x, (const uint32_t*)y, (uint32_t*)out, total, g); break;
-        default: where_kernel<uint64_t><<<grid, 256, 0, s>>>(c, (const uint64_t*)x, (const uint64_t*)y, (uint64_t*)out, total, g); break;
+        case 2: launch_pdl(where_kernel<uint16_t>, dim3(grid), dim3(256), 0, s, c, (const uint16_t*)x, (const uint16_t*)y, (uint16_t*)out, total, g); break;
+        case 4: launch_pdl(where_kernel<uint32_t>, dim3(grid), dim3(256), 0, s, c, (const uint32_t*)x, (const uint32_t*)y, (uint32_t*)out, total, g); break;
+        default: launch_pdl(where_kernel<uint64_t>, dim3(grid), dim3(256), 0, s, c, (const uint64_t*)x, (const uint64_t*)y, (uint64_t*)out, total, g); break;
     }
     return check_launch("where");
 }
@@ -425,6 +439,8 @@ __device__ __forceinline__ D cast_one(S v) {
 
 template <typename S, typename D, bool TO_BOOL>
 __global__ void __launch_bounds__(256) cast_any_kernel(const S* __restrict__ x, D* __restrict__ y, uint64_t n) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const S v = x[i];
@@ -443,13 +459,13 @@ template <typename S>
 static int cast_from(const b200ml_ctx* ctx, int dst, const S* x, void* y, uint64_t n, cudaStream_t s) {
     const unsigned grid = grid_for(ctx, n);
     switch (dst) {
-        case B200ML_F16: cast_any_kernel<S, __half, false><<<grid, 256, 0, s>>>(x, static_cast<__half*>(y), n); break;
-        case B200ML_F32: cast_any_kernel<S, float, false><<<grid, 256, 0, s>>>(x, static_cast<float*>(y), n); break;
-        case B200ML_F64: cast_any_kernel<S, double, false><<<grid, 256, 0, s>>>(x, static_cast<double*>(y), n); break;
-        case B200ML_I32: cast_any_kernel<S, int32_t, false><<<grid, 256, 0, s>>>(x, static_cast<int32_t*>(y), n); break;
-        case B200ML_I64: cast_any_kernel<S, long long, false><<<grid, 256, 0, s>>>(x, static_cast<long long*>(y), n); break;
-        case B200ML_U8: cast_any_kernel<S, uint8_t, false><<<grid, 256, 0, s>>>(x, static_cast<uint8_t*>(y), n); break;
-        default: cast_any_kernel<S, uint8_t, true><<<grid, 256, 0, s>>>(x, static_cast<uint8_t*>(y), n); break;
+        case B200ML_F16: launch_pdl(cast_any_kernel<S, __half, false>, dim3(grid), dim3(256), 0, s, x, static_cast<__half*>(y), n); break;
+        case B200ML_F32: launch_pdl(cast_any_kernel<S, float, false>, dim3(grid), dim3(256), 0, s, x, static_cast<float*>(y), n); break;
+        case B200ML_F64: launch_pdl(cast_any_kernel<S, double, false>, dim3(grid), dim3(256), 0, s, x, static_cast<double*>(y), n); break;
+        case B200ML_I32: launch_pdl(cast_any_kernel<S, int32_t, false>, dim3(grid), dim3(256), 0, s, x, static_cast<int32_t*>(y), n); break;
+        case B200ML_I64: launch_pdl(cast_any_kernel<S, long long, false>, dim3(grid), dim3(256), 0, s, x, static_cast<long long*>(y), n); break;
+        case B200ML_U8: launch_pdl(cast_any_kernel<S, uint8_t, false>, dim3(grid), dim3(256), 0, s, x, static_cast<uint8_t*>(y), n); break;
+        default: launch_pdl(cast_any_kernel<S, uint8_t, true>, dim3(grid), dim3(256), 0, s, x, static_cast<uint8_t*>(y), n); break;
     }
     return check_launch("cast");
 }
@@ -485,20 +501,20 @@ static int compare(const b200ml_ctx* ctx, int kind, int op, const void* a, const
         const int v = kind == B200ML_F16 ? 8 : (kind == B200ML_F32 ? 4 : 2);
         const unsigned fgrid = grid_for(ctx, total / v + 1);
         if (kind == B200ML_F16)
-            compare_fast_kernel<__half><<<fgrid, 256, 0, s>>>((const __half*)a, (const __half*)b, o, total, op, bk == 0);
+            launch_pdl(compare_fast_kernel<__half>, dim3(fgrid), dim3(256), 0, s, (const __half*)a, (const __half*)b, o, total, op, bk == 0);
         else if (kind == B200ML_F32)
-            compare_fast_kernel<float><<<fgrid, 256, 0, s>>>((const float*)a, (const float*)b, o, total, op, bk == 0);
+            launch_pdl(compare_fast_kernel<float>, dim3(fgrid), dim3(256), 0, s, (const float*)a, (const float*)b, o, total, op, bk == 0);
         else
-            compare_fast_kernel<long long><<<fgrid, 256, 0, s>>>((const long long*)a, (const long long*)b, o, total, op, bk == 0);
+            launch_pdl(compare_fast_kernel<long long>, dim3(fgrid), dim3(256), 0, s, (const long long*)a, (const long long*)b, o, total, op, bk == 0);
         return check_launch("compare");
     }
     const unsigned grid = grid_for(ctx, total);
     if (kind == B200ML_F16)
-        compare_kernel<__half><<<grid, 256, 0, s>>>((const __half*)a, (const __half*)b, o, total, op, g);
+        launch_pdl(compare_kernel<__half>, dim3(grid), dim3(256), 0, s, (const __half*)a, (const __half*)b, o, total, op, g);
     else if (kind == B200ML_F32)
-        compare_kernel<float><<<grid, 256, 0, s>>>((const float*)a, (const float*)b, o, total, op, g);
+        launch_pdl(compare_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)a, (const float*)b, o, total, op, g);
     else
-        compare_kernel<long long><<<grid, 256, 0, s>>>((const long long*)a, (const long long*)b, o, total, op, g);
+        launch_pdl(compare_kernel<long long>, dim3(grid), dim3(256), 0, s, (const long long*)a, (const long long*)b, o, total, op, g);
     return check_launch("compare");
 }
 
@@ -507,9 +523,9 @@ static int maxpool2d(const b200ml_ctx* ctx, int dtype, const void* x, void* y, i
     if (total == 0) return B200ML_OK;
     const unsigned grid = grid_for(ctx, total);
     if (dtype == B200ML_F16)
-        maxpool2d_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(y), total, g);
+        launch_pdl(maxpool2d_kernel<__half>, dim3(grid), dim3(256), 0, s, static_cast<const __half*>(x), static_cast<__half*>(y), total, g);
     else
-        maxpool2d_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), static_cast<float*>(y), total, g);
+        launch_pdl(maxpool2d_kernel<float>, dim3(grid), dim3(256), 0, s, static_cast<const float*>(x), static_cast<float*>(y), total, g);
     return check_launch("maxpool2d");
 }
 

@@ -80,6 +80,8 @@ template <typename T, int ITERS, int R>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const T* __restrict__ x, const T* __restrict__ mask,
                                                            T* __restrict__ y, int64_t rows, int cols,
                                                            int64_t mask_row_div, float scale, int is_log) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = Vec<T>::N;
     const int lane = threadIdx.x & 31;
     const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
@@ -170,6 +172,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) softmax_block_kernel(const T* __restrict__ x, const T* __restrict__ mask,
                                                             T* __restrict__ y, int64_t cols, int64_t mask_row_div,
                                                             float scale, int is_log) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     __shared__ float red[8];
     __shared__ float bcast;
     const int64_t row = blockIdx.x;
@@ -222,6 +226,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) softmax_short_kernel(const T* __restrict__ x, const T* __restrict__ mask,
                                                             T* __restrict__ y, int64_t rows, int cols, int64_t mask_row_div,
                                                             float scale, int is_log, int lpr) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane / lpr, l = lane - sub * lpr;
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * 8 + warp) * (32 / lpr) + sub;
@@ -257,7 +263,7 @@ int softmax_t(const T* x, const T* mask, T* y, int64_t rows, int64_t cols, int64
         const int64_t blocks = ceil_div(rows, (int64_t)warps * rpw);
         B200ML_REQUIRE(blocks < (1ll << 31), "softmax: too many rows");
 #define SM_LAUNCH(I, R)                                                                                          \
-    softmax_warp_kernel<T, I, R><<<(unsigned)blocks, warps * 32, 0, stream>>>(x, mask, y, rows, (int)cols, mask_row_div, \
+    launch_pdl(softmax_warp_kernel<T, I, R>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream, x, mask, y, rows, (int)cols, mask_row_div, \
                                                                             scale, is_log)
         if (iters <= 1) SM_LAUNCH(1, 2);
         else if (iters <= 2) SM_LAUNCH(2, 2);
@@ -271,11 +277,11 @@ int softmax_t(const T* x, const T* mask, T* y, int64_t rows, int64_t cols, int64
         while (lpr < 32 && lpr < cols) lpr <<= 1;
         const int64_t blocks = ceil_div(rows, (int64_t)8 * (32 / lpr));
         B200ML_REQUIRE(blocks < (1ll << 31), "softmax: too many rows");
-        softmax_short_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(x, mask, y, rows, (int)cols, mask_row_div, scale, is_log, lpr);
+        launch_pdl(softmax_short_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, x, mask, y, rows, (int)cols, mask_row_div, scale, is_log, lpr);
         return check_launch("softmax_short");
     }
     B200ML_REQUIRE(rows < (1ll << 31), "softmax: too many rows");
-    softmax_block_kernel<T><<<(unsigned)rows, 256, 0, stream>>>(x, mask, y, cols, mask_row_div, scale, is_log);
+    launch_pdl(softmax_block_kernel<T>, dim3((unsigned)rows), dim3(256), 0, stream, x, mask, y, cols, mask_row_div, scale, is_log);
     return check_launch("softmax_block");
 }
 
@@ -359,6 +365,8 @@ __global__ void __launch_bounds__(256) layernorm_block_kernel(const T* __restric
                                                               const T* __restrict__ bias, const T* __restrict__ gamma,
                                                               const T* __restrict__ beta, T* __restrict__ y,
                                                               int64_t cols, float eps) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     __shared__ float red[8];
     __shared__ float bcast;
     const int64_t row = blockIdx.x;
@@ -426,7 +434,7 @@ int layernorm_t(const T* x, const T* residual, const T* bias, const T* gamma, co
         return check_launch("layernorm_warp");
     }
     B200ML_REQUIRE(rows < (1ll << 31), "layernorm: too many rows");
-    layernorm_block_kernel<T><<<(unsigned)rows, 256, 0, stream>>>(x, residual, bias, gamma, beta, y, cols, eps);
+    launch_pdl(layernorm_block_kernel<T>, dim3((unsigned)rows), dim3(256), 0, stream, x, residual, bias, gamma, beta, y, cols, eps);
     return check_launch("layernorm_block");
 }
 
@@ -452,6 +460,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                           float* __restrict__ partial, int64_t reduce, int slices,
                                                           RedOp op) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     __shared__ float red[8];
     const int64_t row = blockIdx.x;
     const int slice = blockIdx.y;
@@ -475,6 +485,8 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const T* __restrict__ 
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_finish_kernel(const float* __restrict__ partial, T* __restrict__ y,
                                                             int64_t rows, int slices, int64_t reduce, RedOp op) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -488,6 +500,8 @@ __global__ void __launch_bounds__(256) reduce_finish_kernel(const float* __restr
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_rows_warp_kernel(const T* __restrict__ x, T* __restrict__ y,
                                                                int64_t rows, int64_t reduce, RedOp op) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -502,6 +516,8 @@ __global__ void __launch_bounds__(256) reduce_rows_warp_kernel(const T* __restri
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_cols_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t outer,
                                                           int64_t reduce, int64_t inner, RedOp op) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= outer * inner) return;
     const int64_t o = idx / inner, i = idx % inner;
@@ -521,7 +537,7 @@ int reduce_t(const b200ml_ctx* ctx, int opcode, const T* x, T* y, int64_t outer,
         if (reduce <= 4096) {
             const int64_t blocks = ceil_div(outer, 8);
             B200ML_REQUIRE(blocks < (1ll << 31), "reduce: too many rows");
-            reduce_rows_warp_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(x, y, outer, reduce, op);
+            launch_pdl(reduce_rows_warp_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, x, y, outer, reduce, op);
             return check_launch("reduce_rows_warp");
         }
         // Long rows: cut each row into slices so that a full-tensor reduction still fills the GPU.
@@ -535,7 +551,7 @@ int reduce_t(const b200ml_ctx* ctx, int opcode, const T* x, T* y, int64_t outer,
         }
         B200ML_REQUIRE(outer < (1ll << 31), "reduce: too many rows");
         if (slices == 1) {
-            reduce_rows_kernel<T><<<dim3((unsigned)outer, 1), 256, 0, stream>>>(x, y, nullptr, reduce, 1, op);
+            launch_pdl(reduce_rows_kernel<T>, dim3(dim3((unsigned)outer, 1)), dim3(256), 0, stream, x, y, nullptr, reduce, 1, op);
             return check_launch("reduce_rows");
         }
         const int64_t need = outer * slices * (int64_t)sizeof(float);
@@ -543,15 +559,15 @@ int reduce_t(const b200ml_ctx* ctx, int opcode, const T* x, T* y, int64_t outer,
             return fail(B200ML_ERR_WORKSPACE, "reduce: needs %lld bytes of scratch, the context has %lld",
                         (long long)need, (long long)ctx->workspace_bytes);
         float* partial = static_cast<float*>(ctx->workspace);
-        reduce_rows_kernel<T><<<dim3((unsigned)outer, (unsigned)slices), 256, 0, stream>>>(x, y, partial, reduce, slices, op);
+        launch_pdl(reduce_rows_kernel<T>, dim3(dim3((unsigned)outer, (unsigned)slices)), dim3(256), 0, stream, x, y, partial, reduce, slices, op);
         int rc = check_launch("reduce_rows");
         if (rc) return rc;
-        reduce_finish_kernel<T><<<(unsigned)ceil_div(outer, 8), 256, 0, stream>>>(partial, y, outer, slices, reduce, op);
+        launch_pdl(reduce_finish_kernel<T>, dim3((unsigned)ceil_div(outer, 8)), dim3(256), 0, stream, partial, y, outer, slices, reduce, op);
         return check_launch("reduce_finish");
     }
     const int64_t blocks = ceil_div(outer * inner, 256);
     B200ML_REQUIRE(blocks < (1ll << 31), "reduce: too many outputs");
-    reduce_cols_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(x, y, outer, reduce, inner, op);
+    launch_pdl(reduce_cols_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, x, y, outer, reduce, inner, op);
     return check_launch("reduce_cols");
 }
 
