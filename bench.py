@@ -507,7 +507,7 @@ def run_profile_kernels(args):
     jobs.append(("transpose heads", lambda: K.transpose(tx, ty, (0, 2, 1, 3))))
     cx, cy = h(64 << 20), e32(64 << 20)
     jobs.append(("cast f16 -> f32", lambda: K.cast(cx, cy)))
-    ga, gw, gy = f(8192, 1024), f(1024, 1024), e32(8192, 1024)
+    ga, gw, gy = f(4096, 1024), f(1024, 1024), e32(4096, 1024)
     jobs.append(("gemm fp32 3xTF32", lambda: K.gemm(ga, gw, gy, b_layout=1)))
     sa, sw, sy = f(262144, 120), f(32, 120), e32(262144, 32)
     jobs.append(("gemm fp32 FMA", lambda: K.gemm(sa, sw, sy, b_layout=1)))

@@ -213,6 +213,15 @@ __device__ __forceinline__ float act_for(float v, int act) { return apply_act(v,
 template <>
 __device__ __forceinline__ float act_for<__half>(float v, int act) { return apply_act_f16(v, act); }
 
+__device__ __forceinline__ void gelu_store8(__half* y, float (&f)[8], const float (&b)[8], bool has_bias) {
+    if (has_bias) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += b[j];
+    }
+    *reinterpret_cast<uint4*>(y) = gelu_pack8(f);
+}
+__device__ __forceinline__ void gelu_store8(float*, float (&)[4], const float (&)[4], bool) {}  // never taken: fp32 keeps fp32 math
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias,
                                                        const T* __restrict__ residual, T* __restrict__ y, int64_t n,
@@ -221,12 +230,24 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
     pdl_wait();               // everything before this kernel in the stream has completed
     constexpr int V = VEC ? Pack<T>::N : 1;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * V;
-    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+    int64_t col = VEC ? first % cols : 0;  // the bias column advances by (stride mod cols): one 64-bit remainder per thread
+    const int64_t col_step = VEC ? stride % cols : 0;
+    const bool half_gelu = VEC && sizeof(T) == 2 && act == B200ML_EPI_GELU && !residual;
+    for (int64_t i = first; i < n; i += stride) {
         if (VEC) {
             float f[Pack<T>::N], t[Pack<T>::N];
             Pack<T>::load(x + i, f);
             if (bias) {
-                Pack<T>::load(bias + i % cols, t);
+                Pack<T>::load(bias + col, t);
+                col += col_step;
+                if (col >= cols) col -= cols;
+            }
+            if (half_gelu) {  // fp16 bias + GELU: pairs in half precision, half the instructions per value
+                gelu_store8(y + i, f, t, bias != nullptr);
+                continue;
+            }
+            if (bias) {
 #pragma unroll
                 for (int j = 0; j < Pack<T>::N; ++j) f[j] += t[j];
             }
@@ -246,15 +267,6 @@ __global__ void __launch_bounds__(256) bias_act_kernel(const T* __restrict__ x, 
         }
     }
 }
-
-__device__ __forceinline__ void gelu_store8(__half* y, float (&f)[8], const float (&b)[8], bool has_bias) {
-    if (has_bias) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] += b[j];
-    }
-    *reinterpret_cast<uint4*>(y) = gelu_pack8(f);
-}
-__device__ __forceinline__ void gelu_store8(float*, float (&)[4], const float (&)[4], bool) {}  // never taken: fp32 keeps fp32 math
 
 // The vector form with the activation fixed at compile time and two packets per thread and step: every 16-byte load of
 // both packets is issued before the first activation is evaluated.
@@ -485,7 +497,7 @@ int bias_act_t(const b200ml_ctx* ctx, const T* x, const T* bias, const T* residu
             case 0: launch_pdl(bias_act2_kernel<T, 0>, dim3(grid), dim3(256), 0, s, x, bias, residual, y, n, cols); break;
             case B200ML_EPI_RELU: launch_pdl(bias_act2_kernel<T, B200ML_EPI_RELU>, dim3(grid), dim3(256), 0, s, x, bias, residual, y, n, cols); break;
             // GELU and Swish are bound by instruction issue, not by loads: two packets per thread made them slower
-            // (17.3 -> 23.5 us for bias + GELU on [4096, 4096] fp16), so they keep one packet per thread
+            // (measured twice), so they keep one packet per thread; fp16 GELU runs on half2 pairs inside it
             default: launch_pdl(bias_act_kernel<T, true>, dim3(grid_for(n / V, ctx->sm_count)), dim3(256), 0, s, x, bias, residual, y, n, cols, act); break;
         }
     }
@@ -600,6 +612,14 @@ int bias_act(const b200ml_ctx* ctx, int dtype, const void* x, const void* bias, 
 
 int transpose(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int rank, const int64_t* shape,
               const int32_t* perm, cudaStream_t s) {
+    // The innermost axis stays innermost (the head split / merge of attention, [B,S,h,d] <-> [B,h,S,d]) and its rows are
+    // whole 16-byte packets: permute packets, not elements.
+    if (rank >= 2 && rank <= 6 && perm[rank - 1] == rank - 1 && (shape[rank - 1] * elem_bytes) % 16 == 0 && aligned16(x) && aligned16(y)) {
+        int64_t packed[6];
+        for (int d = 0; d < rank; ++d) packed[d] = shape[d];
+        packed[rank - 1] = shape[rank - 1] * elem_bytes / 16;
+        return transpose_t<uint4>(ctx, (const uint4*)x, (uint4*)y, rank, packed, perm, s);
+    }
     if (elem_bytes == 2) return transpose_t<uint16_t>(ctx, (const uint16_t*)x, (uint16_t*)y, rank, shape, perm, s);
     return transpose_t<uint32_t>(ctx, (const uint32_t*)x, (uint32_t*)y, rank, shape, perm, s);
 }

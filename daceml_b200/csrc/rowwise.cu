@@ -507,7 +507,28 @@ __global__ void __launch_bounds__(256) reduce_rows_warp_kernel(const T* __restri
     const int lane = threadIdx.x & 31;
     const T* xr = x + row * reduce;
     float v = op.init();
-    for (int64_t c = lane; c < reduce; c += 32) v = op.combine(v, ld1(xr + c));
+    constexpr int V = Vec<T>::N;
+    if (reduce % V == 0 && (reinterpret_cast<uintptr_t>(xr) & 15u) == 0) {
+        // 16-byte packets, four per lane in flight, each with its own partial result
+        const int64_t packets = reduce / V;
+        float acc[4] = {v, v, v, v};
+        for (int64_t p = lane; p < packets; p += 128) {
+            float f[4][V];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (p + 32 * u < packets) Vec<T>::load(xr + (p + 32 * u) * V, f[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (p + 32 * u < packets) {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) acc[u] = op.combine(acc[u], f[u][j]);
+                }
+            }
+        }
+        v = op.combine(op.combine(acc[0], acc[1]), op.combine(acc[2], acc[3]));
+    } else {
+        for (int64_t c = lane; c < reduce; c += 32) v = op.combine(v, ld1(xr + c));
+    }
     v = op.warp(v);
     if (lane == 0) st1(y + row, op.finish(v, reduce));
 }
