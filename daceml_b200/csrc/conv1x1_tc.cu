@@ -84,6 +84,14 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_base32(uint32_t smem_ad
     return d;
 }
 
+__device__ __forceinline__ float4 ld_shared_v4(uint32_t saddr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t saddr, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 __device__ __forceinline__ void st_shared_f32(uint32_t saddr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(saddr), "f"(v) : "memory");
 }
@@ -294,8 +302,8 @@ conv1x1_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                     if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
                     break;
                 }
-                float4* hi = reinterpret_cast<float4*>(smem + stage * PW_STAGE_BYTES);
-                float4* lo = reinterpret_cast<float4*>(smem + stage * PW_STAGE_BYTES + PW_TILE_BYTES);
+                // explicit shared-memory accesses (a generic pointer would cost a generic load and its long latency class)
+                const uint32_t hi = ptx::smem_u32(smem + stage * PW_STAGE_BYTES) + t * 16, lo = hi + PW_TILE_BYTES;
                 // packet t + NT j sits at byte 16 t + 2048 j of the stage: box j / 2, channel row t / 8 (even j) or
                 // t / 8 + 16 (odd j); the swizzle moves packets only inside a row
                 const int row0 = t >> 3, row1 = row0 + 16;
@@ -305,12 +313,11 @@ conv1x1_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                     g0 = c0 < args.c ? __ldg(args.gate + static_cast<int64_t>(n) * args.c + c0) : 0.0f;
                     g1 = c1 < args.c ? __ldg(args.gate + static_cast<int64_t>(n) * args.c + c1) : 0.0f;
                 }
-                const bool ones0 = kb == kb_ones && row0 == row_ones, ones1 = kb == kb_ones && row1 == row_ones;
                 // every packet is read before the first is written back: the reads are independent, while a read
                 // placed after a write to the same buffer would have to wait for it
                 float4 v[NPK];
 #pragma unroll
-                for (int j = 0; j < NPK; ++j) v[j] = hi[t + NT * j];
+                for (int j = 0; j < NPK; ++j) v[j] = ld_shared_v4(hi + j * (NT * 16));
 #pragma unroll
                 for (int j = 0; j < NPK; ++j) {
                     const float g = (j & 1) ? g1 : g0;
@@ -319,12 +326,16 @@ conv1x1_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                     split_tf32(v[j].y * g, h.y, l.y);
                     split_tf32(v[j].z * g, h.z, l.z);
                     split_tf32(v[j].w * g, h.w, l.w);
-                    if ((j & 1) ? ones1 : ones0) {  // the row of ones that meets the bias column of W
-                        h = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-                        l = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    st_shared_v4(hi + j * (NT * 16), h);
+                    st_shared_v4(lo + j * (NT * 16), l);
+                }
+                if (kb == kb_ones && (row0 == row_ones || row1 == row_ones)) {  // the row of ones that meets the bias column of W
+                    const int odd = row1 == row_ones ? 1 : 0;
+#pragma unroll
+                    for (int j = 0; j < NPK; j += 2) {
+                        st_shared_v4(hi + (j + odd) * (NT * 16), make_float4(1.0f, 1.0f, 1.0f, 1.0f));
+                        st_shared_v4(lo + (j + odd) * (NT * 16), make_float4(0.0f, 0.0f, 0.0f, 0.0f));
                     }
-                    hi[t + NT * j] = h;
-                    lo[t + NT * j] = l;
                 }
                 ptx::fence_proxy_async_smem();  // the tensor core reads shared memory through the async proxy
                 __syncwarp();
