@@ -456,6 +456,8 @@ def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
     ragged last pixel tile (H * W not a multiple of 128), channel counts that are not whole 32- or 16-blocks,
     squeeze-excite gate on the input, bias, activation and residual add.  Against the oracle at the fp32 tolerance,
     and against a float64 product at a bound that a single-TF32 product (relative error 5e-4) would break."""
+    if os.environ.get("B200ML_CONV_TC", "1") == "0":
+        pytest.skip("the tensor-core convolution is switched off")
     x = rng.standard_normal((n, cin) + hw).astype(np.float32)
     w = (rng.standard_normal((cout, cin, 1, 1)) * 0.1).astype(np.float32)
     b = (rng.standard_normal(cout) * 3).astype(np.float32)
