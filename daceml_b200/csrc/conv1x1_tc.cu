@@ -454,6 +454,7 @@ bool conv1x1_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_conv_params
     if (2 * npad * kpad * 4 > ctx->workspace_bytes) return false;
     if (hw * p->n < 16 * 1024) return false;                                 // too little work for two launches
     if (hw >= (1ll << 31) || p->n * ceil_div(hw, PW_BM) >= (1ll << 31) || p->n * p->c >= (1ll << 31)) return false;
+    if (p->n * p->c * hw * 4 >= (1ll << 40) || p->n * p->m * hw * 4 >= (1ll << 40)) return false;  // tensor-map strides are below 2^40 bytes
     return true;
 }
 

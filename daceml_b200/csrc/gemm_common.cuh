@@ -27,6 +27,7 @@ struct GemmArgs {
     int64_t ldr, r_so, r_si;
     float alpha, bias_scale, residual_scale;
     int32_t vec_ok;  // C (and residual) rows are 16-byte aligned
+    int32_t b_early;    // B is a constant of the stream: its first pipeline stages are fetched before griddepcontrol.wait
     int32_t tma_store;  // the kernel got a tensor map of C: finished tiles leave through shared memory and bulk stores
     __half* c;
     const __half* bias;

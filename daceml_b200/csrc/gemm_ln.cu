@@ -85,6 +85,24 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // A constant B (weights): its parts of the first stages are requested before the dependency wait (see gemm_tc.cu)
+    const int early = args.b_early ? (num_kb < LN_STAGES ? num_kb : LN_STAGES) : 0;
+    if (warp == 0 && early > 0) {
+        if (ptx::elect_one()) {
+            for (int kb = 0; kb < early; ++kb) {
+                uint8_t* sb = smem + kb * LN_STAGE_BYTES + A_TILE_BYTES;
+                ptx::mbar_expect_tx(&full_bar[kb], LN_STAGE_BYTES);
+                if (B_MN) {
+#pragma unroll
+                    for (int j = 0; j < LN_BN / 64; ++j)
+                        ptx::tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[kb], n0 + j * 64, kb * BK, 0, 0);
+                } else {
+                    ptx::tma_load_4d(sb, &tmap_b, &full_bar[kb], kb * BK, n0, 0, 0);
+                }
+            }
+        }
+        __syncwarp();
+    }
     pdl_wait();
 
     if (warp == 0) {
@@ -98,9 +116,11 @@ gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 }
                 uint8_t* sa = smem + stage * LN_STAGE_BYTES;
                 uint8_t* sb = sa + A_TILE_BYTES;
-                ptx::mbar_expect_tx(&full_bar[stage], LN_STAGE_BYTES);
+                const bool b_done = kb < early;  // requested before the dependency wait
+                if (!b_done) ptx::mbar_expect_tx(&full_bar[stage], LN_STAGE_BYTES);
                 ptx::tma_load_4d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, 0, 0);
-                if (B_MN) {
+                if (b_done) {
+                } else if (B_MN) {
 #pragma unroll
                     for (int j = 0; j < LN_BN / 64; ++j)
                         ptx::tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + j * 64, kb * BK, 0, 0);
@@ -230,6 +250,7 @@ int gemm_f16_layernorm(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaS
     args.bias = static_cast<const __half*>(p->bias);
     args.residual = static_cast<const __half*>(p->residual);
     args.status = ctx->status_dev;
+    args.b_early = (p->flags & B200ML_GEMM_B_CONSTANT) ? 1 : 0;
     la.gamma = static_cast<const __half*>(p->ln_gamma);
     la.beta = static_cast<const __half*>(p->ln_beta);
     la.eps = p->ln_eps;

@@ -87,6 +87,32 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // A constant B (weights) does not depend on the kernel in front of this one: the B parts of the first tile's first
+    // stages are requested before the dependency wait and stream in under the predecessor's tail (fresh stages: their
+    // empty barriers pass); the A parts and everything else follow after the wait.
+    const int early = (args.b_early && static_cast<int>(blockIdx.x) < args.num_tiles) ? (num_kb < STAGES ? num_kb : STAGES) : 0;
+    if (warp == 0 && early > 0) {
+        if (ptx::elect_one()) {
+            const int rest = static_cast<int>(blockIdx.x) / args.tiles_m;
+            const int nt = rest % args.tiles_n;
+            const int batch = rest / args.tiles_n;
+            const int bi = batch % args.batch_inner, bo = batch / args.batch_inner;
+            const int n0 = nt * BN;
+            for (int kb = 0; kb < early; ++kb) {
+                uint8_t* sb = smem + kb * S::STAGE_BYTES + A_TILE_BYTES;
+                ptx::mbar_expect_tx(&full_bar[kb], S::STAGE_BYTES);
+                if (B_MN) {
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        ptx::tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[kb], n0 + j * 64, kb * BK,
+                                         bi * args.b_use_inner, bo * args.b_use_outer);
+                } else {
+                    ptx::tma_load_4d(sb, &tmap_b, &full_bar[kb], kb * BK, n0, bi * args.b_use_inner, bo * args.b_use_outer);
+                }
+            }
+        }
+        __syncwarp();
+    }
     pdl_wait();  // everything above overlaps the previous kernel's tail
 
     if (warp == 0) {
@@ -115,10 +141,12 @@ gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     TRACE_ADD(tr_wait);
                     uint8_t* sa = smem + stage * S::STAGE_BYTES;
                     uint8_t* sb = sa + A_TILE_BYTES;
-                    ptx::mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+                    const bool b_done = tile == static_cast<int>(blockIdx.x) && kb < early;  // requested before the dependency wait
+                    if (!b_done) ptx::mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
                     ptx::tma_load_4d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, bi * args.a_use_inner,
                                      bo * args.a_use_outer);
-                    if (B_MN) {
+                    if (b_done) {
+                    } else if (B_MN) {
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
                             ptx::tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + j * 64, kb * BK,
@@ -417,6 +445,7 @@ int gemm_f16(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cudaStream_t st
     args.bias = static_cast<const __half*>(p->bias);
     args.residual = static_cast<const __half*>(p->residual);
     args.status = ctx->status_dev;
+    args.b_early = (p->flags & B200ML_GEMM_B_CONSTANT) ? 1 : 0;
 #ifdef B200ML_TRACE
     args.trace = static_cast<long long*>(ctx->workspace);  // instrumented builds only: per-CTA cycle counters
 #else

@@ -90,6 +90,33 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     ptx::cluster_sync();  // both CTAs' barriers exist before any remote arrive or load completion
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // A constant B (weights) does not depend on the kernel in front of this one: the B halves of the first tile's first
+    // stages are requested before the dependency wait and stream in under the predecessor's tail.  The stages are fresh
+    // (their empty barriers pass), the A halves and everything else follow after the wait.
+    const int early = (args.b_early && pair < args.num_tiles) ? (num_kb < STAGES ? num_kb : STAGES) : 0;
+    if (warp == 0 && early > 0) {
+        if (ptx::elect_one()) {
+            const int rest = pair / args.tiles_m;
+            const int nt = rest % args.tiles_n;
+            const int batch = rest / args.tiles_n;
+            const int bi = batch % args.batch_inner, bo = batch / args.batch_inner;
+            const int n0 = nt * BN + static_cast<int>(cta) * HALF_N;
+            for (int kb = 0; kb < early; ++kb) {
+                uint8_t* sb = smem + kb * S::STAGE_BYTES + A_TILE_BYTES;
+                const uint32_t bar = ptx::leader_addr(&full_bar[kb]);
+                if (cta == 0) ptx::mbar_expect_tx(&full_bar[kb], 2 * S::STAGE_BYTES);
+                if (B_MN) {
+#pragma unroll
+                    for (int j = 0; j < HALF_N / 64; ++j)
+                        ptx::tma_load_4d_pair(sb + j * (64 * BK * 2), &tmap_b, bar, n0 + j * 64, kb * BK,
+                                              bi * args.b_use_inner, bo * args.b_use_outer);
+                } else {
+                    ptx::tma_load_4d_pair(sb, &tmap_b, bar, kb * BK, n0, bi * args.b_use_inner, bo * args.b_use_outer);
+                }
+            }
+        }
+        __syncwarp();
+    }
     pdl_wait();  // everything above overlaps the previous kernel's tail
 
     if (warp == 0) {
@@ -116,9 +143,11 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     uint8_t* sa = smem + stage * S::STAGE_BYTES;
                     uint8_t* sb = sa + A_TILE_BYTES;
                     const uint32_t bar = ptx::leader_addr(&full_bar[stage]);
-                    if (cta == 0) ptx::mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+                    const bool b_done = tile == pair && kb < early;  // requested before the dependency wait
+                    if (cta == 0 && !b_done) ptx::mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
                     ptx::tma_load_4d_pair(sa, &tmap_a, bar, kb * BK, m0, bi * args.a_use_inner, bo * args.a_use_outer);
-                    if (B_MN) {
+                    if (b_done) {
+                    } else if (B_MN) {
 #pragma unroll
                         for (int j = 0; j < HALF_N / 64; ++j)
                             ptx::tma_load_4d_pair(sb + j * (64 * BK * 2), &tmap_b, bar, n0 + j * 64, kb * BK,

@@ -39,15 +39,17 @@ def gemm_raw(ctx, params, stream):
 
 
 def gemm(a, b, out, *, b_layout=0, a_layout=0, bias=None, residual=None, act=0, alpha=1.0, bias_scale=1.0,
-         residual_scale=1.0, ln=None):
+         residual_scale=1.0, ln=None, b_constant=False):
     """out[M,N] = act(alpha * A.B + bias_scale * bias) + residual_scale * residual for 2-D operands;
     with ``ln=(gamma, beta, eps)`` the rows of that result are layer-normalised before they are stored.
 
     ``a`` is [M,K] (or [K,M] with ``a_layout=1``), ``b`` is [K,N] (``b_layout=0``) or [N,K]
-    (``b_layout=1``); rows may be strided (last dimension contiguous)."""
+    (``b_layout=1``); rows may be strided (last dimension contiguous).  ``b_constant``: nothing enqueued earlier on
+    the stream writes ``b`` (a weight), so the kernel may fetch it before the preceding kernel has finished."""
     ctx = _ctx(a)
     p = L.GemmParams()
     p.dtype = L.dtype_code(a.dtype)
+    p.flags = L.GEMM_B_CONSTANT if b_constant else 0
     p.a_layout, p.b_layout = a_layout, b_layout
     m, k = (a.shape[0], a.shape[1]) if a_layout == 0 else (a.shape[1], a.shape[0])
     n = b.shape[1] if b_layout == 0 else b.shape[0]

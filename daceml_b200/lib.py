@@ -19,6 +19,7 @@ LIB_PATH = os.environ.get("DACEML_B200_LIB") or os.path.join(_HERE, "lib", "libd
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
 F16, F32, I64, I32, F64, U8, BOOL = range(7)
 EPI_BIAS, EPI_RELU, EPI_GELU, EPI_RESIDUAL, EPI_SWISH, EPI_LAYERNORM = 1, 2, 4, 8, 16, 32
+GEMM_B_CONSTANT = 1
 RED_SUM, RED_MEAN, RED_MAX, RED_MIN = 0, 1, 2, 3
 (UN_COPY, UN_RELU, UN_SIGMOID, UN_ERF, UN_SQRT, UN_EXP, UN_LOG, UN_TANH, UN_SWISH, UN_GELU, UN_RECIPROCAL,
  UN_LEAKYRELU, UN_AFFINE, UN_POWS, UN_SOFTPLUS, UN_CLIP, UN_NEG, UN_ABS) = range(18)
@@ -57,7 +58,7 @@ class GemmParams(ctypes.Structure):
         ("ldc", ctypes.c_int64), ("c_stride_outer", ctypes.c_int64), ("c_stride_inner", ctypes.c_int64),
         ("ldr", ctypes.c_int64), ("r_stride_outer", ctypes.c_int64), ("r_stride_inner", ctypes.c_int64),
         ("alpha", ctypes.c_float), ("bias_scale", ctypes.c_float), ("residual_scale", ctypes.c_float),
-        ("reserved", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
         ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p),
         ("c", ctypes.c_void_p),
         ("ln_gamma", ctypes.c_void_p), ("ln_beta", ctypes.c_void_p), ("ln_eps", ctypes.c_float), ("reserved2", ctypes.c_int32),

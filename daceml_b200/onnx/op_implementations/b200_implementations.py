@@ -60,11 +60,20 @@ def _matmul_plan(a_shape, b_shape):
     return None
 
 
+def _b_is_constant(node, state, sdfg, conn="B"):
+    """Whether the array on ``conn`` is a constant of the SDFG (a weight bound at build time): no kernel of the graph
+    writes it, so a GEMM may fetch it before the kernel in front of it has finished."""
+    for e in state.in_edges_by_connector(node, conn):
+        return e.data.data in sdfg.constants
+    return False
+
+
 def _launch_gemm(a, b, out, plan, *, b_layout=0, a_layout=0, alpha=1.0, bias=None, bias_scale=1.0, residual=None,
-                 residual_scale=1.0, act=0, ln=None):
+                 residual_scale=1.0, act=0, ln=None, b_constant=False):
     ctx = L.get_context(a.device)
     p = L.GemmParams()
     p.dtype = L.dtype_code(a.dtype)
+    p.flags = L.GEMM_B_CONSTANT if b_constant else 0
     p.a_layout, p.b_layout = a_layout, b_layout
     m, k, n = plan["m"], plan["k"], plan["n"]
     p.m, p.n, p.k = m, n, k
@@ -102,9 +111,10 @@ class B200MatMul(ONNXForward):
     def forward(node, state, sdfg):
         a, b = in_desc_with_name(node, state, sdfg, "A"), in_desc_with_name(node, state, sdfg, "B")
         plan = _matmul_plan(a.shape, b.shape)
+        bc = _b_is_constant(node, state, sdfg)
 
         def run(ins, outs):
-            _launch_gemm(ins["A"], ins["B"], outs["Y"], plan)
+            _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, b_constant=bc)
 
         return KernelTasklet(node.label, run, kernels=("gemm",))
 
@@ -138,10 +148,11 @@ class B200Gemm(ONNXForward):
         plan = dict(batch=1, m=m, k=k, n=n, a_batched=False, b_batched=False)
         mode = B200Gemm._c_mode(node, state, sdfg)
         alpha, beta = float(node.alpha), float(node.beta)
+        bc = _b_is_constant(node, state, sdfg)
 
         def run(ins, outs):
             c = ins.get("C") if mode != "none" else None
-            _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, a_layout=ta, b_layout=tb, alpha=alpha,
+            _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, a_layout=ta, b_layout=tb, alpha=alpha, b_constant=bc,
                          bias=c if mode == "bias" else None, bias_scale=beta,
                          residual=c if mode == "full" else None, residual_scale=beta)
 
@@ -701,11 +712,12 @@ class B200FusedMatMul(ONNXForward):
         n = b.shape[0] if tb else b.shape[1]
         plan = dict(batch=1, m=prod(a.shape[:-1]), k=k, n=n, a_batched=False, b_batched=False)
         act, alpha = _ACT[node.activation], float(node.alpha)
+        bc = _b_is_constant(node, state, sdfg)
         if node.ln_epsilon is None:
 
             def run(ins, outs):
                 _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
-                             residual=ins.get("Residual"), act=act)
+                             residual=ins.get("Residual"), act=act, b_constant=bc)
 
             return KernelTasklet(node.label, run, kernels=("gemm",))
 
@@ -717,7 +729,8 @@ class B200FusedMatMul(ONNXForward):
 
             def run_fused(ins, outs):
                 _launch_gemm(ins["A"], ins["B"], outs["Y"], plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
-                             residual=ins.get("Residual"), act=act, ln=(ins.get("LnScale"), ins.get("LnBias"), eps))
+                             residual=ins.get("Residual"), act=act, ln=(ins.get("LnScale"), ins.get("LnBias"), eps),
+                             b_constant=bc)
 
             return KernelTasklet(node.label, run_fused, kernels=("gemm_layernorm",))
         y_desc = out_desc_with_name(node, state, sdfg, "Y")
@@ -726,7 +739,7 @@ class B200FusedMatMul(ONNXForward):
         def run_split(ins, outs):
             y, tmp = outs["Y"], outs[pre]
             _launch_gemm(ins["A"], ins["B"], tmp, plan, b_layout=tb, alpha=alpha, bias=ins.get("Bias"),
-                         residual=ins.get("Residual"), act=act)
+                         residual=ins.get("Residual"), act=act, b_constant=bc)
             K.layernorm(tmp, y, gamma=ins.get("LnScale"), beta=ins.get("LnBias"), eps=eps)
 
         return KernelTasklet(node.label, run_split, kernels=("gemm", "layernorm"))

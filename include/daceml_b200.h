@@ -102,6 +102,12 @@ enum {
     B200ML_EPI_LAYERNORM = 32
 };
 
+/* b200ml_gemm_params.flags.  B_CONSTANT: nothing enqueued earlier on the stream writes B (a weight bound when the
+ * graph was built, as DaCeML binds parameters, daceml/onnx/onnx_importer.py:256-297).  The fp16 tensor-core kernels
+ * then fetch the first pipeline stages of B before they wait for the preceding kernel to finish (programmatic
+ * dependent launch): the weights stream in under the predecessor's tail.  Leave it 0 for a B that is an activation. */
+#define B200ML_GEMM_B_CONSTANT 1
+
 typedef struct {
     int32_t dtype;    /* B200ML_F16: tcgen05 tensor cores, fp32 accumulate, fp16 in/out.
                          B200ML_F32: FP32 FMA (no TF32 rounding). */
@@ -116,7 +122,7 @@ typedef struct {
     int64_t ldc, c_stride_outer, c_stride_inner;
     int64_t ldr, r_stride_outer, r_stride_inner;
     float alpha, bias_scale, residual_scale;
-    int32_t reserved;
+    int32_t flags; /* B200ML_GEMM_B_CONSTANT or 0 */
     const void* a;
     const void* b;
     const void* bias;     /* [N] or null */
