@@ -201,18 +201,16 @@ def run_hbm_kernels(args, emit=True):
     parts = [torch.empty(T, HIDDEN, dtype=torch.float16, device=dev) for _ in range(3)]
 
     def split3(i):
-        for j in range(3):
-            K.strided_copy(qkv[i].narrow(1, j * HIDDEN, HIDDEN), parts[j])
+        K.strided_copy_parts([qkv[i].narrow(1, j * HIDDEN, HIDDEN) for j in range(3)], parts)
 
-    cases.append(("strided_copy_kernel", "Split of [4096, 3072] fp16 into three [4096, 1024] (3 launches)", n, 2 * T * 3 * HIDDEN * 2, split3))
+    cases.append(("strided_copy_parts_kernel", "Split of [4096, 3072] fp16 into three [4096, 1024] (1 launch)", n, 2 * T * 3 * HIDDEN * 2, split3))
     cat = [torch.empty(T, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
     halves = [rnd(T, FFN // 2) for _ in range(2 * n)]
 
     def concat2(i):
-        K.strided_copy(halves[2 * i], cat[i].narrow(1, 0, FFN // 2))
-        K.strided_copy(halves[2 * i + 1], cat[i].narrow(1, FFN // 2, FFN // 2))
+        K.strided_copy_parts([halves[2 * i], halves[2 * i + 1]], [cat[i].narrow(1, 0, FFN // 2), cat[i].narrow(1, FFN // 2, FFN // 2)])
 
-    cases.append(("strided_copy_kernel", "Concat of two [4096, 2048] fp16 along the last axis (2 launches)", n, 2 * T * FFN * 2, concat2))
+    cases.append(("strided_copy_parts_kernel", "Concat of two [4096, 2048] fp16 along the last axis (1 launch)", n, 2 * T * FFN * 2, concat2))
     table = rnd(30522, HIDDEN)
     ids = [torch.randint(0, 30522, (64, SEQ), generator=g).to(dev) for _ in range(4)]
     emb = [torch.empty(64, SEQ, HIDDEN, dtype=torch.float16, device=dev) for _ in range(4)]

@@ -59,6 +59,57 @@ __global__ void __launch_bounds__(256) strided_copy_kernel(const E* __restrict__
     }
 }
 
+// Up to eight copies in one launch (the parts of a Split or a Concat): blockIdx.y names the part.
+constexpr int MAXPARTS = 8;
+struct CopyParts {
+    CopyGeom g[MAXPARTS];
+    const void* x[MAXPARTS];
+    void* y[MAXPARTS];
+    uint64_t total[MAXPARTS];
+};
+
+template <typename E>
+__global__ void __launch_bounds__(256) strided_copy_parts_kernel(const __grid_constant__ CopyParts parts) {
+    pdl_launch_dependents();  // the next kernel of the stream may begin its set-up
+    pdl_wait();               // everything before this kernel in the stream has completed
+    const int part = blockIdx.y;
+    const CopyGeom& g = parts.g[part];
+    const E* __restrict__ x = static_cast<const E*>(parts.x[part]);
+    E* __restrict__ y = static_cast<E*>(parts.y[part]);
+    const uint64_t total = parts.total[part];
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += 2 * stride) {
+        int64_t xo[2], yo[2];
+        const bool second = i + stride < total;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            uint64_t rem = i + u * stride;
+            xo[u] = 0, yo[u] = 0;
+#pragma unroll
+            for (int d = MAXR - 1; d >= 0; --d) {
+                if (d < g.rank) {
+                    uint64_t c;
+                    if (rem < (1ull << 32)) {
+                        const uint32_t r32 = static_cast<uint32_t>(rem);
+                        c = r32 % g.shape[d];
+                        rem = r32 / g.shape[d];
+                    } else {
+                        c = rem % g.shape[d];
+                        rem = rem / g.shape[d];
+                    }
+                    xo[u] += static_cast<int64_t>(c) * g.xs[d];
+                    yo[u] += static_cast<int64_t>(c) * g.ys[d];
+                }
+            }
+        }
+        const E v0 = x[xo[0]];
+        E v1 = E();
+        if (second) v1 = x[xo[1]];
+        y[yo[0]] = v0;
+        if (second) y[yo[1]] = v1;
+    }
+}
+
 // y[o][j][k] = data[o][wrap(idx[j])][k]; k runs over `inner` units of E.  An index outside [-dim, dim) writes zeros and
 // records DEV_BAD_INDEX in the context's status word.
 template <typename E>
@@ -295,8 +346,9 @@ static int stride_kind(int rank, const int64_t* shape, const int64_t* st) {
     return contiguous ? 1 : (scalar ? 0 : -1);
 }
 
-static int strided_copy(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int rank, const int64_t* shape,
-                 const int64_t* xs, const int64_t* ys, cudaStream_t s) {
+// Coalesces the index space of one copy and picks the unit that moves (1 .. 16 bytes).  *total == 0: nothing to copy.
+static int normalize_copy(int elem_bytes, const void* x, const void* y, int rank, const int64_t* shape, const int64_t* xs,
+                          const int64_t* ys, CopyGeom* out, uint64_t* total_out, int* unit_out) {
     // drop unit axes, merge neighbours that are contiguous with respect to each other on both sides
     CopyGeom g = {};
     int64_t shp[MAXR];
@@ -316,6 +368,7 @@ static int strided_copy(const b200ml_ctx* ctx, int elem_bytes, const void* x, vo
             ++r;
         }
     }
+    *total_out = total;
     if (total == 0) return B200ML_OK;
     if (r == 0) {
         shp[0] = 1, g.xs[0] = 1, g.ys[0] = 1, r = 1;
@@ -336,6 +389,19 @@ static int strided_copy(const b200ml_ctx* ctx, int elem_bytes, const void* x, vo
     }
     g.rank = r;
     for (int d = 0; d < r; ++d) g.shape[d] = static_cast<uint32_t>(shp[d]);
+    *out = g;
+    *total_out = total;
+    *unit_out = unit;
+    return B200ML_OK;
+}
+
+static int strided_copy(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int rank, const int64_t* shape,
+                 const int64_t* xs, const int64_t* ys, cudaStream_t s) {
+    CopyGeom g = {};
+    uint64_t total = 0;
+    int unit = elem_bytes;
+    const int rc = normalize_copy(elem_bytes, x, y, rank, shape, xs, ys, &g, &total, &unit);
+    if (rc || total == 0) return rc;
     switch (unit) {
         case 1: return launch_copy<uint8_t>(ctx, x, y, total, g, s);
         case 2: return launch_copy<uint16_t>(ctx, x, y, total, g, s);
@@ -529,6 +595,54 @@ static int maxpool2d(const b200ml_ctx* ctx, int dtype, const void* x, void* y, i
     return check_launch("maxpool2d");
 }
 
+namespace {
+template <typename E>
+int launch_parts(const b200ml_ctx* ctx, const CopyParts& parts, int nparts, uint64_t largest, cudaStream_t s) {
+    const dim3 grid(grid_for(ctx, (largest + 1) / 2), (unsigned)nparts);
+    launch_pdl(strided_copy_parts_kernel<E>, grid, dim3(256), 0, s, parts);
+    return check_launch("strided_copy_parts");
+}
+}  // namespace
+
+// Several copies of the same element size at once.  One launch when every part moves the same unit, else one per part.
+static int strided_copy_parts(const b200ml_ctx* ctx, int elem_bytes, int nparts, const void* const* xs_, void* const* ys_,
+                              int rank, const int64_t* shapes, const int64_t* x_strides, const int64_t* y_strides,
+                              cudaStream_t s) {
+    CopyParts parts = {};
+    int units[MAXPARTS];
+    uint64_t largest = 0;
+    int live = 0;
+    bool same = true;
+    for (int p = 0; p < nparts; ++p) {
+        CopyGeom g = {};
+        uint64_t total = 0;
+        int unit = elem_bytes;
+        const int rc = normalize_copy(elem_bytes, xs_[p], ys_[p], rank, shapes + p * rank, x_strides + p * rank,
+                                      y_strides + p * rank, &g, &total, &unit);
+        if (rc) return rc;
+        if (total == 0) continue;
+        parts.g[live] = g, parts.x[live] = xs_[p], parts.y[live] = ys_[p], parts.total[live] = total, units[live] = unit;
+        same = same && unit == units[0];
+        largest = total > largest ? total : largest;
+        ++live;
+    }
+    if (live == 0) return B200ML_OK;
+    if (!same || live == 1) {
+        for (int p = 0; p < nparts; ++p) {
+            const int rc = strided_copy(ctx, elem_bytes, xs_[p], ys_[p], rank, shapes + p * rank, x_strides + p * rank,
+                                        y_strides + p * rank, s);
+            if (rc) return rc;
+        }
+        return B200ML_OK;
+    }
+    switch (units[0]) {
+        case 1: return launch_parts<uint8_t>(ctx, parts, live, largest, s);
+        case 2: return launch_parts<uint16_t>(ctx, parts, live, largest, s);
+        case 4: return launch_parts<uint32_t>(ctx, parts, live, largest, s);
+        case 8: return launch_parts<uint64_t>(ctx, parts, live, largest, s);
+        default: return launch_parts<uint4>(ctx, parts, live, largest, s);
+    }
+}
 }  // namespace b200ml
 
 using namespace b200ml;
@@ -551,6 +665,27 @@ int b200ml_strided_copy(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void
     B200ML_REQUIRE(x && y, "strided_copy: null tensor");
     DeviceGuard guard(ctx->device);
     return strided_copy(ctx, elem_bytes, x, y, rank, shape, x_strides, y_strides, static_cast<cudaStream_t>(stream));
+}
+
+int b200ml_strided_copy_parts(b200ml_ctx* ctx, int32_t elem_bytes, int32_t nparts, const void* const* xs, void* const* ys,
+                              int32_t rank, const int64_t* shapes, const int64_t* x_strides, const int64_t* y_strides,
+                              b200ml_stream stream) {
+    B200ML_REQUIRE(ctx, "strided_copy_parts: null context");
+    B200ML_REQUIRE(elem_bytes == 1 || elem_bytes == 2 || elem_bytes == 4 || elem_bytes == 8,
+                   "strided_copy_parts: element size %d not supported", elem_bytes);
+    B200ML_REQUIRE(nparts >= 1 && nparts <= MAXPARTS, "strided_copy_parts: %d parts, 1 to 8 are taken", nparts);
+    B200ML_REQUIRE(rank >= 1 && rank <= MAXR, "strided_copy_parts: rank %d not in [1, 6]", rank);
+    B200ML_REQUIRE(xs && ys && shapes && x_strides && y_strides, "strided_copy_parts: null argument");
+    for (int p = 0; p < nparts; ++p) {
+        B200ML_REQUIRE(xs[p] && ys[p], "strided_copy_parts: null tensor in part %d", p);
+        for (int d = 0; d < rank; ++d) {
+            const int64_t ext = shapes[p * rank + d], xst = x_strides[p * rank + d], yst = y_strides[p * rank + d];
+            B200ML_REQUIRE(ext >= 0 && xst >= 0 && yst >= 0, "strided_copy_parts: negative extent or stride");
+            B200ML_REQUIRE(yst > 0 || ext <= 1, "strided_copy_parts: destination stride 0 on an axis of extent %lld", (long long)ext);
+        }
+    }
+    DeviceGuard guard(ctx->device);
+    return strided_copy_parts(ctx, elem_bytes, nparts, xs, ys, rank, shapes, x_strides, y_strides, static_cast<cudaStream_t>(stream));
 }
 
 int b200ml_gather(b200ml_ctx* ctx, int32_t elem_bytes, const void* data, const int64_t* indices, void* y, int64_t outer,

@@ -193,6 +193,33 @@ def strided_copy(src, dst):
     return dst
 
 
+def strided_copy_parts(srcs, dsts):
+    """``dsts[i][...] = srcs[i]`` for several pairs of equally shaped views of one dtype and rank: the parts of a Split
+    or a Concat in one launch (eight parts per launch)."""
+    if len(srcs) != len(dsts) or not srcs:
+        raise L.B200Error(L.ERR_INVALID, "strided_copy_parts: need as many sources as destinations, at least one")
+    rank, dtype = srcs[0].dim(), srcs[0].dtype
+    pairs = [(s_, d_) for s_, d_ in zip(srcs, dsts) if s_.numel() > 0]
+    for s_, d_ in zip(srcs, dsts):
+        if tuple(s_.shape) != tuple(d_.shape) or s_.dtype != dtype or d_.dtype != dtype or s_.dim() != rank:
+            raise L.B200Error(L.ERR_INVALID, "strided_copy_parts: parts must agree in dtype and rank, and each pair in shape")
+    if rank == 0 or rank > 6 or len(pairs) == 1:
+        for s_, d_ in pairs:
+            strided_copy(s_, d_)
+        return dsts
+    ctx = _ctx(dsts[0])
+    for lo in range(0, len(pairs), 8):
+        chunk = pairs[lo:lo + 8]
+        n = len(chunk)
+        xs = (ctypes.c_void_p * n)(*[s_.data_ptr() for s_, _ in chunk])
+        ys = (ctypes.c_void_p * n)(*[d_.data_ptr() for _, d_ in chunk])
+        shapes = _i64([e for s_, _ in chunk for e in s_.shape])
+        xst = _i64([e for s_, _ in chunk for e in s_.stride()])
+        yst = _i64([e for _, d_ in chunk for e in d_.stride()])
+        L.check(ctx.lib.b200ml_strided_copy_parts(ctx.handle, dtype.itemsize, n, xs, ys, rank, shapes, xst, yst, _stream(dsts[0])))
+    return dsts
+
+
 def gather(data, indices, out, axis=0):
     """``out = numpy.take(data, indices, axis)`` with int64 ``indices`` of any shape."""
     ctx = _ctx(data)

@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = [
     "b200ml_last_error", "b200ml_version", "b200ml_launch_count", "b200ml_gemm", "b200ml_softmax",
     "b200ml_layernorm", "b200ml_reduce", "b200ml_reduce_static", "b200ml_unary", "b200ml_binary", "b200ml_bias_act", "b200ml_transpose",
     "b200ml_cast", "b200ml_conv2d", "b200ml_se_gate", "b200ml_attention_f16", "b200ml_strided_copy", "b200ml_gather",
-    "b200ml_where", "b200ml_compare", "b200ml_maxpool2d", "b200ml_wait_probe",
+    "b200ml_where", "b200ml_compare", "b200ml_maxpool2d", "b200ml_wait_probe", "b200ml_strided_copy_parts",
 ]
 
 
@@ -139,6 +139,7 @@ def load_library(path=None):
         lib.b200ml_compare.argtypes = [vp, c_i32, c_i32, vp, vp, vp, c_i32, i64p, i64p, i64p, vp]
         lib.b200ml_maxpool2d.argtypes = [vp, c_i32, vp, vp, c_i64, c_i64, c_i64] + [c_i32] * 8 + [vp]
         lib.b200ml_wait_probe.argtypes = [vp, c_i64, vp, vp]
+        lib.b200ml_strided_copy_parts.argtypes = [vp, c_i32, c_i32, ctypes.POINTER(vp), ctypes.POINTER(vp), c_i32, i64p, i64p, i64p, vp]
         for name in EXPORTED_SYMBOLS:
             fn = getattr(lib, name)
             if name not in ("b200ml_last_error", "b200ml_launch_count", "b200ml_ctx_workspace_bytes"):

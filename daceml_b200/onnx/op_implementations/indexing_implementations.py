@@ -126,7 +126,7 @@ def _split_sizes(node, state, sdfg):
 
 @op_implementation(op="Split", name="b200")
 class B200Split(ONNXForward):
-    """Split along ``axis`` into the sizes of the ``split`` attribute (equal parts when absent): one copy per output."""
+    """Split along ``axis`` into the sizes of the ``split`` attribute (equal parts when absent): one launch copies all parts."""
 
     @staticmethod
     def forward_can_be_applied(node, state, sdfg):
@@ -139,12 +139,14 @@ class B200Split(ONNXForward):
         axis, conns, sizes = _split_sizes(node, state, sdfg)
 
         def run(ins, outs):
-            off = 0
+            off, srcs, dsts = 0, [], []
             for c, n in zip(conns, sizes):
-                K.strided_copy(ins["input"].narrow(axis, off, n), outs[c])
+                srcs.append(ins["input"].narrow(axis, off, n))
+                dsts.append(outs[c])
                 off += n
+            K.strided_copy_parts(srcs, dsts)  # every part in one launch (eight parts per launch)
 
-        return KernelTasklet(node.label, run, kernels=("strided_copy", ) * len(conns))
+        return KernelTasklet(node.label, run, kernels=("strided_copy", ) * ((len(conns) + 7) // 8))
 
 
 def _concat_plan(node, state, sdfg):
@@ -177,13 +179,15 @@ class B200Concat(ONNXForward):
         axis, conns = _concat_plan(node, state, sdfg)
 
         def run(ins, outs):
-            off = 0
+            off, srcs, dsts = 0, [], []
             for c in conns:
                 n = ins[c].shape[axis]
-                K.strided_copy(ins[c], outs["concat_result"].narrow(axis, off, n))
+                srcs.append(ins[c])
+                dsts.append(outs["concat_result"].narrow(axis, off, n))
                 off += n
+            K.strided_copy_parts(srcs, dsts)  # every part in one launch (eight parts per launch)
 
-        return KernelTasklet(node.label, run, kernels=("strided_copy", ) * len(conns))
+        return KernelTasklet(node.label, run, kernels=("strided_copy", ) * ((len(conns) + 7) // 8))
 
 
 # ---------------------------------------------------------------------------------------------

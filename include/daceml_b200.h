@@ -258,6 +258,13 @@ int b200ml_strided_copy(b200ml_ctx* ctx, int32_t elem_bytes, const void* x, void
                         const int64_t* shape, const int64_t* x_strides, const int64_t* y_strides,
                         b200ml_stream stream);
 
+/* The same for up to eight copies of one element size in a single launch: part p copies shapes[p * rank ...] from xs[p]
+ * to ys[p] with its own strides.  This is Split (pure_implementations.py:781-827: one sub-range copy per output) and
+ * Concat as one kernel instead of one per part; parts that cannot move the same unit fall back to one launch each. */
+int b200ml_strided_copy_parts(b200ml_ctx* ctx, int32_t elem_bytes, int32_t nparts, const void* const* xs,
+                              void* const* ys, int32_t rank, const int64_t* shapes, const int64_t* x_strides,
+                              const int64_t* y_strides, b200ml_stream stream);
+
 /* numpy.take along one axis: data is [outer, axis_dim, inner], y is [outer, n_indices, inner],
  * y[o, j, :] = data[o, indices[j], :]; negative indices count from the end.  An index outside [-axis_dim, axis_dim)
  * writes zeros and sets the context's device status.  Replaces Gather (pure_implementations.py:949-1014). */

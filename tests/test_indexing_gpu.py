@@ -322,3 +322,43 @@ def test_tiny_bert_with_mask_through_dace_module(rng):
     assert_close(hidden, ref_hidden, dtype=torch.float16, what="hidden states")
     assert_close(pooled, ref_pooled, dtype=torch.float16, what="pooled output")
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.int64, torch.bool])
+def test_strided_copy_parts_is_one_launch_per_eight_parts(dtype, rng):
+    """Split and Concat through the multi-part copy: all parts in one launch when they move the same unit, parts of
+    odd widths (different units) and more than eight parts included; bit-exact against torch slicing."""
+    def make(*shape):
+        if dtype == torch.bool:
+            return torch.from_numpy(rng.random(shape) > 0.5).cuda()
+        if dtype == torch.int64:
+            return torch.from_numpy(rng.integers(-1000, 1000, shape)).cuda()
+        return torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dtype).cuda()
+
+    x = make(37, 3 * 64)
+    parts = [torch.empty(37, 64, dtype=dtype, device="cuda") for _ in range(3)]
+    before = L.launch_count()
+    K.strided_copy_parts([x.narrow(1, 64 * j, 64) for j in range(3)], parts)
+    assert L.launch_count() - before == 1
+    for j in range(3):
+        assert torch.equal(parts[j], x[:, 64 * j:64 * (j + 1)])
+    # Concat of ragged widths (7, 64, 9 columns: not all 16-byte units) into one row-major output
+    widths = [7, 64, 9]
+    srcs = [make(11, w) for w in widths]
+    out = torch.zeros(11, sum(widths), dtype=dtype, device="cuda")
+    off, dsts = 0, []
+    for w in widths:
+        dsts.append(out.narrow(1, off, w))
+        off += w
+    K.strided_copy_parts(srcs, dsts)
+    assert torch.equal(out, torch.cat(srcs, dim=1))
+    # eleven parts along axis 0: two launches
+    big = make(11 * 5, 24)
+    outs = [torch.empty(5, 24, dtype=dtype, device="cuda") for _ in range(11)]
+    before = L.launch_count()
+    K.strided_copy_parts([big.narrow(0, 5 * j, 5) for j in range(11)], outs)
+    assert L.launch_count() - before == 2
+    for j in range(11):
+        assert torch.equal(outs[j], big[5 * j:5 * j + 5])
+    torch.cuda.synchronize()
+    assert L.get_context(0).device_status() == 0
