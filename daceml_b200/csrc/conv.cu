@@ -15,6 +15,8 @@ int reduce(const b200ml_ctx* ctx, int dtype, int op, const void* x, void* y, int
            cudaStream_t s);
 bool conv1x1_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p);
 int conv1x1_tensor_core(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t stream);
+bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow);
+int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow, cudaStream_t stream);
 
 namespace {
 
@@ -550,6 +552,10 @@ static int conv2d_fast(const b200ml_ctx* ctx, const b200ml_conv_params* p, const
     if (conv1x1_tensor_core_applies(ctx, p)) {  // 1x1, stride 1: the tensor-core kernel (3 x TF32), HBM-bound
         *launched = true;
         return conv1x1_tensor_core(ctx, p, s);
+    }
+    if (conv_igemm_applies(ctx, p, g.oh, g.ow)) {  // k x k, stride 1, group 1: implicit GEMM on the tensor core (3 x TF32)
+        *launched = true;
+        return conv_igemm(ctx, p, g.oh, g.ow, s);
     }
     const bool unit = p->stride_h == 1 && p->stride_w == 1 && p->dil_h == 1 && p->dil_w == 1;
     const bool nopad = !p->pad_top && !p->pad_left && !p->pad_bottom && !p->pad_right;

@@ -1,0 +1,535 @@
+// k x k stride-1 convolution (NCHW, fp32, group 1) as an implicit GEMM on the tensor cores, fp32-grade accuracy
+// ("3 x TF32"):
+//     Y[n, m, h, w] = act(B[m] + sum_{c, i, j} W[m, c, i, j] * X[n, c, h - pad_top + i, w - pad_left + j]) + R[n, m, h, w]
+// (the reference's routes: the loop nest of daceml/onnx/op_implementations/img_op_implementations.py:217-288 and cuDNN,
+// cudnn_implementations.py:123-410).
+//
+// No im2col buffer exists anywhere.  A tile is 8 output rows x 32 output columns of one image (two accumulators of 128
+// pixels: one TMEM lane per pixel) times a block of up to 128 output channels (TMEM columns).  The reduction runs over
+// (8 input channels) x (kernel column j) "stages", each of which serves the kh kernel rows:
+//   * TMA brings the raw input window of 8 channels (8 + kh - 1 rows, 32 + halo columns; the tensor map fills the
+//     padding and the channels past C with zeros) into shared memory once per 8 channels;
+//   * eight split warps (one channel each) write, for kernel column j, the window shifted by j as an MN-major tf32
+//     operand - hi part and lo part - in the 128-byte swizzle with 32-byte atoms: one 512-byte atom per (image row,
+//     group of 4 channels), 32 pixels per 128-byte line.  A shift by j is not a multiple of 16 bytes, which is why it is
+//     made here and not by the tensor map;
+//   * kernel row i needs no copy: its operand is the same shifted window starting i atoms (image rows) further down,
+//     so the three or five products of a stage differ only in their descriptors' start addresses;
+//   * the weights of the stage (8 channels x kh rows x the channel block, hi and lo, split once per call by a small
+//     kernel into an [.., c, j, i, m] order) arrive by TMA as the N-major operand in the same swizzle.
+// The tensor core accumulates X_lo.W_hi + X_hi.W_lo + X_hi.W_hi per kernel row and half tile.  Bias, activation and
+// residual are applied by sixteen epilogue warps (a lane = a pixel of one output row), which stage [8 channels][32 pixels]
+// boxes in shared memory and send them with bulk tensor stores; those clip the columns past the image and the channels
+// past M.  Roles as in the 1x1 kernel: warp 0 TMA, warp 1 MMA and TMEM owner, warps 2-9 split, warps 10-25 epilogue;
+// one persistent CTA per SM; two accumulator sets, so a tile's epilogue runs under the next tile's products.
+#include "conv_tc.cuh"
+
+namespace b200ml {
+
+using namespace convtc;
+
+namespace {
+
+constexpr int IG_KC = 8;                       // input channels per stage = one tf32 MMA step
+constexpr int IG_ROWS = 8, IG_COLS = 32;       // output tile: two halves of 4 rows x 32 columns = 2 x 128 pixels
+constexpr int IG_RAW_SLOTS = 2;
+constexpr int IG_MAX_STAGES = 6;
+constexpr int IG_SPLIT_WARPS = IG_KC, IG_EPI_WARPS = 16;
+constexpr int IG_FIRST_EPI = 2 + IG_SPLIT_WARPS;
+constexpr int IG_THREADS = 32 * (2 + IG_SPLIT_WARPS + IG_EPI_WARPS);
+constexpr int IG_OUT_BYTES = 2 * 8 * 32 * 4;   // per epilogue warp: two [8 channels][32 pixels] boxes
+constexpr int IG_BAR_BYTES = 256;
+constexpr int IG_SMEM_LIMIT = 227 * 1024;
+
+struct IgArgs {
+    int32_t c, m, oh, ow, kh, kw;
+    int32_t cblocks, nb, nblocks, hblocks, wblocks, num_tiles;
+    int32_t rb, wb, xoff;                 // raw window: rows, columns, column of kernel column 0 for output column 0
+    int32_t pla, pad_top;                 // the window starts pla columns left of the tile and pad_top rows above it
+    int32_t stages, raw_bytes, stage_bytes, shift_bytes;
+    int32_t act;
+    const float* bias;      // [M] or null
+    const float* residual;  // like Y or null
+    int32_t* status;
+};
+
+// W [m, c, kh, kw] -> out [2][row][ntot], row = ((c / 8 * kw + j) * kh + i) * 8 + c % 8: hi and lo parts, zero-padded to
+// whole 8-channel blocks and to ntot output channels.  Rounded to nearest here (|lo| <= 2^-11 |w|).
+__global__ void __launch_bounds__(256) ig_split_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int m,
+                                                               int c, int kh, int kw, int ntot, int rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = static_cast<int64_t>(rows) * ntot;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / ntot), n = static_cast<int>(i - static_cast<int64_t>(row) * ntot);
+        const int ch = row & 7, t = row >> 3;
+        const int ki = t % kh, kj = (t / kh) % kw, cb = t / (kh * kw);
+        const int cc = cb * 8 + ch;
+        float v = 0.0f;
+        if (n < m && cc < c) v = __ldg(w + ((static_cast<int64_t>(n) * c + cc) * kh + ki) * kw + kj);
+        const uint32_t b = __float_as_uint(v);
+        const bool finite = (b & 0x7f800000u) != 0x7f800000u;
+        const float hi = __uint_as_float(finite ? ((b + 0xfffu + ((b >> 13) & 1u)) & 0xffffe000u) : b);
+        out[i] = hi;
+        out[total + i] = finite ? v - hi : 0.0f;
+    }
+}
+
+struct IgTile {
+    int n, nblk, h0, w0;
+};
+__device__ __forceinline__ IgTile ig_tile(const IgArgs& a, int tile) {
+    IgTile t;
+    const int wblk = tile % a.wblocks;
+    tile /= a.wblocks;
+    const int hblk = tile % a.hblocks;
+    tile /= a.hblocks;
+    t.nblk = tile % a.nblocks;
+    t.n = tile / a.nblocks;
+    t.h0 = hblk * IG_ROWS;
+    t.w0 = wblk * IG_COLS;
+    return t;
+}
+
+__global__ void __launch_bounds__(IG_THREADS, 1)
+conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                         const __grid_constant__ CUtensorMap tmap_y, const IgArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // [stages][shifted X hi, lo | W hi, lo]  [raw slots]  [epilogue staging]  [barriers]
+    uint8_t* raw_base = smem + args.stages * args.stage_bytes;
+    uint8_t* out_stage = raw_base + IG_RAW_SLOTS * args.raw_bytes;
+    uint64_t* ready = reinterpret_cast<uint64_t*>(out_stage + IG_EPI_WARPS * IG_OUT_BYTES);  // W bytes + the split warps
+    uint64_t* empty = ready + IG_MAX_STAGES;
+    uint64_t* raw_full = empty + IG_MAX_STAGES;
+    uint64_t* raw_empty = raw_full + IG_RAW_SLOTS;
+    uint64_t* tmem_full = raw_empty + IG_RAW_SLOTS;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < 4u * args.nb) tmem_cols <<= 1;
+    const uint32_t acc_stride = tmem_cols / 2, half_stride = tmem_cols / 4;  // [accumulator set][half tile][channel]
+    const int natoms = args.nb / 32;                                          // 32-channel atoms of the weight operand
+    const int w_part_bytes = natoms * args.kh * 1024;                         // W_hi (or W_lo) of a stage
+    const int x_part_bytes = args.rb * 1024;                                  // X_hi (or X_lo) of a stage
+
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_x);
+        ptx::prefetch_tensormap(&tmap_w);
+        ptx::prefetch_tensormap(&tmap_y);
+    }
+    if (warp == 1) {
+        if (lane == 0) {
+            for (int s = 0; s < args.stages; ++s) {
+                ptx::mbar_init(&ready[s], 1 + IG_SPLIT_WARPS);
+                ptx::mbar_init(&empty[s], 1);
+            }
+            for (int r = 0; r < IG_RAW_SLOTS; ++r) {
+                ptx::mbar_init(&raw_full[r], 1);
+                ptx::mbar_init(&raw_empty[r], IG_SPLIT_WARPS);
+            }
+            for (int a = 0; a < 2; ++a) {
+                ptx::mbar_init(&tmem_full[a], 1);
+                ptx::mbar_init(&tmem_empty[a], IG_EPI_WARPS);
+            }
+            ptx::fence_mbar_init();
+        }
+        __syncwarp();
+        ptx::tmem_alloc(tmem_slot, tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();  // the split weights (and possibly X, the residual) come from kernels before this one in the stream
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer: raw windows and weight chunks ------------------------------
+        if (ptx::elect_one()) {
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, slot_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
+                const IgTile t = ig_tile(args, tile);
+                for (int cb = 0; ok && cb < args.cblocks; ++cb) {
+                    if (!ptx::mbar_wait_suspend(&raw_empty[slot], slot_phase ^ 1)) {
+                        atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_expect_tx(&raw_full[slot], static_cast<uint32_t>(args.wb * args.rb * IG_KC * 4));
+                    // x is a multiple of 4 elements (16 bytes); rows and columns outside the image arrive as zeros
+                    ptx::tma_load_4d(raw_base + slot * args.raw_bytes, &tmap_x, &raw_full[slot], t.w0 - args.pla,
+                                     t.h0 - args.pad_top, cb * IG_KC, t.n);
+                    if (++slot == IG_RAW_SLOTS) {
+                        slot = 0;
+                        slot_phase ^= 1;
+                    }
+                    for (int kj = 0; kj < args.kw; ++kj) {
+                        if (!ptx::mbar_wait_suspend(&empty[stage], phase ^ 1)) {
+                            atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* wst = smem + stage * args.stage_bytes + args.shift_bytes;
+                        ptx::mbar_expect_tx(&ready[stage], static_cast<uint32_t>(2 * w_part_bytes));
+                        const int row0 = (cb * args.kw + kj) * args.kh * IG_KC;
+                        for (int part = 0; part < 2; ++part)
+                            for (int a = 0; a < natoms; ++a)
+                                ptx::tma_load_4d(wst + part * w_part_bytes + a * args.kh * 1024, &tmap_w, &ready[stage],
+                                                 t.nblk * args.nb + a * 32, row0, part, 0);
+                        if (++stage == args.stages) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (ptx::elect_one()) {
+            const uint32_t idesc = pw_idesc(static_cast<uint32_t>(args.nb), 1u);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                if (!ptx::mbar_wait_suspend(&tmem_empty[acc], ((it >> 1) & 1) ^ 1)) {
+                    atomicExch(args.status, DEV_TIMEOUT_MMA);
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * acc_stride;
+                const int nstages = args.cblocks * args.kw;
+                for (int st = 0; st < nstages; ++st) {
+                    if (!ptx::mbar_wait(&ready[stage], phase)) {
+                        atomicExch(args.status, DEV_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t xh = ptx::smem_u32(smem + stage * args.stage_bytes), xl = xh + x_part_bytes;
+                    const uint32_t wh = xh + args.shift_bytes, wl = wh + w_part_bytes;
+                    for (int ki = 0; ki < args.kh; ++ki) {
+                        // W: N-major, 32-channel atoms kh KB apart, 4-channel (K) groups 512 bytes apart
+                        const uint64_t d_wh = make_smem_desc_sw128_base32(wh + ki * 1024, args.kh * 1024, 512);
+                        const uint64_t d_wl = make_smem_desc_sw128_base32(wl + ki * 1024, args.kh * 1024, 512);
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            // X: MN-major, one atom per image row (1 KB apart: two 4-channel groups of 512 bytes); kernel
+                            // row ki of half hf starts at window row 4 hf + ki
+                            const uint64_t d_xh = make_smem_desc_sw128_base32(xh + (4 * hf + ki) * 1024, 1024, 512);
+                            const uint64_t d_xl = make_smem_desc_sw128_base32(xl + (4 * hf + ki) * 1024, 1024, 512);
+                            const uint32_t d = d_tmem + hf * half_stride;
+                            pw_mma(d, d_xl, d_wh, idesc, (st | ki) != 0 ? 1u : 0u);  // the two small terms first
+                            pw_mma(d, d_xh, d_wl, idesc, 1u);
+                            pw_mma(d, d_xh, d_wh, idesc, 1u);
+                        }
+                    }
+                    ptx::mma_commit(&empty[stage]);
+                    if (++stage == args.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                ptx::mma_commit(&tmem_full[acc]);
+            }
+        }
+    } else if (warp < IG_FIRST_EPI) {
+        // ------------------------------ split: raw window -> shifted hi / lo operands ------------------------------
+        // Warp = one of the 8 channels of the stage, lane = output column.  For kernel column kj the value under output
+        // column `lane` of window row r is raw[ch][r][xoff + kj + lane]; it goes to line (ch & 3) of atom (r, ch >> 2) of
+        // the stage, 32-byte chunk (lane / 8) ^ (ch & 3): a warp reads and writes whole 128-byte lines, conflict-free.
+        const int ch = warp - 2, cr = ch & 3;
+        const uint32_t dst_lane = (ch >> 2) * 512 + cr * 128 + ((lane * 4) ^ (cr << 5));
+        int stage = 0, slot = 0;
+        uint32_t phase = 0, slot_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
+            for (int cb = 0; ok && cb < args.cblocks; ++cb) {
+                ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&raw_full[slot], slot_phase));
+                if (!ok) {
+                    if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                    break;
+                }
+                const uint32_t src0 = ptx::smem_u32(raw_base + slot * args.raw_bytes) + (ch * args.rb * args.wb + args.xoff + lane) * 4;
+                for (int kj = 0; kj < args.kw; ++kj) {
+                    ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&empty[stage], phase ^ 1));
+                    if (!ok) {
+                        if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                        break;
+                    }
+                    const uint32_t hi = ptx::smem_u32(smem + stage * args.stage_bytes) + dst_lane, lo = hi + x_part_bytes;
+                    const uint32_t src = src0 + kj * 4;
+#pragma unroll 1
+                    for (int r0 = 0; r0 < args.rb; r0 += 4) {
+                        float v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) v[u] = r0 + u < args.rb ? ld_shared_f32(src + (r0 + u) * args.wb * 4) : 0.0f;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (r0 + u < args.rb) {
+                                float h, l;
+                                split_tf32(v[u], h, l);
+                                st_shared_f32(hi + (r0 + u) * 1024, h);
+                                st_shared_f32(lo + (r0 + u) * 1024, l);
+                            }
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();  // the tensor core reads shared memory through the async proxy
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&ready[stage]);
+                    if (++stage == args.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&raw_empty[slot]);  // this warp has read its channel of the window
+                if (++slot == IG_RAW_SLOTS) {
+                    slot = 0;
+                    slot_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue: one output row x every fourth 8-channel unit per warp ------------------------------
+        const int quarter = warp & 3;                      // TMEM lanes [32 q, 32 q + 32): a warp may only touch its own quarter
+        const int group = (warp - IG_FIRST_EPI) >> 2;      // units group, group + 4, ...
+        constexpr int NGROUPS = IG_EPI_WARPS / 4;
+        uint8_t* stg = out_stage + (warp - IG_FIRST_EPI) * IG_OUT_BYTES;
+        const uint32_t stg_lane = ptx::smem_u32(stg) + lane * 4;
+        const int64_t plane = static_cast<int64_t>(args.oh) * args.ow;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x, ++it) {
+            const int acc = it & 1;
+            const IgTile t = ig_tile(args, tile);
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_suspend(&tmem_full[acc], (it >> 1) & 1))) {
+                if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                break;
+            }
+            ptx::tc_fence_after();
+            const int m0 = t.nblk * args.nb;                                   // first output channel of the block
+            const int nunits = ((args.m - m0 < args.nb ? args.m - m0 : args.nb) + 7) / 8;
+            const bool p_ok = t.w0 + lane < args.ow;
+#pragma unroll 1
+            for (int hf = 0; hf < 2; ++hf) {
+                const int row = t.h0 + 4 * hf + quarter;
+                if (row >= args.oh) continue;  // warp-uniform: rows past the image have nothing to store
+                const uint32_t t_base = tmem_base + acc * acc_stride + hf * half_stride + (static_cast<uint32_t>(quarter * 32) << 16);
+                const float* res = args.residual
+                                       ? args.residual + (static_cast<int64_t>(t.n) * args.m + m0) * plane + static_cast<int64_t>(row) * args.ow + t.w0 + lane
+                                       : nullptr;
+#pragma unroll 1
+                for (int ua = group; ua < nunits; ua += 2 * NGROUPS) {
+                    const int ub = ua + NGROUPS;
+                    const bool two = ub < nunits;  // warp-uniform
+                    const int ca = ua * 8, cb = two ? ub * 8 : ca;
+                    uint32_t r[2][8];
+                    float rv[2][8], bv[2][8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        bv[0][j] = (args.bias && m0 + ca + j < args.m) ? __ldg(args.bias + m0 + ca + j) : 0.0f;
+                        bv[1][j] = (args.bias && m0 + cb + j < args.m) ? __ldg(args.bias + m0 + cb + j) : 0.0f;
+                    }
+                    if (res) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            rv[0][j] = (p_ok && m0 + ca + j < args.m) ? __ldg(res + static_cast<int64_t>(ca + j) * plane) : 0.0f;
+                            rv[1][j] = (p_ok && m0 + cb + j < args.m) ? __ldg(res + static_cast<int64_t>(cb + j) * plane) : 0.0f;
+                        }
+                    }
+                    ptx::tmem_ld_32x32b_x8(t_base + ca, r[0]);
+                    ptx::tmem_ld_32x32b_x8(t_base + cb, r[1]);
+                    if (lane == 0) ptx::tma_store_wait_read<0>();  // the stores of the last turn have read the staging boxes
+                    ptx::tmem_ld_wait();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        r[0][j] = __float_as_uint(__uint_as_float(r[0][j]) + bv[0][j]);
+                        r[1][j] = __float_as_uint(__uint_as_float(r[1][j]) + bv[1][j]);
+                    }
+                    if (res) {
+                        if (args.act == B200ML_EPI_SWISH) pw_finish_turn<B200ML_EPI_SWISH, true>(r, rv, stg_lane);
+                        else if (args.act == 0) pw_finish_turn<0, true>(r, rv, stg_lane);
+                        else if (args.act == B200ML_EPI_RELU) pw_finish_turn<B200ML_EPI_RELU, true>(r, rv, stg_lane);
+                        else pw_finish_turn<B200ML_EPI_GELU, true>(r, rv, stg_lane);
+                    } else {
+                        if (args.act == B200ML_EPI_SWISH) pw_finish_turn<B200ML_EPI_SWISH, false>(r, rv, stg_lane);
+                        else if (args.act == 0) pw_finish_turn<0, false>(r, rv, stg_lane);
+                        else if (args.act == B200ML_EPI_RELU) pw_finish_turn<B200ML_EPI_RELU, false>(r, rv, stg_lane);
+                        else pw_finish_turn<B200ML_EPI_GELU, false>(r, rv, stg_lane);
+                    }
+                    ptx::fence_proxy_async_smem();  // the bulk stores read shared memory through the async proxy
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_4d(&tmap_y, stg, t.w0, row, m0 + ca, t.n);  // columns past OW and channels past M are clipped
+                        if (two) ptx::tma_store_4d(&tmap_y, stg + 1024, t.w0, row, m0 + cb, t.n);
+                        ptx::tma_store_commit();
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+        }
+        if (lane == 0) ptx::tma_store_wait<0>();  // the bulk stores have landed before the CTA may leave
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        if (*reinterpret_cast<volatile int32_t*>(args.status) != DEV_OK) {
+            for (int i = 0; i < 200; ++i) __nanosleep(1000);  // a wait gave up: let copies in flight land before the CTA leaves
+        }
+        ptx::tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// The shape of the launch: channel block, window, stages, shared memory.  `ok` is false when nothing fits.
+struct IgPlan {
+    bool ok;
+    int nb, nblocks, ntot, cblocks, rows, rb, wb, pla, stages, raw_bytes, shift_bytes, stage_bytes, smem;
+};
+
+IgPlan ig_plan(const b200ml_conv_params* p) {
+    IgPlan pl{};
+    const int kh = (int)p->kh, kw = (int)p->kw;
+    pl.cblocks = (int)ceil_div(p->c, IG_KC);
+    pl.rows = pl.cblocks * kw * kh * IG_KC;
+    pl.rb = IG_ROWS + kh - 1;
+    pl.pla = (int)ceil_div(p->pad_left, 4) * 4;
+    pl.wb = (int)ceil_div(pl.pla - p->pad_left + kw + IG_COLS - 1, 4) * 4;
+    pl.raw_bytes = (int)ceil_div((int64_t)pl.wb * pl.rb * IG_KC * 4, 1024) * 1024;
+    pl.shift_bytes = 2 * pl.rb * 1024;
+    const int fixed = IG_RAW_SLOTS * pl.raw_bytes + IG_EPI_WARPS * IG_OUT_BYTES + IG_BAR_BYTES + 1024 /* alignment */;
+    // the widest channel block that leaves three stages (two if there is no other way)
+    for (int want = 3; want >= 2 && !pl.ok; --want) {
+        for (int nb = 128; nb >= 32 && !pl.ok; nb /= 2) {
+            const int use = p->m <= nb ? (int)ceil_div(p->m, 32) * 32 : nb;
+            const int stage = pl.shift_bytes + 2 * (use / 32) * kh * 1024;
+            const int stages = (IG_SMEM_LIMIT - fixed) / stage;
+            if (stages >= want) {
+                pl.ok = true;
+                pl.nb = use;
+                pl.stage_bytes = stage;
+                pl.stages = stages < IG_MAX_STAGES ? stages : IG_MAX_STAGES;
+            }
+        }
+    }
+    if (!pl.ok) return pl;
+    pl.nblocks = (int)ceil_div(p->m, pl.nb);
+    pl.ntot = pl.nblocks * pl.nb;
+    pl.smem = pl.stages * pl.stage_bytes + fixed;
+    return pl;
+}
+
+bool conv_tc_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200ML_CONV_TC");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+}  // namespace
+
+// Whether the implicit-GEMM kernel covers this convolution (the caller uses the direct FP32-FMA kernel otherwise).
+bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow) {
+    if (!conv_tc_enabled() || p->dtype != B200ML_F32 || !ctx->encode_tiled) return false;
+    if (p->group != 1 || p->gate) return false;
+    if (p->kh * p->kw < 2 || p->kh > 7 || p->kw > 7) return false;
+    if (p->stride_h != 1 || p->stride_w != 1 || p->dil_h != 1 || p->dil_w != 1) return false;
+    if (p->pad_top > 8 || p->pad_left > 8 || p->pad_bottom > 8 || p->pad_right > 8) return false;
+    if (p->c * p->kh * p->kw < 64 || p->m < 16) return false;                 // short reductions stay on the FP32 pipe
+    if (p->w % 4 != 0 || ow % 4 != 0 || !aligned16(p->x) || !aligned16(p->y)) return false;  // 16-byte strides and bases for the tensor maps
+    if (p->n * oh * ow < 4 * 1024) return false;                              // too little work for two launches
+    const IgPlan pl = ig_plan(p);
+    if (!pl.ok) return false;
+    if (2ll * pl.rows * pl.ntot * 4 > ctx->workspace_bytes) return false;     // the split weights live in the context's scratch
+    const int64_t tiles = p->n * pl.nblocks * ceil_div(oh, IG_ROWS) * ceil_div(ow, IG_COLS);
+    if (tiles >= (1ll << 31) || p->h >= (1 << 24) || p->w >= (1 << 24) || p->c >= (1 << 24) || p->m >= (1 << 24) || p->n >= (1 << 24)) return false;
+    if (p->n * p->c * p->h * p->w * 4 >= (1ll << 40) || p->n * p->m * oh * ow * 4 >= (1ll << 40)) return false;  // tensor-map strides are below 2^40 bytes
+    return true;
+}
+
+int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow, cudaStream_t stream) {
+    const IgPlan pl = ig_plan(p);
+    float* wsplit = static_cast<float*>(ctx->workspace);
+    {
+        const int64_t total = (int64_t)pl.rows * pl.ntot;
+        const unsigned grid = (unsigned)(ceil_div(total, 256) < 1184 ? ceil_div(total, 256) : 1184);
+        B200ML_CUDA(launch_pdl(ig_split_weights_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const float*>(p->weight),
+                               wsplit, (int)p->m, (int)p->c, (int)p->kh, (int)p->kw, pl.ntot, pl.rows));
+        int rc = check_launch("ig_split_weights");
+        if (rc) return rc;
+    }
+    CUtensorMap tx, tw, ty;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->c, (cuuint64_t)p->n};
+        const cuuint64_t strides[3] = {(cuuint64_t)p->w * 4, (cuuint64_t)p->w * p->h * 4, (cuuint64_t)p->w * p->h * p->c * 4};
+        const cuuint32_t box[4] = {(cuuint32_t)pl.wb, (cuuint32_t)pl.rb, IG_KC, 1};
+        CUresult r = encode_tiled_cached(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "conv k x k: cuTensorMapEncodeTiled(X) failed with CUresult %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)pl.ntot, (cuuint64_t)pl.rows, 2, 1};
+        const cuuint64_t strides[3] = {(cuuint64_t)pl.ntot * 4, (cuuint64_t)pl.ntot * 4 * pl.rows, (cuuint64_t)pl.ntot * 4 * pl.rows * 2};
+        const cuuint32_t box[4] = {32, (cuuint32_t)(p->kh * IG_KC), 1, 1};
+        CUresult r = encode_tiled_cached(ctx, &tw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, wsplit, dims, strides, box,
+                                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+        if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "conv k x k: cuTensorMapEncodeTiled(W) failed with CUresult %d", (int)r);
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)ow, (cuuint64_t)oh, (cuuint64_t)p->m, (cuuint64_t)p->n};
+        const cuuint64_t strides[3] = {(cuuint64_t)ow * 4, (cuuint64_t)ow * oh * 4, (cuuint64_t)ow * oh * p->m * 4};
+        const cuuint32_t box[4] = {32, 1, 8, 1};
+        CUresult r = encode_tiled_cached(ctx, &ty, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->y, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "conv k x k: cuTensorMapEncodeTiled(Y) failed with CUresult %d", (int)r);
+    }
+    IgArgs a{};
+    a.c = (int32_t)p->c;
+    a.m = (int32_t)p->m;
+    a.oh = (int32_t)oh;
+    a.ow = (int32_t)ow;
+    a.kh = (int32_t)p->kh;
+    a.kw = (int32_t)p->kw;
+    a.cblocks = pl.cblocks;
+    a.nb = pl.nb;
+    a.nblocks = pl.nblocks;
+    a.hblocks = (int32_t)ceil_div(oh, IG_ROWS);
+    a.wblocks = (int32_t)ceil_div(ow, IG_COLS);
+    a.num_tiles = (int32_t)(p->n * pl.nblocks * a.hblocks * a.wblocks);
+    a.rb = pl.rb;
+    a.wb = pl.wb;
+    a.pla = pl.pla;
+    a.xoff = pl.pla - (int32_t)p->pad_left;
+    a.pad_top = (int32_t)p->pad_top;
+    a.stages = pl.stages;
+    a.raw_bytes = pl.raw_bytes;
+    a.stage_bytes = pl.stage_bytes;
+    a.shift_bytes = pl.shift_bytes;
+    a.act = p->act & (B200ML_EPI_RELU | B200ML_EPI_SWISH | B200ML_EPI_GELU);
+    a.bias = static_cast<const float*>(p->bias);
+    a.residual = static_cast<const float*>(p->residual);
+    a.status = ctx->status_dev;
+    static int configured[64] = {};
+    if (configured[ctx->device & 63] < pl.smem) {
+        B200ML_CUDA(cudaFuncSetAttribute(conv_igemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem));
+        configured[ctx->device & 63] = pl.smem;
+    }
+    const int grid = a.num_tiles < ctx->sm_count ? a.num_tiles : ctx->sm_count;
+    B200ML_CUDA(launch_pdl(conv_igemm_tf32x3_kernel, dim3(grid), dim3(IG_THREADS), (size_t)pl.smem, stream, tx, tw, ty, a));
+    return check_launch("conv_igemm_tf32x3");
+}
+
+}  // namespace b200ml

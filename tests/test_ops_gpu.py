@@ -481,6 +481,46 @@ def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
     status_ok()
 
 
+@pytest.mark.parametrize("n, cin, cout, hw, k, pads", [(8, 16, 32, (48, 48), (3, 3), (1, 1, 1, 1)), (4, 64, 64, (56, 56), (3, 3), (1, 1, 1, 1)),
+                                                       (6, 10, 40, (36, 40), (5, 5), (2, 2, 2, 2)), (4, 24, 200, (30, 44), (3, 3), (0, 1, 0, 1)),
+                                                       (3, 32, 16, (80, 96), (3, 5), (1, 2, 1, 2)), (5, 12, 48, (40, 64), (3, 3), (2, 0, 0, 2)),
+                                                       (2, 8, 32, (64, 64), (7, 7), (3, 3, 3, 3)), (64, 128, 128, (16, 16), (3, 3), (1, 1, 1, 1))])
+@pytest.mark.parametrize("act", ["", "Relu"])
+def test_conv_kxk_tensor_core(n, cin, cout, hw, k, pads, act, rng):
+    """k x k stride-1 convolutions large enough for the implicit-GEMM kernel (3 x TF32; kernel columns as shifted copies
+    of the input window, kernel rows as descriptor offsets): ragged tiles in both directions, channel counts that are
+    not whole 8- or 32-blocks, more than one block of output channels, asymmetric padding, non-square kernels, bias,
+    activation and residual.  Against the oracle at the fp32 tolerance, and against a float64 convolution at a bound
+    that a single-TF32 product (relative error 5e-4) would break."""
+    if os.environ.get("B200ML_CONV_TC", "1") == "0":
+        pytest.skip("the tensor-core convolution is switched off")
+    x = rng.standard_normal((n, cin) + hw).astype(np.float32)
+    w = (rng.standard_normal((cout, cin) + k) * 0.1).astype(np.float32)
+    b = (rng.standard_normal(cout) * 3).astype(np.float32)
+    oracle = ops.conv2d(x, w, b, pads=pads)
+    res = rng.standard_normal(oracle.shape).astype(np.float32)
+    guard = torch.full((oracle.size + 4096, ), 7.0, dtype=torch.float32, device="cuda")
+    y = guard[:oracle.size].view(oracle.shape)
+    before = L.launch_count()
+    donnx.ONNXFusedConv(X=dev(x), W=dev(w), B=dev(b), Residual=dev(res), Y=y, pads=list(pads), activation=act)
+    assert L.launch_count() - before == 2, "expected the weight split and the implicit-GEMM kernel"
+    pt, pl, pb, pr = pads
+    xp = torch.nn.functional.pad(torch.from_numpy(x).double(), (pl, pr, pt, pb))
+    pre = torch.nn.functional.conv2d(xp, torch.from_numpy(w).double(), torch.from_numpy(b).double()).numpy()
+    mag = torch.nn.functional.conv2d(xp.abs(), torch.from_numpy(w).double().abs(), torch.from_numpy(b).double().abs()).numpy() + np.abs(res)
+    post = {"": pre, "Relu": np.maximum(pre, 0)}[act] + res
+    err = np.abs(y.double().cpu().numpy() - post)
+    assert (err <= 4e-6 * mag + 1e-6).all(), "3 x TF32 accuracy lost: worst error / magnitude %.3g" % float((err / (mag + 1e-9)).max())
+    # the oracle adds its cin * kh * kw terms one after the other in fp32: its own rounding error grows with the terms'
+    # magnitudes, so they enter the bound next to the fp32 tolerance
+    oracle = {"": oracle, "Relu": ops.relu(oracle)}[act] + res
+    err_o = np.abs(y.cpu().numpy().astype(np.float64) - oracle)
+    bad = err_o > 2e-5 + 1e-4 * np.abs(oracle) + 4e-6 * mag
+    assert not bad.any(), f"{k} conv {cin}->{cout} {hw} {pads} {act}: {bad.sum()} of {bad.size} elements away from the oracle, worst {err_o.max():.3g}"
+    assert bool((guard[oracle.size:] == 7.0).all()), "written past the end of Y"
+    status_ok()
+
+
 @pytest.mark.parametrize("c, hw, pads", [(144, (56, 56), (1, 1, 1, 1)), (5, (7, 8), (1, 1, 1, 1)), (3, (13, 12), (1, 1, 1, 1)), (6, (33, 64), (1, 1, 1, 1)),
                                          (4, (1, 16), (1, 1, 1, 1)), (5, (9, 10), (1, 1, 1, 1)), (4, (12, 12), (0, 1, 1, 0)), (2, (70, 72), (1, 1, 1, 1))])
 @pytest.mark.parametrize("act", ["", "Swish"])
