@@ -280,6 +280,10 @@ def run_other_configs(args, emit=True):
         ("config 4: MBConv block fp32 [128,24,56,56], expand 144, SE 6", graphs.mbconv_sdfg(mb_p, (128, 24, 56, 56), fused=True).compile(),
          {"input": torch.randn(128, 24, 56, 56, device=dev)}, "__return", (128, 24, 56, 56),
          2 * 128 * 56 * 56 * (24 * 144 + 9 * 144 + 144 * 24)),
+        # not one of the reference's configurations: a 3x3 convolution with enough channels for the implicit-GEMM kernel
+        ("extra: Conv fp32 X[32,64,56,56] W[64,64,3,3] pad 1", graphs.conv_sdfg((32, 64, 56, 56), (64, 64, 3, 3), pads=(1, 1, 1, 1)).compile(),
+         {"X": torch.randn(32, 64, 56, 56, device=dev), "W": torch.randn(64, 64, 3, 3, device=dev) * 0.05}, "Y", (32, 64, 56, 56),
+         2 * 32 * 64 * 56 * 56 * 64 * 9),
     ]
     reps = max(args.steps // 8, 10)
     rows = []
@@ -330,12 +334,14 @@ def run_other_configs(args, emit=True):
             per_kernel.append({"kernel": "+".join(tasklet.kernels), "us": round(kus, 2), "MB": round(kb / 1e6, 2),
                                "GB/s": round(kb / kus / 1e3, 1)})
         info = None
-        if name.startswith("config 1") or name.startswith("config 4"):
+        if name.startswith("config 1") or name.startswith("config 4") or name.startswith("extra: Conv"):
             # information only: the same arithmetic through torch's library kernels (cuDNN), the reference's GPU route
             # for convolutions (daceml/onnx/op_implementations/cudnn_implementations.py:360-379); not part of any claim
             import torch.nn.functional as Fn
             if name.startswith("config 1"):
                 lib_call = lambda: Fn.conv2d(inputs["X"], inputs["W"], stride=2)
+            elif name.startswith("extra: Conv"):
+                lib_call = lambda: Fn.conv2d(inputs["X"], inputs["W"], padding=1)
             else:
                 P = {k: v.to(dev) for k, v in mb_p.items()}
                 sw = lambda t: t * torch.sigmoid(t)
@@ -356,7 +362,22 @@ def run_other_configs(args, emit=True):
                 l1.record()
                 torch.cuda.synchronize()
             info = {"torch_library_kernels_us": round(l0.elapsed_time(l1) * 1e3 / reps, 2),
-                    "note": "cuDNN / ATen via torch eager, information only"}
+                    "note": "cuDNN / ATen via torch eager, information only; torch.backends.cudnn.allow_tf32 = %s (single TF32 "
+                            "products, relative error 5e-4, when True)" % torch.backends.cudnn.allow_tf32}
+            if name.startswith("extra: Conv"):  # the same with full fp32 products, which is what the 3 x TF32 kernel delivers
+                was = torch.backends.cudnn.allow_tf32
+                torch.backends.cudnn.allow_tf32 = False
+                with torch.no_grad():
+                    for _ in range(3):
+                        lib_call()
+                    torch.cuda.synchronize()
+                    l0.record()
+                    for _ in range(reps):
+                        lib_call()
+                    l1.record()
+                    torch.cuda.synchronize()
+                torch.backends.cudnn.allow_tf32 = was
+                info["torch_library_kernels_fp32_us"] = round(l0.elapsed_time(l1) * 1e3 / reps, 2)
         row = {"workload": name, "info": info, "kernels": comp.kernel_names(), "launches_per_run": len(comp.kernel_names()),
                "per_kernel": per_kernel, "us_per_run": us, "samples_per_s": out_shape[0] / (us * 1e-6), "flops": flops, "tflops": flops / us / 1e6,
                "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / pk["hbm_gbs"],
@@ -520,6 +541,8 @@ def run_profile_kernels(args):
     jobs.append(("depthwise 3x3", lambda: K.conv2d(big, w_dw, big2, bias=b_dw, pads=(1, 1, 1, 1), group=144, act=L.EPI_SWISH, pool_mean=pool)))
     gate, w_proj, b_proj, my = torch.rand(128, 144, 1, 1, generator=g).to(dev), f(24, 144, 1, 1) * 0.05, f(24) * 0.05, e32(128, 24, 56, 56)
     jobs.append(("conv 1x1 project (tensor core)", lambda: K.conv2d(big2, w_proj, my, bias=b_proj, gate=gate, residual=mx)))
+    kx, kwt, kb, ky_ = f(128, 64, 56, 56), f(64, 64, 3, 3) * 0.05, f(64) * 0.05, e32(128, 64, 56, 56)  # 103 MB in, 103 MB out
+    jobs.append(("conv 3x3 implicit GEMM (tensor core)", lambda: K.conv2d(kx, kwt, ky_, bias=kb, pads=(1, 1, 1, 1), act=L.EPI_RELU)))
     for name, fn in jobs:
         for _ in range(2):
             fn()

@@ -34,7 +34,8 @@ constexpr int IG_KC = 8;                       // input channels per stage = one
 constexpr int IG_ROWS = 8, IG_COLS = 32;       // output tile: two halves of 4 rows x 32 columns = 2 x 128 pixels
 constexpr int IG_RAW_SLOTS = 2;
 constexpr int IG_MAX_STAGES = 6;
-constexpr int IG_SPLIT_WARPS = IG_KC, IG_EPI_WARPS = 16;
+constexpr int IG_SPLIT_WARPS = IG_KC, IG_EPI_WARPS = 16;  // one split warp per channel of a stage
+constexpr int IG_MAX_RB = IG_ROWS + 7 - 1;                // window rows of the tallest kernel (7)
 constexpr int IG_FIRST_EPI = 2 + IG_SPLIT_WARPS;
 constexpr int IG_THREADS = 32 * (2 + IG_SPLIT_WARPS + IG_EPI_WARPS);
 constexpr int IG_OUT_BYTES = 2 * 8 * 32 * 4;   // per epilogue warp: two [8 channels][32 pixels] boxes
@@ -48,6 +49,10 @@ struct IgArgs {
     int32_t pla, pad_top;                 // the window starts pla columns left of the tile and pad_top rows above it
     int32_t stages, raw_bytes, stage_bytes, shift_bytes;
     int32_t act;
+    int32_t direct_io, h, w;  // direct_io: X and Y cannot be described to the TMA unit (row pitch or base not a multiple of
+                              // 16 bytes); the split warps fetch the window and the epilogue warps store Y themselves
+    const float* x;
+    float* y;
     const float* bias;      // [M] or null
     const float* residual;  // like Y or null
     int32_t* status;
@@ -91,6 +96,70 @@ __device__ __forceinline__ IgTile ig_tile(const IgArgs& a, int tile) {
     return t;
 }
 
+// Direct mode: a split warp fetches its channel's window of the next channel block into registers (lane = window column,
+// and column + 32), zeros for the padding and for channels past C; the loads fly while the warp works on the current block.
+__device__ __forceinline__ void ig_fetch_window(const IgArgs& a, const IgTile& t, int cb, int ch, int lane, float (&pre)[IG_MAX_RB][2]) {
+    const int c = cb * IG_KC + ch;
+    const float* xc = a.x + (static_cast<int64_t>(t.n) * a.c + (c < a.c ? c : 0)) * a.h * a.w;
+    const int gy0 = t.h0 - a.pad_top, gx0 = t.w0 - a.pla + lane;
+#pragma unroll
+    for (int r = 0; r < IG_MAX_RB; ++r) {
+        const int gy = gy0 + r;
+        const bool r_ok = c < a.c && r < a.rb && gy >= 0 && gy < a.h;
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+            const int gx = gx0 + 32 * hc;
+            pre[r][hc] = (r_ok && lane + 32 * hc < a.wb && gx >= 0 && gx < a.w) ? __ldg(xc + static_cast<int64_t>(gy) * a.w + gx) : 0.0f;
+        }
+    }
+}
+__device__ __forceinline__ void ig_store_window(uint32_t dst, const IgArgs& a, int lane, const float (&pre)[IG_MAX_RB][2]) {
+#pragma unroll
+    for (int r = 0; r < IG_MAX_RB; ++r) {
+        if (r < a.rb) {
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc)
+                if (lane + 32 * hc < a.wb) st_shared_f32(dst + (r * a.wb + 32 * hc) * 4, pre[r][hc]);
+        }
+    }
+}
+
+// Direct mode: two finished 8-channel units of 32 pixels straight to Y (lane = pixel: a warp writes whole row pieces).
+template <int ACT, bool RES>
+__device__ __forceinline__ void ig_finish_direct(const uint32_t (&r)[2][8], const float (&rv)[2][8], float* ya, float* yb, int64_t plane,
+                                                 int na, int nb) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float va = pw_act<ACT>(__uint_as_float(r[0][j]));
+        float vb = pw_act<ACT>(__uint_as_float(r[1][j]));
+        if (RES) va += rv[0][j], vb += rv[1][j];
+        if (j < na) ya[j * plane] = va;
+        if (j < nb) yb[j * plane] = vb;
+    }
+}
+
+// One split warp's share of a stage: its channel's window rows, shifted by the kernel column (already in `src`), as hi
+// and lo lines of the operand.  Four rows at a time: the loads are independent, the stores follow.
+__device__ __forceinline__ void ig_split_stage(uint32_t src, uint32_t hi, uint32_t lo, int rb, int wb) {
+#pragma unroll 1
+    for (int r0 = 0; r0 < rb; r0 += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = r0 + u < rb ? ld_shared_f32(src + (r0 + u) * wb * 4) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (r0 + u < rb) {
+                float h, l;
+                split_tf32(v[u], h, l);
+                st_shared_f32(hi + (r0 + u) * 1024, h);
+                st_shared_f32(lo + (r0 + u) * 1024, l);
+            }
+        }
+    }
+}
+
+// DIRECT: X and Y do not go through the TMA unit (see IgArgs::direct_io).
+template <bool DIRECT>
 __global__ void __launch_bounds__(IG_THREADS, 1)
 conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ CUtensorMap tmap_y, const IgArgs args) {
@@ -157,18 +226,20 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
                 const IgTile t = ig_tile(args, tile);
                 for (int cb = 0; ok && cb < args.cblocks; ++cb) {
-                    if (!ptx::mbar_wait_suspend(&raw_empty[slot], slot_phase ^ 1)) {
-                        atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
-                        ok = false;
-                        break;
-                    }
-                    ptx::mbar_expect_tx(&raw_full[slot], static_cast<uint32_t>(args.wb * args.rb * IG_KC * 4));
-                    // x is a multiple of 4 elements (16 bytes); rows and columns outside the image arrive as zeros
-                    ptx::tma_load_4d(raw_base + slot * args.raw_bytes, &tmap_x, &raw_full[slot], t.w0 - args.pla,
-                                     t.h0 - args.pad_top, cb * IG_KC, t.n);
-                    if (++slot == IG_RAW_SLOTS) {
-                        slot = 0;
-                        slot_phase ^= 1;
+                    if constexpr (!DIRECT) {
+                        if (!ptx::mbar_wait_suspend(&raw_empty[slot], slot_phase ^ 1)) {
+                            atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
+                            ok = false;
+                            break;
+                        }
+                        ptx::mbar_expect_tx(&raw_full[slot], static_cast<uint32_t>(args.wb * args.rb * IG_KC * 4));
+                        // x is a multiple of 4 elements (16 bytes); rows and columns outside the image arrive as zeros
+                        ptx::tma_load_4d(raw_base + slot * args.raw_bytes, &tmap_x, &raw_full[slot], t.w0 - args.pla,
+                                         t.h0 - args.pad_top, cb * IG_KC, t.n);
+                        if (++slot == IG_RAW_SLOTS) {
+                            slot = 0;
+                            slot_phase ^= 1;
+                        }
                     }
                     for (int kj = 0; kj < args.kw; ++kj) {
                         if (!ptx::mbar_wait_suspend(&empty[stage], phase ^ 1)) {
@@ -195,6 +266,8 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         // ------------------------------ MMA issuer ------------------------------
         if (ptx::elect_one()) {
             const uint32_t idesc = pw_idesc(static_cast<uint32_t>(args.nb), 1u);
+            const uint64_t d_x_first = make_smem_desc_sw128_base32(ptx::smem_u32(smem), 1024, 512);
+            const uint64_t d_w_first = make_smem_desc_sw128_base32(ptx::smem_u32(smem) + args.shift_bytes, args.kh * 1024, 512);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -215,18 +288,17 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t xh = ptx::smem_u32(smem + stage * args.stage_bytes), xl = xh + x_part_bytes;
-                    const uint32_t wh = xh + args.shift_bytes, wl = wh + w_part_bytes;
+                    // descriptors differ only in their start address field (bytes / 16): one 64-bit add each
+                    const uint64_t d_xh0 = d_x_first + static_cast<uint32_t>(stage * (args.stage_bytes >> 4));
+                    const uint64_t d_wh0 = d_w_first + static_cast<uint32_t>(stage * (args.stage_bytes >> 4));
                     for (int ki = 0; ki < args.kh; ++ki) {
-                        // W: N-major, 32-channel atoms kh KB apart, 4-channel (K) groups 512 bytes apart
-                        const uint64_t d_wh = make_smem_desc_sw128_base32(wh + ki * 1024, args.kh * 1024, 512);
-                        const uint64_t d_wl = make_smem_desc_sw128_base32(wl + ki * 1024, args.kh * 1024, 512);
+                        // W: N-major, 32-channel atoms kh KB apart, 4-channel (K) groups 512 bytes apart; kernel row ki is 1 KB in
+                        const uint64_t d_wh = d_wh0 + static_cast<uint32_t>(ki * 64), d_wl = d_wh + static_cast<uint32_t>(w_part_bytes >> 4);
 #pragma unroll
                         for (int hf = 0; hf < 2; ++hf) {
                             // X: MN-major, one atom per image row (1 KB apart: two 4-channel groups of 512 bytes); kernel
                             // row ki of half hf starts at window row 4 hf + ki
-                            const uint64_t d_xh = make_smem_desc_sw128_base32(xh + (4 * hf + ki) * 1024, 1024, 512);
-                            const uint64_t d_xl = make_smem_desc_sw128_base32(xl + (4 * hf + ki) * 1024, 1024, 512);
+                            const uint64_t d_xh = d_xh0 + static_cast<uint32_t>((4 * hf + ki) * 64), d_xl = d_xh + static_cast<uint32_t>(x_part_bytes >> 4);
                             const uint32_t d = d_tmem + hf * half_stride;
                             pw_mma(d, d_xl, d_wh, idesc, (st | ki) != 0 ? 1u : 0u);  // the two small terms first
                             pw_mma(d, d_xh, d_wl, idesc, 1u);
@@ -253,12 +325,23 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         int stage = 0, slot = 0;
         uint32_t phase = 0, slot_phase = 0;
         bool ok = true;
+        float pre[DIRECT ? IG_MAX_RB : 1][2];
+        if constexpr (DIRECT) if (blockIdx.x < args.num_tiles) ig_fetch_window(args, ig_tile(args, blockIdx.x), 0, ch, lane, pre);
         for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
             for (int cb = 0; ok && cb < args.cblocks; ++cb) {
-                ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&raw_full[slot], slot_phase));
-                if (!ok) {
-                    if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
-                    break;
+                if constexpr (DIRECT) {
+                    // this warp alone writes and reads its channel of the window: no barrier, program order is enough
+                    ig_store_window(ptx::smem_u32(raw_base + slot * args.raw_bytes) + (ch * args.rb * args.wb + lane) * 4, args, lane, pre);
+                    __syncwarp();
+                    const bool last_cb = cb + 1 == args.cblocks;
+                    const int next_tile = last_cb ? tile + gridDim.x : tile;
+                    if (next_tile < args.num_tiles) ig_fetch_window(args, ig_tile(args, next_tile), last_cb ? 0 : cb + 1, ch, lane, pre);
+                } else {
+                    ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&raw_full[slot], slot_phase));
+                    if (!ok) {
+                        if (lane == 0) atomicExch(args.status, DEV_TIMEOUT_EPILOGUE);
+                        break;
+                    }
                 }
                 const uint32_t src0 = ptx::smem_u32(raw_base + slot * args.raw_bytes) + (ch * args.rb * args.wb + args.xoff + lane) * 4;
                 for (int kj = 0; kj < args.kw; ++kj) {
@@ -269,21 +352,7 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                     }
                     const uint32_t hi = ptx::smem_u32(smem + stage * args.stage_bytes) + dst_lane, lo = hi + x_part_bytes;
                     const uint32_t src = src0 + kj * 4;
-#pragma unroll 1
-                    for (int r0 = 0; r0 < args.rb; r0 += 4) {
-                        float v[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) v[u] = r0 + u < args.rb ? ld_shared_f32(src + (r0 + u) * args.wb * 4) : 0.0f;
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (r0 + u < args.rb) {
-                                float h, l;
-                                split_tf32(v[u], h, l);
-                                st_shared_f32(hi + (r0 + u) * 1024, h);
-                                st_shared_f32(lo + (r0 + u) * 1024, l);
-                            }
-                        }
-                    }
+                    ig_split_stage(src, hi, lo, args.rb, args.wb);
                     ptx::fence_proxy_async_smem();  // the tensor core reads shared memory through the async proxy
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&ready[stage]);
@@ -293,7 +362,7 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                     }
                 }
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&raw_empty[slot]);  // this warp has read its channel of the window
+                if (lane == 0 && !DIRECT) ptx::mbar_arrive(&raw_empty[slot]);  // this warp has read its channel of the window
                 if (++slot == IG_RAW_SLOTS) {
                     slot = 0;
                     slot_phase ^= 1;
@@ -356,6 +425,23 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                     for (int j = 0; j < 8; ++j) {
                         r[0][j] = __float_as_uint(__uint_as_float(r[0][j]) + bv[0][j]);
                         r[1][j] = __float_as_uint(__uint_as_float(r[1][j]) + bv[1][j]);
+                    }
+                    if constexpr (DIRECT) {
+                        float* yo = args.y + (static_cast<int64_t>(t.n) * args.m + m0) * plane + static_cast<int64_t>(row) * args.ow + t.w0 + lane;
+                        const int na = p_ok ? args.m - (m0 + ca) : 0, nb2 = (p_ok && two) ? args.m - (m0 + cb) : 0;  // channels to store (8 or fewer)
+                        float *ya = yo + ca * plane, *yb = yo + cb * plane;
+                        if (res) {
+                            if (args.act == B200ML_EPI_SWISH) ig_finish_direct<B200ML_EPI_SWISH, true>(r, rv, ya, yb, plane, na, nb2);
+                            else if (args.act == 0) ig_finish_direct<0, true>(r, rv, ya, yb, plane, na, nb2);
+                            else if (args.act == B200ML_EPI_RELU) ig_finish_direct<B200ML_EPI_RELU, true>(r, rv, ya, yb, plane, na, nb2);
+                            else ig_finish_direct<B200ML_EPI_GELU, true>(r, rv, ya, yb, plane, na, nb2);
+                        } else {
+                            if (args.act == B200ML_EPI_SWISH) ig_finish_direct<B200ML_EPI_SWISH, false>(r, rv, ya, yb, plane, na, nb2);
+                            else if (args.act == 0) ig_finish_direct<0, false>(r, rv, ya, yb, plane, na, nb2);
+                            else if (args.act == B200ML_EPI_RELU) ig_finish_direct<B200ML_EPI_RELU, false>(r, rv, ya, yb, plane, na, nb2);
+                            else ig_finish_direct<B200ML_EPI_GELU, false>(r, rv, ya, yb, plane, na, nb2);
+                        }
+                        continue;
                     }
                     if (res) {
                         if (args.act == B200ML_EPI_SWISH) pw_finish_turn<B200ML_EPI_SWISH, true>(r, rv, stg_lane);
@@ -451,7 +537,6 @@ bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int6
     if (p->stride_h != 1 || p->stride_w != 1 || p->dil_h != 1 || p->dil_w != 1) return false;
     if (p->pad_top > 8 || p->pad_left > 8 || p->pad_bottom > 8 || p->pad_right > 8) return false;
     if (p->c * p->kh * p->kw < 64 || p->m < 16) return false;                 // short reductions stay on the FP32 pipe
-    if (p->w % 4 != 0 || ow % 4 != 0 || !aligned16(p->x) || !aligned16(p->y)) return false;  // 16-byte strides and bases for the tensor maps
     if (p->n * oh * ow < 4 * 1024) return false;                              // too little work for two launches
     const IgPlan pl = ig_plan(p);
     if (!pl.ok) return false;
@@ -473,8 +558,10 @@ int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, i
         int rc = check_launch("ig_split_weights");
         if (rc) return rc;
     }
+    // X and Y go through the TMA unit when their row pitches and bases are multiples of 16 bytes
+    const bool direct_io = p->w % 4 != 0 || ow % 4 != 0 || !aligned16(p->x) || !aligned16(p->y);
     CUtensorMap tx, tw, ty;
-    {
+    if (!direct_io) {
         const cuuint64_t dims[4] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->c, (cuuint64_t)p->n};
         const cuuint64_t strides[3] = {(cuuint64_t)p->w * 4, (cuuint64_t)p->w * p->h * 4, (cuuint64_t)p->w * p->h * p->c * 4};
         const cuuint32_t box[4] = {(cuuint32_t)pl.wb, (cuuint32_t)pl.rb, IG_KC, 1};
@@ -489,7 +576,10 @@ int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, i
                                          CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
         if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "conv k x k: cuTensorMapEncodeTiled(W) failed with CUresult %d", (int)r);
     }
-    {
+    if (direct_io) {
+        tx = tw;  // never used for a copy; the kernel's parameters still have to be valid maps
+        ty = tw;
+    } else {
         const cuuint64_t dims[4] = {(cuuint64_t)ow, (cuuint64_t)oh, (cuuint64_t)p->m, (cuuint64_t)p->n};
         const cuuint64_t strides[3] = {(cuuint64_t)ow * 4, (cuuint64_t)ow * oh * 4, (cuuint64_t)ow * oh * p->m * 4};
         const cuuint32_t box[4] = {32, 1, 8, 1};
@@ -519,16 +609,23 @@ int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, i
     a.stage_bytes = pl.stage_bytes;
     a.shift_bytes = pl.shift_bytes;
     a.act = p->act & (B200ML_EPI_RELU | B200ML_EPI_SWISH | B200ML_EPI_GELU);
+    a.direct_io = direct_io ? 1 : 0;
+    a.h = (int32_t)p->h;
+    a.w = (int32_t)p->w;
+    a.x = static_cast<const float*>(p->x);
+    a.y = static_cast<float*>(p->y);
     a.bias = static_cast<const float*>(p->bias);
     a.residual = static_cast<const float*>(p->residual);
     a.status = ctx->status_dev;
     static int configured[64] = {};
     if (configured[ctx->device & 63] < pl.smem) {
-        B200ML_CUDA(cudaFuncSetAttribute(conv_igemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem));
+        B200ML_CUDA(cudaFuncSetAttribute(conv_igemm_tf32x3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem));
+        B200ML_CUDA(cudaFuncSetAttribute(conv_igemm_tf32x3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem));
         configured[ctx->device & 63] = pl.smem;
     }
     const int grid = a.num_tiles < ctx->sm_count ? a.num_tiles : ctx->sm_count;
-    B200ML_CUDA(launch_pdl(conv_igemm_tf32x3_kernel, dim3(grid), dim3(IG_THREADS), (size_t)pl.smem, stream, tx, tw, ty, a));
+    if (direct_io) B200ML_CUDA(launch_pdl(conv_igemm_tf32x3_kernel<true>, dim3(grid), dim3(IG_THREADS), (size_t)pl.smem, stream, tx, tw, ty, a));
+    else B200ML_CUDA(launch_pdl(conv_igemm_tf32x3_kernel<false>, dim3(grid), dim3(IG_THREADS), (size_t)pl.smem, stream, tx, tw, ty, a));
     return check_launch("conv_igemm_tf32x3");
 }
 

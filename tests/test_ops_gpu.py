@@ -484,13 +484,17 @@ def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
 @pytest.mark.parametrize("n, cin, cout, hw, k, pads", [(8, 16, 32, (48, 48), (3, 3), (1, 1, 1, 1)), (4, 64, 64, (56, 56), (3, 3), (1, 1, 1, 1)),
                                                        (6, 10, 40, (36, 40), (5, 5), (2, 2, 2, 2)), (4, 24, 200, (30, 44), (3, 3), (0, 1, 0, 1)),
                                                        (3, 32, 16, (80, 96), (3, 5), (1, 2, 1, 2)), (5, 12, 48, (40, 64), (3, 3), (2, 0, 0, 2)),
-                                                       (2, 8, 32, (64, 64), (7, 7), (3, 3, 3, 3)), (64, 128, 128, (16, 16), (3, 3), (1, 1, 1, 1))])
+                                                       (2, 8, 32, (64, 64), (7, 7), (3, 3, 3, 3)), (64, 128, 128, (16, 16), (3, 3), (1, 1, 1, 1)),
+                                                       (24, 32, 48, (14, 14), (3, 3), (1, 1, 1, 1)), (96, 16, 32, (7, 7), (3, 3), (1, 1, 1, 1)),
+                                                       (10, 8, 24, (30, 27), (3, 3), (1, 1, 1, 1)), (6, 8, 16, (32, 32), (3, 3), (0, 0, 0, 0)),
+                                                       (8, 9, 40, (21, 37), (5, 3), (2, 1, 2, 1))])
 @pytest.mark.parametrize("act", ["", "Relu"])
 def test_conv_kxk_tensor_core(n, cin, cout, hw, k, pads, act, rng):
     """k x k stride-1 convolutions large enough for the implicit-GEMM kernel (3 x TF32; kernel columns as shifted copies
     of the input window, kernel rows as descriptor offsets): ragged tiles in both directions, channel counts that are
     not whole 8- or 32-blocks, more than one block of output channels, asymmetric padding, non-square kernels, bias,
-    activation and residual.  Against the oracle at the fp32 tolerance, and against a float64 convolution at a bound
+    activation and residual; image widths that are not a multiple of 4 (no tensor map for X and Y: the warps load and
+    store themselves).  Against the oracle at the fp32 tolerance, and against a float64 convolution at a bound
     that a single-TF32 product (relative error 5e-4) would break."""
     if os.environ.get("B200ML_CONV_TC", "1") == "0":
         pytest.skip("the tensor-core convolution is switched off")
