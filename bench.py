@@ -617,6 +617,29 @@ def main():
     bufs[0].copy_(x0)
     gathered = torch.empty(world * BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev) if world > 1 else None
     final_buf = bufs[(args.warmup + args.steps) % 2]
+    # the final all-gather: this library's kernel that stores the rank's block into every peer's memory (CUDA IPC, NVLink),
+    # unless B200ML_GATHER=nccl or the mapping cannot be set up on some rank - then NCCL's collective
+    peer = None
+    if world > 1:
+        ok = 0
+        if os.environ.get("B200ML_GATHER", "peer") != "nccl":
+            try:
+                peer = D.PeerGather((BATCH, SEQ, HIDDEN), torch.float16, dev, rank, world)
+                ok = 1
+            except Exception as e:
+                sys.stderr.write("rank %d: peer all-gather not available (%s)\n" % (rank, str(e).splitlines()[0] if str(e) else type(e).__name__))
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if not int(flag):
+            peer = None
+        if peer is not None:
+            gathered = peer.gathered
+
+    def do_gather():
+        if peer is not None:
+            peer.gather(final_buf)
+        else:
+            D.gather_outputs(final_buf, out=gathered)
 
     def run_steps(first, count):
         for s in range(first, first + count):
@@ -639,11 +662,11 @@ def main():
         with torch.cuda.graph(g, capture_error_mode="thread_local"):
             run_steps(first, count)
             if gather:
-                D.gather_outputs(final_buf, out=gathered)
+                do_gather()
         return g
 
     if world > 1:
-        D.gather_outputs(final_buf, out=gathered)  # creates the NCCL communicator before any capture
+        do_gather()  # NCCL: creates the communicator before any capture
         barrier()
     warm_graph = capture(0, args.warmup)
     gather_in_graph = False
@@ -667,7 +690,7 @@ def main():
     uploaded = upload_graph(timed_graph)  # the first replay is a timed one: the upload must not be part of it
     after = None
     if world > 1 and not gather_in_graph:
-        after = lambda: D.gather_outputs(final_buf, out=gathered)
+        after = do_gather
 
     # ---- device-timed region: W warm-up steps, then the K-step graph R times back to back ----
     barrier()
@@ -724,7 +747,7 @@ def main():
         barrier()
         g0.record()
         for _ in range(10):
-            D.gather_outputs(final_buf, out=gathered)
+            do_gather()
         g1.record()
         torch.cuda.synchronize()
         gather_ms = g0.elapsed_time(g1) / 10
@@ -922,12 +945,14 @@ def main():
                              "p10": float(np.percentile(times, 10)), "p90": float(np.percentile(times, 90))},
                "timed_region_ms": float(np.sum(times)), "timed_region_host_ms": host_ms,
                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_config5": e2e_config5,
-               "gpu_launches": kernels_per_step * args.steps * replays,
+               "gpu_launches": kernels_per_step * args.steps * replays + (replays if peer is not None else 0),
                "kernels_per_step": kernels_per_step, "clocks": clocks, "device_status": status,
                "peaks": pk}
         if world > 1:
             out["gather_checked"] = gather_checked
             out["gather_ms"] = gather_ms
+            out["gather_method"] = ("b200ml_peer_allgather: one kernel per rank, 16-byte stores into the peers' memory (CUDA IPC) over NVLink"
+                                    if peer is not None else "NCCL all_gather_into_tensor")
             out["gather_bytes_per_rank"] = nbytes
         if other_configs is not None:
             out["other_configs"] = other_configs
@@ -944,6 +969,8 @@ def main():
         gc.collect()
         torch.cuda.synchronize()
         dist.barrier()
+        if peer is not None:
+            peer.close()
         dist.destroy_process_group()
         guard.cancel()
 

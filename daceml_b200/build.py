@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdaceml_b200.so")
 
-SOURCES = ["api.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_ln.cu", "gemm_simt.cu", "gemm_tf32.cu", "rowwise.cu", "elementwise.cu", "indexing.cu", "conv.cu", "conv1x1_tc.cu", "conv_igemm.cu", "attention.cu", "diagnostics.cu"]
+SOURCES = ["api.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_ln.cu", "gemm_simt.cu", "gemm_tf32.cu", "rowwise.cu", "elementwise.cu", "indexing.cu", "conv.cu", "conv1x1_tc.cu", "conv_igemm.cu", "attention.cu", "diagnostics.cu", "peer.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -175,6 +175,10 @@ int b200ml_ctx_create(int device, int64_t workspace_bytes, b200ml_ctx** out) {
     err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
     if (err == cudaSuccess && qres == cudaDriverEntryPointSuccess) ctx->encode_tiled = fn;
     else (void)cudaGetLastError();
+    fn = nullptr;
+    err = cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres);
+    if (err == cudaSuccess && qres == cudaDriverEntryPointSuccess) ctx->mem_get_address_range = fn;
+    else (void)cudaGetLastError();
     *out = ctx;
     return B200ML_OK;
 }

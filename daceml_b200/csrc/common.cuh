@@ -20,6 +20,7 @@ enum : int32_t {
     DEV_TIMEOUT_ATTN = 4,
     DEV_BAD_INDEX = 5,  // Gather met an index outside its axis
     DEV_TIMEOUT_PROBE = 6,  // the wait probe's barrier was (as intended) never completed
+    DEV_TIMEOUT_PEER = 7,   // a rank's all-gather kernel gave up waiting for a peer's flag
 };
 
 struct b200ml_ctx {
@@ -29,6 +30,7 @@ struct b200ml_ctx {
     int64_t workspace_bytes = 0;
     int32_t* status_dev = nullptr;  // one word in device memory
     void* encode_tiled = nullptr;   // cuTensorMapEncodeTiled, resolved through the runtime
+    void* mem_get_address_range = nullptr;  // cuMemGetAddressRange, likewise
 };
 
 namespace b200ml {

@@ -98,3 +98,70 @@ class ShardedEncoder:
     def __call__(self, x_global, gather=True):
         y = self.model(shard_batch(x_global, self.rank, self.world))
         return gather_outputs(y, group=self.group) if gather else y
+
+
+class PeerGather:
+    """The final all-gather as one kernel per rank that stores its block into every peer's memory over NVLink
+    (``b200ml_peer_allgather``), instead of an NCCL collective.
+
+    Construction is collective: every rank allocates ``gathered`` (``[world * rows_per_rank, ...]``) and its flag
+    words in one device allocation, exports it through CUDA IPC, exchanges handles with ``all_gather_object`` and maps
+    the peers' allocations.  ``gather(y_local)`` launches the kernel on the current stream and returns ``gathered``; it
+    may be captured in a CUDA graph.  Raises if the mapping cannot be set up (the caller then stays with NCCL)."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, shape_per_rank, dtype, device, rank, world, group=None):
+        import ctypes
+        from . import lib as L
+        if world > L.MAX_PEERS:
+            raise ValueError("at most {} ranks".format(L.MAX_PEERS))
+        self.rank, self.world, self.group = rank, world, group
+        self.ctx = L.get_context(device)
+        per = 1
+        for d in shape_per_rank:
+            per *= int(d)
+        self.bytes_per_rank = per * torch.empty((), dtype=dtype).element_size()
+        if self.bytes_per_rank % 16:
+            raise ValueError("the rank block must be a multiple of 16 bytes")
+        total = world * self.bytes_per_rank
+        # one allocation of its own (at least 2 MB: the caching allocator gives such a request its own segment), zeroed
+        self.storage = torch.zeros(max(total + self.FLAG_BYTES, 2 << 20), dtype=torch.uint8, device=device)
+        self.gathered = self.storage[:total].view(dtype).view((world * int(shape_per_rank[0]), ) + tuple(shape_per_rank[1:]))
+        torch.cuda.synchronize(device)
+        handle = (ctypes.c_ubyte * 64)()
+        offset = ctypes.c_int64(0)
+        L.check(self.ctx.lib.b200ml_ipc_export(self.ctx.handle, ctypes.c_void_p(self.storage.data_ptr()), handle, ctypes.byref(offset)))
+        mine = (bytes(handle), int(offset.value))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._opened = []
+        self.peers = L.PeerGroup()
+        self.peers.rank, self.peers.world = rank, world
+        for r in range(world):
+            if r == rank:
+                base = self.storage.data_ptr()
+            else:
+                h = (ctypes.c_ubyte * 64).from_buffer_copy(everyone[r][0])
+                ptr = ctypes.c_void_p()
+                L.check(self.ctx.lib.b200ml_ipc_open(self.ctx.handle, h, everyone[r][1], ctypes.byref(ptr)))
+                self._opened.append((ptr.value, everyone[r][1]))
+                base = ptr.value
+            self.peers.gathered[r] = base
+            self.peers.flags[r] = base + total
+        dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores into one
+
+    def gather(self, y_local):
+        import ctypes
+        from . import lib as L
+        if not y_local.is_contiguous() or y_local.numel() * y_local.element_size() != self.bytes_per_rank:
+            raise ValueError("the local block must be contiguous and of the size given at construction")
+        L.check(self.ctx.lib.b200ml_peer_allgather(self.ctx.handle, ctypes.byref(self.peers), ctypes.c_void_p(y_local.data_ptr()),
+                                                   self.bytes_per_rank, L.current_stream()))
+        return self.gathered
+
+    def close(self):
+        """Unmaps the peers' allocations.  Collective in effect: call it on every rank once no launch is in flight."""
+        for ptr, off in self._opened:
+            self.ctx.lib.b200ml_ipc_close(self.ctx.handle, ptr, off)
+        self._opened = []

@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = [
     "b200ml_layernorm", "b200ml_reduce", "b200ml_reduce_static", "b200ml_unary", "b200ml_binary", "b200ml_bias_act", "b200ml_transpose",
     "b200ml_cast", "b200ml_conv2d", "b200ml_se_gate", "b200ml_attention_f16", "b200ml_strided_copy", "b200ml_gather",
     "b200ml_where", "b200ml_compare", "b200ml_maxpool2d", "b200ml_wait_probe", "b200ml_strided_copy_parts",
+    "b200ml_peer_allgather", "b200ml_ipc_export", "b200ml_ipc_open", "b200ml_ipc_close",
 ]
 
 
@@ -45,6 +46,15 @@ class B200Error(RuntimeError):
 
 class Unsupported(B200Error):
     """The library has no kernel for this (valid) request; expansions report "cannot be applied"."""
+
+
+MAX_PEERS = 16
+
+
+class PeerGroup(ctypes.Structure):
+    """b200ml_peer_group of include/daceml_b200.h."""
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("gathered", ctypes.c_void_p * MAX_PEERS),
+                ("flags", ctypes.c_void_p * MAX_PEERS)]
 
 
 class GemmParams(ctypes.Structure):
@@ -140,6 +150,10 @@ def load_library(path=None):
         lib.b200ml_maxpool2d.argtypes = [vp, c_i32, vp, vp, c_i64, c_i64, c_i64] + [c_i32] * 8 + [vp]
         lib.b200ml_wait_probe.argtypes = [vp, c_i64, vp, vp]
         lib.b200ml_strided_copy_parts.argtypes = [vp, c_i32, c_i32, ctypes.POINTER(vp), ctypes.POINTER(vp), c_i32, i64p, i64p, i64p, vp]
+        lib.b200ml_peer_allgather.argtypes = [vp, ctypes.POINTER(PeerGroup), vp, c_i64, vp]
+        lib.b200ml_ipc_export.argtypes = [vp, vp, vp, i64p]
+        lib.b200ml_ipc_open.argtypes = [vp, vp, c_i64, ctypes.POINTER(vp)]
+        lib.b200ml_ipc_close.argtypes = [vp, vp, c_i64]
         for name in EXPORTED_SYMBOLS:
             fn = getattr(lib, name)
             if name not in ("b200ml_last_error", "b200ml_launch_count", "b200ml_ctx_workspace_bytes"):

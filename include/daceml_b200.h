@@ -336,6 +336,37 @@ int b200ml_se_gate(b200ml_ctx* ctx, int32_t dtype, const void* pooled, const voi
                    int64_t r, b200ml_stream stream);
 
 /* ------------------------------------------------------------------------- */
+/* Multi-GPU: all-gather of the ranks' outputs over peer memory               */
+/* ------------------------------------------------------------------------- */
+
+/* No counterpart in the reference (it has no multi-device path).  One process per GPU; the batch is split over the
+ * ranks and their outputs are gathered once at the end.  Every rank allocates a gathered buffer
+ * ([world][bytes_per_rank], 16-byte aligned) and 64 zero-initialised uint32 flag words, exports them with
+ * b200ml_ipc_export, sends handle and offset to its peers through whatever channel the host program has, and maps the
+ * peers' with b200ml_ipc_open (CUDA IPC: device memory obtained from cudaMalloc, all processes on one box). */
+#define B200ML_MAX_PEERS 16
+typedef struct {
+    int32_t rank, world;
+    void* gathered[B200ML_MAX_PEERS];    /* [r]: rank r's gathered buffer as mapped in this process ([rank] is this rank's own) */
+    void* flags[B200ML_MAX_PEERS];       /* [r]: rank r's 64 flag words as mapped in this process */
+} b200ml_peer_group;
+
+/* Every rank calls this once per step, in the same order on every rank: src (bytes_per_rank bytes, a multiple of 16)
+ * lands in slot [rank] of every rank's gathered buffer by plain 16-byte stores over NVLink; when the kernel has
+ * completed on a rank, that rank's gathered buffer holds every rank's block.  A rank does not overwrite a peer's
+ * buffer before that peer has entered the same step on its stream.  The waits on the peers' flags are bounded (1 s):
+ * a peer that never arrives leaves status 7 in the context's status word (b200ml_ctx_device_status) instead of a hang.
+ * The launch can be captured in a CUDA graph and replayed (the step counter lives in the flag words). */
+int b200ml_peer_allgather(b200ml_ctx* ctx, const b200ml_peer_group* group, const void* src, int64_t bytes_per_rank,
+                          b200ml_stream stream);
+/* handle64 receives the 64-byte CUDA IPC handle of the allocation that holds ptr, *offset ptr's offset inside it. */
+int b200ml_ipc_export(b200ml_ctx* ctx, const void* ptr, void* handle64, int64_t* offset);
+/* Maps the allocation behind a peer's handle into this process and returns the address that corresponds to the
+ * peer's ptr; enables peer access from this context's device as needed.  Not for handles of this same process. */
+int b200ml_ipc_open(b200ml_ctx* ctx, const void* handle64, int64_t offset, void** ptr);
+int b200ml_ipc_close(b200ml_ctx* ctx, void* ptr, int64_t offset);
+
+/* ------------------------------------------------------------------------- */
 /* Fused attention                                                            */
 /* ------------------------------------------------------------------------- */
 
