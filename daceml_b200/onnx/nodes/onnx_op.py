@@ -191,10 +191,26 @@ class ONNXOp(sd.Node, metaclass=_ONNXOpMeta):
             raise KeyError('{} has no implementation "{}" (registered: {})'.format(
                 type(self).__name__, impl, sorted(type(self).implementations)))
         result = type(self).implementations[impl].expansion(self, state, sdfg, **kwargs)
+        if isinstance(result, sd.SDFG):
+            result = _nested_sdfg_tasklet(self, result)
         if not isinstance(result, sd.KernelTasklet):
             raise TypeError("expansion of {} returned {}, expected a KernelTasklet".format(self, type(result)))
         state.replace_node(self, result)
         return impl
+
+
+def _nested_sdfg_tasklet(node, nsdfg):
+    """An expansion may return an SDFG whose non-transient arrays are named after the node's connectors (see
+    ``empty_sdfg_for_node``); it is compiled here (its own library nodes expand, its transients are allocated) and runs in
+    the node's place."""
+    compiled = nsdfg.compile()
+
+    def run(ins, outs):
+        args = dict(ins)
+        args.update(outs)
+        compiled(**{k: v for k, v in args.items() if k in nsdfg.arrays})
+
+    return sd.KernelTasklet(node.label + "_expansion", run, kernels=tuple(compiled.kernel_names()))
 
 
 def attach_implementation(op, name, forward_cls):

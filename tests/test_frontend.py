@@ -236,3 +236,52 @@ def test_validate_checks_the_schema_type_constraints():
     one[0].validate(one[1], one[2])
     one = one_node("Gather", {"data": ((5, 4), torch.float16), "indices": ((3, ), torch.int64)}, {"output": ((3, 4), torch.float16)})
     one[0].validate(one[1], one[2])
+
+
+def test_helper_api_for_python_implementations():
+    """``python_pure_op_implementation`` / ``program_for_node`` / ``empty_sdfg_for_node``
+    (daceml/onnx/op_implementations/utils.py:43-225): registration under the function's name, compute variables,
+    the reference's messages for parameters that are not connectors."""
+    import torch
+    import daceml_b200.onnx as donnx
+    from daceml_b200 import sdfg as sd
+    from daceml_b200.onnx.forward_implementation_abc import ONNXForward
+    from daceml_b200.onnx.op_implementations.utils import (empty_sdfg_for_node, parse_variadic_param, program_for_node,
+                                                           python_pure_op_implementation)
+
+    @python_pure_op_implementation(alpha=lambda node: node.alpha, shape=lambda X: X.shape)
+    def LeakyRelu(X, Y):
+        Y[:] = torch.where(X > 0, X, alpha * X).reshape(shape)  # noqa: F821 - alpha and shape come from compute
+
+    try:
+        assert "pure" in donnx.ONNXLeakyRelu.implementations
+        assert any(args.get("op") == "LeakyRelu" and args.get("name") == "pure" for _, args in ONNXForward.extensions().items())
+        g = sd.SDFG("leaky")
+        g.add_array("x", (4, 5), torch.float32)
+        g.add_array("y", (4, 5), torch.float32)
+        st = g.add_state()
+        node = donnx.ONNXLeakyRelu("leaky0", alpha=0.25)
+        node.implementation = "pure"
+        st.add_edge(st.add_read("x"), None, node, "X", g.make_array_memlet("x"))
+        st.add_edge(node, "Y", st.add_write("y"), None, g.make_array_memlet("y"))
+        ns, nst, ins, outs = empty_sdfg_for_node(g, st, node)
+        assert set(ns.arrays) == {"X", "Y"} and ns.arrays["X"].shape == (4, 5) and not ns.arrays["Y"].transient
+        assert set(ins) == {"X"} and set(outs) == {"Y"}
+        g.expand_library_nodes()
+        (tasklet, ) = [n for n in st.nodes() if isinstance(n, sd.KernelTasklet)]
+        x = torch.linspace(-2, 2, 20).reshape(4, 5)
+        y = torch.empty(4, 5)
+        tasklet.fn({"X": x}, {"Y": y})  # the function itself runs anywhere; compiled SDFGs bind device tensors
+        assert torch.equal(y, torch.where(x > 0, x, 0.25 * x))
+
+        def wrong(X, Z):
+            pass
+
+        with pytest.raises(ValueError, match="'Z' was not found as an input or output for LeakyRelu"):
+            program_for_node(wrong, g, st, node)
+        assert parse_variadic_param("Inputs__3") == ("Inputs", 3)
+        with pytest.raises(ValueError):
+            parse_variadic_param("Inputs__03")
+    finally:
+        donnx.ONNXLeakyRelu.implementations.pop("pure", None)
+        ONNXForward.unregister(LeakyRelu)
