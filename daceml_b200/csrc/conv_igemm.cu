@@ -22,6 +22,12 @@
 // boxes in shared memory and send them with bulk tensor stores; those clip the columns past the image and the channels
 // past M.  Roles as in the 1x1 kernel: warp 0 TMA, warp 1 MMA and TMEM owner, warps 2-9 split, warps 10-25 epilogue;
 // one persistent CTA per SM; two accumulator sets, so a tile's epilogue runs under the next tile's products.
+//
+// Two variations.  DIRECT: images whose rows the TMA unit cannot describe (width not a multiple of 4 elements) - each split
+// warp copies its channel's window with asynchronous 4-byte copies (cp.async, zero fill for the padding), one channel
+// block ahead, and the epilogue warps store Y themselves.
+// Narrow images (output width <= 16, always DIRECT): an operand line holds two image rows, 8 apart, of 16 columns, so a
+// tile is 16 rows x 16 columns; kernel row i is still "i lines further down" for both rows of a line.
 #include "conv_tc.cuh"
 
 namespace b200ml {
@@ -35,7 +41,6 @@ constexpr int IG_ROWS = 8, IG_COLS = 32;       // output tile: two halves of 4 r
 constexpr int IG_RAW_SLOTS = 2;
 constexpr int IG_MAX_STAGES = 6;
 constexpr int IG_SPLIT_WARPS = IG_KC, IG_EPI_WARPS = 16;  // one split warp per channel of a stage
-constexpr int IG_MAX_RB = IG_ROWS + 7 - 1;                // window rows of the tallest kernel (7)
 constexpr int IG_FIRST_EPI = 2 + IG_SPLIT_WARPS;
 constexpr int IG_THREADS = 32 * (2 + IG_SPLIT_WARPS + IG_EPI_WARPS);
 constexpr int IG_OUT_BYTES = 2 * 8 * 32 * 4;   // per epilogue warp: two [8 channels][32 pixels] boxes
@@ -45,7 +50,8 @@ constexpr int IG_SMEM_LIMIT = 227 * 1024;
 struct IgArgs {
     int32_t c, m, oh, ow, kh, kw;
     int32_t cblocks, nb, nblocks, hblocks, wblocks, num_tiles;
-    int32_t rb, wb, xoff;                 // raw window: rows, columns, column of kernel column 0 for output column 0
+    int32_t parts, cw;                    // a 128-byte operand line = `parts` image rows (8 apart) of `cw` = 32 / parts columns
+    int32_t rb, rr, wb, xoff;             // window: operand lines, raw rows, raw columns, column of kernel column 0 for output column 0
     int32_t pla, pad_top;                 // the window starts pla columns left of the tile and pad_top rows above it
     int32_t stages, raw_bytes, stage_bytes, shift_bytes;
     int32_t act;
@@ -91,38 +97,34 @@ __device__ __forceinline__ IgTile ig_tile(const IgArgs& a, int tile) {
     tile /= a.hblocks;
     t.nblk = tile % a.nblocks;
     t.n = tile / a.nblocks;
-    t.h0 = hblk * IG_ROWS;
-    t.w0 = wblk * IG_COLS;
+    t.h0 = hblk * IG_ROWS * a.parts;
+    t.w0 = wblk * a.cw;
     return t;
 }
 
-// Direct mode: a split warp fetches its channel's window of the next channel block into registers (lane = window column,
-// and column + 32), zeros for the padding and for channels past C; the loads fly while the warp works on the current block.
-__device__ __forceinline__ void ig_fetch_window(const IgArgs& a, const IgTile& t, int cb, int ch, int lane, float (&pre)[IG_MAX_RB][2]) {
+// Direct mode: a split warp copies its channel's window of a channel block into its part of a raw slot with asynchronous
+// 4-byte copies (lane = window column, and column + 32); padding and channels past C are written as zeros (source size
+// 0).  The copies of the next block fly while the warp works on the current one; nothing is held in registers.
+__device__ __forceinline__ void ig_prefetch_window(uint32_t dst, const IgArgs& a, const IgTile& t, int cb, int ch, int lane) {
     const int c = cb * IG_KC + ch;
     const float* xc = a.x + (static_cast<int64_t>(t.n) * a.c + (c < a.c ? c : 0)) * a.h * a.w;
     const int gy0 = t.h0 - a.pad_top, gx0 = t.w0 - a.pla + lane;
-#pragma unroll
-    for (int r = 0; r < IG_MAX_RB; ++r) {
+    for (int r = 0; r < a.rr; ++r) {
         const int gy = gy0 + r;
-        const bool r_ok = c < a.c && r < a.rb && gy >= 0 && gy < a.h;
+        const bool r_ok = c < a.c && gy >= 0 && gy < a.h;
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
             const int gx = gx0 + 32 * hc;
-            pre[r][hc] = (r_ok && lane + 32 * hc < a.wb && gx >= 0 && gx < a.w) ? __ldg(xc + static_cast<int64_t>(gy) * a.w + gx) : 0.0f;
+            if (lane + 32 * hc < a.wb) {
+                const bool ok = r_ok && gx >= 0 && gx < a.w;
+                const float* src = ok ? xc + static_cast<int64_t>(gy) * a.w + gx : a.x;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + (r * a.wb + 32 * hc) * 4), "l"(src), "r"(ok ? 4 : 0) : "memory");
+            }
         }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void ig_store_window(uint32_t dst, const IgArgs& a, int lane, const float (&pre)[IG_MAX_RB][2]) {
-#pragma unroll
-    for (int r = 0; r < IG_MAX_RB; ++r) {
-        if (r < a.rb) {
-#pragma unroll
-            for (int hc = 0; hc < 2; ++hc)
-                if (lane + 32 * hc < a.wb) st_shared_f32(dst + (r * a.wb + 32 * hc) * 4, pre[r][hc]);
-        }
-    }
-}
+__device__ __forceinline__ void ig_prefetch_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // Direct mode: two finished 8-channel units of 32 pixels straight to Y (lane = pixel: a warp writes whole row pieces).
 template <int ACT, bool RES>
@@ -232,7 +234,7 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                             ok = false;
                             break;
                         }
-                        ptx::mbar_expect_tx(&raw_full[slot], static_cast<uint32_t>(args.wb * args.rb * IG_KC * 4));
+                        ptx::mbar_expect_tx(&raw_full[slot], static_cast<uint32_t>(args.wb * args.rr * IG_KC * 4));
                         // x is a multiple of 4 elements (16 bytes); rows and columns outside the image arrive as zeros
                         ptx::tma_load_4d(raw_base + slot * args.raw_bytes, &tmap_x, &raw_full[slot], t.w0 - args.pla,
                                          t.h0 - args.pad_top, cb * IG_KC, t.n);
@@ -325,17 +327,19 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         int stage = 0, slot = 0;
         uint32_t phase = 0, slot_phase = 0;
         bool ok = true;
-        float pre[DIRECT ? IG_MAX_RB : 1][2];
-        if constexpr (DIRECT) if (blockIdx.x < args.num_tiles) ig_fetch_window(args, ig_tile(args, blockIdx.x), 0, ch, lane, pre);
+        const uint32_t my_raw = ptx::smem_u32(raw_base) + (ch * args.rr * args.wb + lane) * 4;  // this warp's channel, slot 0
+        if constexpr (DIRECT) if (blockIdx.x < args.num_tiles) ig_prefetch_window(my_raw, args, ig_tile(args, blockIdx.x), 0, ch, lane);
         for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
             for (int cb = 0; ok && cb < args.cblocks; ++cb) {
                 if constexpr (DIRECT) {
-                    // this warp alone writes and reads its channel of the window: no barrier, program order is enough
-                    ig_store_window(ptx::smem_u32(raw_base + slot * args.raw_bytes) + (ch * args.rb * args.wb + lane) * 4, args, lane, pre);
+                    // this warp alone writes and reads its channel of the window: no barrier, its own copies' completion
+                    // and program order are enough; the other slot is free (the block that used it is done)
+                    ig_prefetch_wait();
                     __syncwarp();
                     const bool last_cb = cb + 1 == args.cblocks;
                     const int next_tile = last_cb ? tile + gridDim.x : tile;
-                    if (next_tile < args.num_tiles) ig_fetch_window(args, ig_tile(args, next_tile), last_cb ? 0 : cb + 1, ch, lane, pre);
+                    if (next_tile < args.num_tiles)
+                        ig_prefetch_window(my_raw + (slot ^ 1) * args.raw_bytes, args, ig_tile(args, next_tile), last_cb ? 0 : cb + 1, ch, lane);
                 } else {
                     ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&raw_full[slot], slot_phase));
                     if (!ok) {
@@ -343,7 +347,9 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         break;
                     }
                 }
-                const uint32_t src0 = ptx::smem_u32(raw_base + slot * args.raw_bytes) + (ch * args.rb * args.wb + args.xoff + lane) * 4;
+                // lane = (part, column): part j of operand line L is raw row L + 8 j
+                const uint32_t src0 = ptx::smem_u32(raw_base + slot * args.raw_bytes) +
+                                      ((ch * args.rr + 8 * (lane / args.cw)) * args.wb + args.xoff + lane % args.cw) * 4;
                 for (int kj = 0; kj < args.kw; ++kj) {
                     ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&empty[stage], phase ^ 1));
                     if (!ok) {
@@ -388,14 +394,15 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             ptx::tc_fence_after();
             const int m0 = t.nblk * args.nb;                                   // first output channel of the block
             const int nunits = ((args.m - m0 < args.nb ? args.m - m0 : args.nb) + 7) / 8;
-            const bool p_ok = t.w0 + lane < args.ow;
+            const int col = t.w0 + lane % args.cw;   // lane = (part, column); one part of 32 columns with TMA stores
 #pragma unroll 1
             for (int hf = 0; hf < 2; ++hf) {
-                const int row = t.h0 + 4 * hf + quarter;
-                if (row >= args.oh) continue;  // warp-uniform: rows past the image have nothing to store
+                const int row = t.h0 + 4 * hf + quarter + 8 * (lane / args.cw);
+                const bool p_ok = col < args.ow && row < args.oh;
+                if (!__any_sync(0xffffffffu, p_ok)) continue;  // rows past the image have nothing to store
                 const uint32_t t_base = tmem_base + acc * acc_stride + hf * half_stride + (static_cast<uint32_t>(quarter * 32) << 16);
                 const float* res = args.residual
-                                       ? args.residual + (static_cast<int64_t>(t.n) * args.m + m0) * plane + static_cast<int64_t>(row) * args.ow + t.w0 + lane
+                                       ? args.residual + (static_cast<int64_t>(t.n) * args.m + m0) * plane + static_cast<int64_t>(row) * args.ow + col
                                        : nullptr;
 #pragma unroll 1
                 for (int ua = group; ua < nunits; ua += 2 * NGROUPS) {
@@ -427,7 +434,7 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         r[1][j] = __float_as_uint(__uint_as_float(r[1][j]) + bv[1][j]);
                     }
                     if constexpr (DIRECT) {
-                        float* yo = args.y + (static_cast<int64_t>(t.n) * args.m + m0) * plane + static_cast<int64_t>(row) * args.ow + t.w0 + lane;
+                        float* yo = args.y + (static_cast<int64_t>(t.n) * args.m + m0) * plane + static_cast<int64_t>(row) * args.ow + col;
                         const int na = p_ok ? args.m - (m0 + ca) : 0, nb2 = (p_ok && two) ? args.m - (m0 + cb) : 0;  // channels to store (8 or fewer)
                         float *ya = yo + ca * plane, *yb = yo + cb * plane;
                         if (res) {
@@ -485,17 +492,22 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
 struct IgPlan {
     bool ok;
     int nb, nblocks, ntot, cblocks, rows, rb, wb, pla, stages, raw_bytes, shift_bytes, stage_bytes, smem;
+    int parts, cw, rr;
 };
 
-IgPlan ig_plan(const b200ml_conv_params* p) {
+IgPlan ig_plan(const b200ml_conv_params* p, int64_t ow) {
     IgPlan pl{};
+    // narrow images: two image rows (8 apart) of 16 columns per operand line, i.e. tiles of 16 x 16 instead of 8 x 32
+    pl.parts = ow <= 16 ? 2 : 1;
+    pl.cw = 32 / pl.parts;
+    pl.rr = IG_ROWS * pl.parts + (int)p->kh - 1;
     const int kh = (int)p->kh, kw = (int)p->kw;
     pl.cblocks = (int)ceil_div(p->c, IG_KC);
     pl.rows = pl.cblocks * kw * kh * IG_KC;
     pl.rb = IG_ROWS + kh - 1;
     pl.pla = (int)ceil_div(p->pad_left, 4) * 4;
-    pl.wb = (int)ceil_div(pl.pla - p->pad_left + kw + IG_COLS - 1, 4) * 4;
-    pl.raw_bytes = (int)ceil_div((int64_t)pl.wb * pl.rb * IG_KC * 4, 1024) * 1024;
+    pl.wb = (int)ceil_div(pl.pla - p->pad_left + kw + pl.cw - 1, 4) * 4;
+    pl.raw_bytes = (int)ceil_div((int64_t)pl.wb * pl.rr * IG_KC * 4, 1024) * 1024;
     pl.shift_bytes = 2 * pl.rb * 1024;
     const int fixed = IG_RAW_SLOTS * pl.raw_bytes + IG_EPI_WARPS * IG_OUT_BYTES + IG_BAR_BYTES + 1024 /* alignment */;
     // the widest channel block that leaves three stages (two if there is no other way)
@@ -538,17 +550,17 @@ bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int6
     if (p->pad_top > 8 || p->pad_left > 8 || p->pad_bottom > 8 || p->pad_right > 8) return false;
     if (p->c * p->kh * p->kw < 64 || p->m < 16) return false;                 // short reductions stay on the FP32 pipe
     if (p->n * oh * ow < 4 * 1024) return false;                              // too little work for two launches
-    const IgPlan pl = ig_plan(p);
+    const IgPlan pl = ig_plan(p, ow);
     if (!pl.ok) return false;
     if (2ll * pl.rows * pl.ntot * 4 > ctx->workspace_bytes) return false;     // the split weights live in the context's scratch
-    const int64_t tiles = p->n * pl.nblocks * ceil_div(oh, IG_ROWS) * ceil_div(ow, IG_COLS);
+    const int64_t tiles = p->n * pl.nblocks * ceil_div(oh, IG_ROWS * pl.parts) * ceil_div(ow, pl.cw);
     if (tiles >= (1ll << 31) || p->h >= (1 << 24) || p->w >= (1 << 24) || p->c >= (1 << 24) || p->m >= (1 << 24) || p->n >= (1 << 24)) return false;
     if (p->n * p->c * p->h * p->w * 4 >= (1ll << 40) || p->n * p->m * oh * ow * 4 >= (1ll << 40)) return false;  // tensor-map strides are below 2^40 bytes
     return true;
 }
 
 int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow, cudaStream_t stream) {
-    const IgPlan pl = ig_plan(p);
+    const IgPlan pl = ig_plan(p, ow);
     float* wsplit = static_cast<float*>(ctx->workspace);
     {
         const int64_t total = (int64_t)pl.rows * pl.ntot;
@@ -559,12 +571,13 @@ int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, i
         if (rc) return rc;
     }
     // X and Y go through the TMA unit when their row pitches and bases are multiples of 16 bytes
-    const bool direct_io = p->w % 4 != 0 || ow % 4 != 0 || !aligned16(p->x) || !aligned16(p->y);
+    // (and tiles of one row of 32 columns per operand line: the bulk stores write [8 channels][32 columns] boxes)
+    const bool direct_io = pl.parts != 1 || p->w % 4 != 0 || ow % 4 != 0 || !aligned16(p->x) || !aligned16(p->y);
     CUtensorMap tx, tw, ty;
     if (!direct_io) {
         const cuuint64_t dims[4] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->c, (cuuint64_t)p->n};
         const cuuint64_t strides[3] = {(cuuint64_t)p->w * 4, (cuuint64_t)p->w * p->h * 4, (cuuint64_t)p->w * p->h * p->c * 4};
-        const cuuint32_t box[4] = {(cuuint32_t)pl.wb, (cuuint32_t)pl.rb, IG_KC, 1};
+        const cuuint32_t box[4] = {(cuuint32_t)pl.wb, (cuuint32_t)pl.rr, IG_KC, 1};
         CUresult r = encode_tiled_cached(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "conv k x k: cuTensorMapEncodeTiled(X) failed with CUresult %d", (int)r);
     }
@@ -596,8 +609,11 @@ int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, i
     a.cblocks = pl.cblocks;
     a.nb = pl.nb;
     a.nblocks = pl.nblocks;
-    a.hblocks = (int32_t)ceil_div(oh, IG_ROWS);
-    a.wblocks = (int32_t)ceil_div(ow, IG_COLS);
+    a.parts = pl.parts;
+    a.cw = pl.cw;
+    a.rr = pl.rr;
+    a.hblocks = (int32_t)ceil_div(oh, IG_ROWS * pl.parts);
+    a.wblocks = (int32_t)ceil_div(ow, pl.cw);
     a.num_tiles = (int32_t)(p->n * pl.nblocks * a.hblocks * a.wblocks);
     a.rb = pl.rb;
     a.wb = pl.wb;

@@ -487,14 +487,15 @@ def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
                                                        (2, 8, 32, (64, 64), (7, 7), (3, 3, 3, 3)), (64, 128, 128, (16, 16), (3, 3), (1, 1, 1, 1)),
                                                        (24, 32, 48, (14, 14), (3, 3), (1, 1, 1, 1)), (96, 16, 32, (7, 7), (3, 3), (1, 1, 1, 1)),
                                                        (10, 8, 24, (30, 27), (3, 3), (1, 1, 1, 1)), (6, 8, 16, (32, 32), (3, 3), (0, 0, 0, 0)),
-                                                       (8, 9, 40, (21, 37), (5, 3), (2, 1, 2, 1))])
+                                                       (8, 9, 40, (21, 37), (5, 3), (2, 1, 2, 1)), (32, 16, 24, (20, 18), (3, 3), (0, 0, 0, 0)),
+                                                       (40, 8, 20, (12, 12), (5, 5), (2, 2, 2, 2)), (16, 24, 136, (33, 9), (3, 3), (1, 1, 1, 1))])
 @pytest.mark.parametrize("act", ["", "Relu"])
 def test_conv_kxk_tensor_core(n, cin, cout, hw, k, pads, act, rng):
     """k x k stride-1 convolutions large enough for the implicit-GEMM kernel (3 x TF32; kernel columns as shifted copies
     of the input window, kernel rows as descriptor offsets): ragged tiles in both directions, channel counts that are
     not whole 8- or 32-blocks, more than one block of output channels, asymmetric padding, non-square kernels, bias,
     activation and residual; image widths that are not a multiple of 4 (no tensor map for X and Y: the warps load and
-    store themselves).  Against the oracle at the fp32 tolerance, and against a float64 convolution at a bound
+    store themselves), narrow images (two image rows per operand line).  Against the oracle at the fp32 tolerance, and against a float64 convolution at a bound
     that a single-TF32 product (relative error 5e-4) would break."""
     if os.environ.get("B200ML_CONV_TC", "1") == "0":
         pytest.skip("the tensor-core convolution is switched off")
@@ -584,3 +585,59 @@ def test_kernels_match_reference_source(case):
         else:
             assert_close(got, want, torch.float32, what=f"{case['case']}:{conn}")
     status_ok()
+
+
+def test_python_implementations_through_the_helper_api(rng):
+    """An implementation written with ``python_pure_op_implementation`` (a function over the connectors' tensors) and one
+    that returns a nested SDFG built with ``empty_sdfg_for_node`` (Softplus as Exp -> Add 1 -> Log from this library's own
+    nodes), selected per node, against the oracle."""
+    from daceml_b200 import sdfg as sd
+    from daceml_b200.onnx.forward_implementation_abc import ONNXForward
+    from daceml_b200.onnx.op_implementations.utils import empty_sdfg_for_node, op_implementation, python_pure_op_implementation
+
+    @python_pure_op_implementation(alpha=lambda node: node.alpha)
+    def LeakyRelu(X, Y):
+        K.unary(X, Y, L.UN_LEAKYRELU, alpha)  # noqa: F821 - alpha comes from compute
+
+    @op_implementation(op="Softplus", name="composed")
+    class ComposedSoftplus(ONNXForward):
+        @staticmethod
+        def forward(node, state, sdfg):
+            ns, nst, ins, outs = empty_sdfg_for_node(sdfg, state, node)
+            shape, dtype = ns.arrays["X"].shape, ns.arrays["X"].dtype
+            ns.add_transient("e", shape, dtype)
+            ns.add_transient("s", shape, dtype)
+            ns.add_constant("one", torch.ones((), dtype=dtype))
+            ex, add, log = donnx.ONNXExp("exp"), donnx.ONNXAdd("add"), donnx.ONNXLog("log")
+            nst.add_edge(ins["X"], None, ex, "input", ns.make_array_memlet("X"))
+            nst.add_edge(ex, "output", nst.add_access("e"), None, ns.make_array_memlet("e"))
+            nst.add_edge(nst.add_access("e"), None, add, "A", ns.make_array_memlet("e"))
+            nst.add_edge(nst.add_read("one"), None, add, "B", ns.make_array_memlet("one"))
+            nst.add_edge(add, "C", nst.add_access("s"), None, ns.make_array_memlet("s"))
+            nst.add_edge(nst.add_access("s"), None, log, "input", ns.make_array_memlet("s"))
+            nst.add_edge(log, "output", outs["Y"], None, ns.make_array_memlet("Y"))
+            return ns
+
+    try:
+        x = rng.standard_normal((37, 50)).astype(np.float32)
+        for op_cls, impl, attrs, want in ((donnx.ONNXLeakyRelu, "pure", dict(alpha=0.2), np.where(x > 0, x, np.float32(0.2) * x)),
+                                          (donnx.ONNXSoftplus, "composed", {}, ops.softplus(x))):
+            g = sd.SDFG("helper_" + impl)
+            g.add_array("x", x.shape, torch.float32)
+            g.add_array("y", x.shape, torch.float32)
+            st = g.add_state()
+            node = op_cls("n0", **attrs)
+            node.implementation = impl
+            st.add_edge(st.add_read("x"), None, node, "X", g.make_array_memlet("x"))
+            st.add_edge(node, "Y", st.add_write("y"), None, g.make_array_memlet("y"))
+            comp = g.compile()
+            y = empty(x.shape, torch.float32)
+            comp(x=dev(x), y=y)
+            assert_close(y, want, what=impl)
+            assert len(comp.kernel_names()) == (1 if impl == "pure" else 3)
+        status_ok()
+    finally:
+        donnx.ONNXLeakyRelu.implementations.pop("pure", None)
+        donnx.ONNXSoftplus.implementations.pop("composed", None)
+        ONNXForward.unregister(LeakyRelu)
+        ONNXForward.unregister(ComposedSoftplus)
