@@ -179,6 +179,10 @@ def run_hbm_kernels(args, emit=True):
                   lambda i: K.layernorm(xs[i], ys[i], gamma=gamma, beta=beta, residual=rs[i], bias=bias_h, eps=1e-12)))
     cases.append(("binary_fast_kernel", "residual add [4096, 1024] fp16", n, 3 * T * HIDDEN * 2,
                   lambda i: K.binary(xs[i], rs[i], ys[i], L.BIN_ADD)))
+    # the floor at this size: a plain copy that moves the same 25 MB (12.6 MB in, 12.6 MB out) through the same launch path
+    cx, cy = [rnd(T * 3 // 2, HIDDEN) for _ in range(n)], [torch.empty(T * 3 // 2, HIDDEN, dtype=torch.float16, device=dev) for _ in range(n)]
+    cases.append(("unary_kernel", "plain copy of [6144, 1024] fp16: what a 25 MB launch can reach", n, 2 * (T * 3 // 2) * HIDDEN * 2,
+                  lambda i: K.unary(cx[i], cy[i], L.UN_COPY)))
     n = 6  # 6 x 67 MB
     hs, ho = [rnd(T, FFN) for _ in range(n)], [torch.empty(T, FFN, dtype=torch.float16, device=dev) for _ in range(n)]
     cases.append(("bias_act_kernel", "bias + GELU(erf) [4096, 4096] fp16", n, 2 * T * FFN * 2,
@@ -668,6 +672,18 @@ def main():
     if world > 1:
         do_gather()  # NCCL: creates the communicator before any capture
         barrier()
+        if peer is not None:
+            # the peer kernel's first result against NCCL's, on every rank, before it is trusted with the timed region
+            ref = torch.empty_like(gathered)
+            dist.all_gather_into_tensor(ref, final_buf)
+            torch.cuda.synchronize()
+            good = int(torch.equal(ref, peer.gathered) and L.get_context(dev).device_status() == 0)
+            flag = torch.tensor([good], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if not int(flag):
+                sys.stderr.write("rank %d: peer all-gather disagreed with NCCL or left a status; using NCCL\n" % rank)
+                peer, gathered = None, ref
+            barrier()
     warm_graph = capture(0, args.warmup)
     gather_in_graph = False
     if world > 1:
