@@ -555,6 +555,60 @@ def run_profile_kernels(args):
     assert L.get_context(dev).device_status() == 0
 
 
+def run_gather_only(args):
+    """Under torchrun: the final all-gather alone (8.4 MB per rank, the layer's output), this library's peer-store kernel
+    and NCCL's collective, each as a CUDA graph of 20 launches timed with CUDA events, max over ranks.  Rank 0 prints one
+    JSON line."""
+    import torch.distributed as dist
+    from daceml_b200 import distributed as D
+    rank, world, local_rank = D.init_from_env()
+    if world < 2:
+        raise SystemExit("--gather-only needs torchrun with two or more ranks")
+    dev = torch.device("cuda", local_rank)
+    y = torch.randn(BATCH, SEQ, HIDDEN, device=dev).half()
+    ref = torch.empty(world * BATCH, SEQ, HIDDEN, dtype=torch.float16, device=dev)
+    peer = D.PeerGather((BATCH, SEQ, HIDDEN), torch.float16, dev, rank, world)
+
+    def timeit(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                for _ in range(n):
+                    fn()
+            g.replay()
+            side.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            side.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del g
+        return float(t)
+
+    t_peer = timeit(lambda: peer.gather(y))
+    t_nccl = timeit(lambda: dist.all_gather_into_tensor(ref, y))
+    same = bool(torch.equal(peer.gathered, ref))
+    if rank == 0:
+        out_bytes = y.numel() * 2 * (world - 1)
+        print(json.dumps({"workload": "all-gather of [8,512,1024] fp16 per rank", "n_gpus": world, "bytes_out_per_gpu": out_bytes,
+                          "peer_store_kernel_us": round(t_peer, 2), "peer_store_gbs_out_per_gpu": round(out_bytes / t_peer / 1e3, 1),
+                          "nccl_all_gather_us": round(t_nccl, 2), "same_result": same}), flush=True)
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    peer.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -575,11 +629,15 @@ def main():
     ap.add_argument("--profile-kernels", action="store_true",
                     help="instead of the layer: launch every kernel family twice on operands larger than L2, nothing timed "
                          "(the workload the ncu summaries under profiles/ were taken on)")
+    ap.add_argument("--gather-only", action="store_true",
+                    help="under torchrun: time the final all-gather alone, this library's peer-store kernel against NCCL")
     ap.add_argument("--via-module", action="store_true",
                     help="instead of the hand-built layer graphs: 24 transformers BertLayer modules wrapped in one DaceModule "
                          "(export, import, fusion), timed the same way; one JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.gather_only:
+        return run_gather_only(args)
     if args.profile_kernels:
         run_profile_kernels(args)
         return
@@ -826,7 +884,7 @@ def main():
                                "frac_sustained": step_tf / pk["tf_sustained"], "flops_per_step": LAYER_FLOPS}}
 
     # ---- end to end through the public API with host buffers: H2D of the step's input, layer, D2H of its output ----
-    n_e2e = max(24, min(args.steps, 96))
+    n_e2e = 240  # long enough (about 50 ms) for the fill and drain of the three-deep pipeline (about 0.5 ms) not to count
     depth = 3
     hin = [torch.randn(BATCH, SEQ, HIDDEN).half().pin_memory() for _ in range(depth)]
     hout = [torch.empty(BATCH, SEQ, HIDDEN, dtype=torch.float16).pin_memory() for _ in range(depth)]

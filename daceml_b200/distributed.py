@@ -129,27 +129,44 @@ class PeerGather:
         self.storage = torch.zeros(max(total + self.FLAG_BYTES, 2 << 20), dtype=torch.uint8, device=device)
         self.gathered = self.storage[:total].view(dtype).view((world * int(shape_per_rank[0]), ) + tuple(shape_per_rank[1:]))
         torch.cuda.synchronize(device)
-        handle = (ctypes.c_ubyte * 64)()
-        offset = ctypes.c_int64(0)
-        L.check(self.ctx.lib.b200ml_ipc_export(self.ctx.handle, ctypes.c_void_p(self.storage.data_ptr()), handle, ctypes.byref(offset)))
-        mine = (bytes(handle), int(offset.value))
+        # every step below is collective: a rank that fails still takes part in the exchanges, and all ranks raise together
+        mine = None
+        try:
+            handle = (ctypes.c_ubyte * 64)()
+            offset = ctypes.c_int64(0)
+            L.check(self.ctx.lib.b200ml_ipc_export(self.ctx.handle, ctypes.c_void_p(self.storage.data_ptr()), handle, ctypes.byref(offset)))
+            mine = (bytes(handle), int(offset.value))
+        except Exception:  # noqa: BLE001 - every rank learns of it from the None this rank sends
+            mine = None
         everyone = [None] * world
         dist.all_gather_object(everyone, mine, group=group)
         self._opened = []
         self.peers = L.PeerGroup()
         self.peers.rank, self.peers.world = rank, world
-        for r in range(world):
-            if r == rank:
-                base = self.storage.data_ptr()
-            else:
-                h = (ctypes.c_ubyte * 64).from_buffer_copy(everyone[r][0])
-                ptr = ctypes.c_void_p()
-                L.check(self.ctx.lib.b200ml_ipc_open(self.ctx.handle, h, everyone[r][1], ctypes.byref(ptr)))
-                self._opened.append((ptr.value, everyone[r][1]))
-                base = ptr.value
-            self.peers.gathered[r] = base
-            self.peers.flags[r] = base + total
-        dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores into one
+        problem = None
+        if any(e is None for e in everyone):
+            problem = "rank(s) {} could not export their buffer".format([r for r, e in enumerate(everyone) if e is None])
+        else:
+            try:
+                for r in range(world):
+                    if r == rank:
+                        base = self.storage.data_ptr()
+                    else:
+                        h = (ctypes.c_ubyte * 64).from_buffer_copy(everyone[r][0])
+                        ptr = ctypes.c_void_p()
+                        L.check(self.ctx.lib.b200ml_ipc_open(self.ctx.handle, h, everyone[r][1], ctypes.byref(ptr)))
+                        self._opened.append((ptr.value, everyone[r][1]))
+                        base = ptr.value
+                    self.peers.gathered[r] = base
+                    self.peers.flags[r] = base + total
+            except Exception as e:  # noqa: BLE001
+                problem = "rank {}: {}".format(rank, e)
+        # also the barrier behind the mapping: every rank has mapped every buffer before anyone stores into one
+        problems = [None] * world
+        dist.all_gather_object(problems, problem, group=group)
+        if any(problems):
+            self.close()
+            raise RuntimeError("peer all-gather not available: " + "; ".join(p for p in problems if p))
 
     def gather(self, y_local):
         import ctypes
