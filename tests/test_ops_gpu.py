@@ -488,7 +488,8 @@ def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
                                                        (24, 32, 48, (14, 14), (3, 3), (1, 1, 1, 1)), (96, 16, 32, (7, 7), (3, 3), (1, 1, 1, 1)),
                                                        (10, 8, 24, (30, 27), (3, 3), (1, 1, 1, 1)), (6, 8, 16, (32, 32), (3, 3), (0, 0, 0, 0)),
                                                        (8, 9, 40, (21, 37), (5, 3), (2, 1, 2, 1)), (32, 16, 24, (20, 18), (3, 3), (0, 0, 0, 0)),
-                                                       (40, 8, 20, (12, 12), (5, 5), (2, 2, 2, 2)), (16, 24, 136, (33, 9), (3, 3), (1, 1, 1, 1))])
+                                                       (40, 8, 20, (12, 12), (5, 5), (2, 2, 2, 2)), (16, 24, 136, (33, 9), (3, 3), (1, 1, 1, 1)),
+                                                       (16, 16, 32, (24, 20), (3, 3), (1, 1, 1, 1)), (12, 8, 16, (20, 24), (3, 3), (0, 0, 0, 0))])
 @pytest.mark.parametrize("act", ["", "Relu"])
 def test_conv_kxk_tensor_core(n, cin, cout, hw, k, pads, act, rng):
     """k x k stride-1 convolutions large enough for the implicit-GEMM kernel (3 x TF32; kernel columns as shifted copies
