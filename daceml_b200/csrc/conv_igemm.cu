@@ -1,6 +1,6 @@
-// k x k stride-1 convolution (NCHW, fp32, group 1) as an implicit GEMM on the tensor cores, fp32-grade accuracy
-// ("3 x TF32"):
-//     Y[n, m, h, w] = act(B[m] + sum_{c, i, j} W[m, c, i, j] * X[n, c, h - pad_top + i, w - pad_left + j]) + R[n, m, h, w]
+// k x k convolution with stride 1 or 2 (NCHW, fp32, group 1) as an implicit GEMM on the tensor cores, fp32-grade
+// accuracy ("3 x TF32"):
+//     Y[n, m, h, w] = act(B[m] + sum_{c, i, j} W[m, c, i, j] * X[n, c, sh h - pad_top + i, sw w - pad_left + j]) + R[n, m, h, w]
 // (the reference's routes: the loop nest of daceml/onnx/op_implementations/img_op_implementations.py:217-288 and cuDNN,
 // cudnn_implementations.py:123-410).
 //
@@ -28,6 +28,8 @@
 // block ahead, and the epilogue warps store Y themselves.
 // Narrow images (output width <= 16, always DIRECT): an operand line holds two image rows, 8 apart, of 16 columns, so a
 // tile is 16 rows x 16 columns; kernel row i is still "i lines further down" for both rows of a line.
+// Stride (sh, sw): the split warps pick every sw-th column of the window when they write a line, and output row r of a
+// half tile, kernel row i, is line sh r + i - the operand's atoms are sh lines apart instead of one.
 #include "conv_tc.cuh"
 
 namespace b200ml {
@@ -53,6 +55,7 @@ struct IgArgs {
     int32_t parts, cw;                    // a 128-byte operand line = `parts` image rows (8 apart) of `cw` = 32 / parts columns
     int32_t rb, rr, wb, xoff;             // window: operand lines, raw rows, raw columns, column of kernel column 0 for output column 0
     int32_t pla, pad_top;                 // the window starts pla columns left of the tile and pad_top rows above it
+    int32_t sh, sw;                       // strides (1 or 2): output row r reads lines sh r + i, output column w raw column sw w + j
     int32_t stages, raw_bytes, stage_bytes, shift_bytes;
     int32_t act;
     int32_t direct_io, h, w;  // direct_io: X and Y cannot be described to the TMA unit (row pitch or base not a multiple of
@@ -108,14 +111,14 @@ __device__ __forceinline__ IgTile ig_tile(const IgArgs& a, int tile) {
 __device__ __forceinline__ void ig_prefetch_window(uint32_t dst, const IgArgs& a, const IgTile& t, int cb, int ch, int lane) {
     const int c = cb * IG_KC + ch;
     const float* xc = a.x + (static_cast<int64_t>(t.n) * a.c + (c < a.c ? c : 0)) * a.h * a.w;
-    const int gy0 = t.h0 - a.pad_top, gx0 = t.w0 - a.pla + lane;
+    const int gy0 = t.h0 * a.sh - a.pad_top, gx0 = t.w0 * a.sw - a.pla;
     for (int r = 0; r < a.rr; ++r) {
         const int gy = gy0 + r;
         const bool r_ok = c < a.c && gy >= 0 && gy < a.h;
 #pragma unroll
-        for (int hc = 0; hc < 2; ++hc) {
-            const int gx = gx0 + 32 * hc;
-            if (lane + 32 * hc < a.wb) {
+        for (int hc = 0; hc < 3; ++hc) {  // the window is at most 96 columns wide (stride 2: 62 + kernel + alignment)
+            const int col = lane + 32 * hc, gx = gx0 + col;
+            if (col < a.wb) {
                 const bool ok = r_ok && gx >= 0 && gx < a.w;
                 const float* src = ok ? xc + static_cast<int64_t>(gy) * a.w + gx : a.x;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + (r * a.wb + 32 * hc) * 4), "l"(src), "r"(ok ? 4 : 0) : "memory");
@@ -236,8 +239,8 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         }
                         ptx::mbar_expect_tx(&raw_full[slot], static_cast<uint32_t>(args.wb * args.rr * IG_KC * 4));
                         // x is a multiple of 4 elements (16 bytes); rows and columns outside the image arrive as zeros
-                        ptx::tma_load_4d(raw_base + slot * args.raw_bytes, &tmap_x, &raw_full[slot], t.w0 - args.pla,
-                                         t.h0 - args.pad_top, cb * IG_KC, t.n);
+                        ptx::tma_load_4d(raw_base + slot * args.raw_bytes, &tmap_x, &raw_full[slot], t.w0 * args.sw - args.pla,
+                                         t.h0 * args.sh - args.pad_top, cb * IG_KC, t.n);
                         if (++slot == IG_RAW_SLOTS) {
                             slot = 0;
                             slot_phase ^= 1;
@@ -268,7 +271,7 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         // ------------------------------ MMA issuer ------------------------------
         if (ptx::elect_one()) {
             const uint32_t idesc = pw_idesc(static_cast<uint32_t>(args.nb), 1u);
-            const uint64_t d_x_first = make_smem_desc_sw128_base32(ptx::smem_u32(smem), 1024, 512);
+            const uint64_t d_x_first = make_smem_desc_sw128_base32(ptx::smem_u32(smem), args.sh * 1024, 512);  // output rows are sh lines apart
             const uint64_t d_w_first = make_smem_desc_sw128_base32(ptx::smem_u32(smem) + args.shift_bytes, args.kh * 1024, 512);
             int stage = 0;
             uint32_t phase = 0;
@@ -300,7 +303,7 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         for (int hf = 0; hf < 2; ++hf) {
                             // X: MN-major, one atom per image row (1 KB apart: two 4-channel groups of 512 bytes); kernel
                             // row ki of half hf starts at window row 4 hf + ki
-                            const uint64_t d_xh = d_xh0 + static_cast<uint32_t>((4 * hf + ki) * 64), d_xl = d_xh + static_cast<uint32_t>(x_part_bytes >> 4);
+                            const uint64_t d_xh = d_xh0 + static_cast<uint32_t>((4 * hf * args.sh + ki) * 64), d_xl = d_xh + static_cast<uint32_t>(x_part_bytes >> 4);
                             const uint32_t d = d_tmem + hf * half_stride;
                             pw_mma(d, d_xl, d_wh, idesc, (st | ki) != 0 ? 1u : 0u);  // the two small terms first
                             pw_mma(d, d_xh, d_wl, idesc, 1u);
@@ -347,9 +350,9 @@ conv_igemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                         break;
                     }
                 }
-                // lane = (part, column): part j of operand line L is raw row L + 8 j
+                // lane = (part, column): part j of operand line L is raw row L + 8 sh j; column w reads raw column sw w + kj
                 const uint32_t src0 = ptx::smem_u32(raw_base + slot * args.raw_bytes) +
-                                      ((ch * args.rr + 8 * (lane / args.cw)) * args.wb + args.xoff + lane % args.cw) * 4;
+                                      ((ch * args.rr + 8 * args.sh * (lane / args.cw)) * args.wb + args.xoff + args.sw * (lane % args.cw)) * 4;
                 for (int kj = 0; kj < args.kw; ++kj) {
                     ok = __all_sync(0xffffffffu, ptx::mbar_wait_suspend(&empty[stage], phase ^ 1));
                     if (!ok) {
@@ -500,13 +503,14 @@ IgPlan ig_plan(const b200ml_conv_params* p, int64_t ow) {
     // narrow images: two image rows (8 apart) of 16 columns per operand line, i.e. tiles of 16 x 16 instead of 8 x 32
     pl.parts = ow <= 16 ? 2 : 1;
     pl.cw = 32 / pl.parts;
-    pl.rr = IG_ROWS * pl.parts + (int)p->kh - 1;
+    const int sh = (int)p->stride_h, sw = (int)p->stride_w;
+    pl.rr = (IG_ROWS * pl.parts - 1) * sh + (int)p->kh;
     const int kh = (int)p->kh, kw = (int)p->kw;
     pl.cblocks = (int)ceil_div(p->c, IG_KC);
     pl.rows = pl.cblocks * kw * kh * IG_KC;
-    pl.rb = IG_ROWS + kh - 1;
+    pl.rb = (IG_ROWS - 1) * sh + kh;  // operand lines: output row r of a half, kernel row i -> line sh r + i
     pl.pla = (int)ceil_div(p->pad_left, 4) * 4;
-    pl.wb = (int)ceil_div(pl.pla - p->pad_left + kw + pl.cw - 1, 4) * 4;
+    pl.wb = (int)ceil_div(pl.pla - p->pad_left + kw + (pl.cw - 1) * sw, 4) * 4;
     pl.raw_bytes = (int)ceil_div((int64_t)pl.wb * pl.rr * IG_KC * 4, 1024) * 1024;
     pl.shift_bytes = 2 * pl.rb * 1024;
     const int fixed = IG_RAW_SLOTS * pl.raw_bytes + IG_EPI_WARPS * IG_OUT_BYTES + IG_BAR_BYTES + 1024 /* alignment */;
@@ -545,8 +549,9 @@ bool conv_tc_enabled() {
 bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow) {
     if (!conv_tc_enabled() || p->dtype != B200ML_F32 || !ctx->encode_tiled) return false;
     if (p->group != 1 || p->gate) return false;
-    if (p->kh * p->kw < 2 || p->kh > 7 || p->kw > 7) return false;
-    if (p->stride_h != 1 || p->stride_w != 1 || p->dil_h != 1 || p->dil_w != 1) return false;
+    if (p->kh > 7 || p->kw > 7) return false;
+    if (p->kh * p->kw < 2 && p->stride_h == 1 && p->stride_w == 1) return false;  // the 1x1 kernel's case
+    if (p->stride_h > 2 || p->stride_w > 2 || p->dil_h != 1 || p->dil_w != 1) return false;
     if (p->pad_top > 8 || p->pad_left > 8 || p->pad_bottom > 8 || p->pad_right > 8) return false;
     if (p->c * p->kh * p->kw < 64 || p->m < 16) return false;                 // short reductions stay on the FP32 pipe
     if (p->n * oh * ow < 4 * 1024) return false;                              // too little work for two launches
@@ -620,6 +625,8 @@ int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, i
     a.pla = pl.pla;
     a.xoff = pl.pla - (int32_t)p->pad_left;
     a.pad_top = (int32_t)p->pad_top;
+    a.sh = (int32_t)p->stride_h;
+    a.sw = (int32_t)p->stride_w;
     a.stages = pl.stages;
     a.raw_bytes = pl.raw_bytes;
     a.stage_bytes = pl.stage_bytes;

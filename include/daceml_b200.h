@@ -323,9 +323,9 @@ typedef struct {
 
 /* ONNX Conv (cross-correlation, NCHW).  Replaces PureConv2D (img_op_implementations.py:164-330)
  * for stride 1 / no pad / group 1, and CudnnConvolution (cudnn_implementations.py:123-410) for
- * strided, padded and grouped convolutions.  fp32 stride-1 group-1 convolutions run on the tensor
- * cores at fp32 accuracy (three TF32 products per term): 1x1 kernels with 8..256 output channels,
- * and k x k kernels up to 7 x 7 whose reduction has 64 terms or more as an implicit GEMM; both use
+ * strided, padded and grouped convolutions.  fp32 group-1 convolutions run on the tensor cores at
+ * fp32 accuracy (three TF32 products per term): stride-1 1x1 kernels with 8..256 output channels,
+ * and kernels up to 7 x 7 with stride 1 or 2 whose reduction has 64 terms or more as an implicit GEMM; both use
  * the context's scratch for the split weights, so calls sharing a context must not overlap. */
 int b200ml_conv2d(b200ml_ctx* ctx, const b200ml_conv_params* p, b200ml_stream stream);
 

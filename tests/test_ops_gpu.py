@@ -489,31 +489,36 @@ def test_conv_pointwise_tensor_core(n, cin, cout, hw, act, rng):
                                                        (10, 8, 24, (30, 27), (3, 3), (1, 1, 1, 1)), (6, 8, 16, (32, 32), (3, 3), (0, 0, 0, 0)),
                                                        (8, 9, 40, (21, 37), (5, 3), (2, 1, 2, 1)), (32, 16, 24, (20, 18), (3, 3), (0, 0, 0, 0)),
                                                        (40, 8, 20, (12, 12), (5, 5), (2, 2, 2, 2)), (16, 24, 136, (33, 9), (3, 3), (1, 1, 1, 1)),
-                                                       (16, 16, 32, (24, 20), (3, 3), (1, 1, 1, 1)), (12, 8, 16, (20, 24), (3, 3), (0, 0, 0, 0))])
+                                                       (16, 16, 32, (24, 20), (3, 3), (1, 1, 1, 1)), (12, 8, 16, (20, 24), (3, 3), (0, 0, 0, 0)),
+                                                       (8, 32, 64, (56, 56), (3, 3), (1, 1, 1, 1, 2, 2)), (24, 16, 32, (30, 30), (3, 3), (0, 0, 0, 0, 2, 2)),
+                                                       (6, 16, 24, (40, 48), (3, 3), (1, 1, 1, 1, 2, 1)), (8, 64, 96, (48, 64), (1, 1), (0, 0, 0, 0, 2, 2)),
+                                                       (8, 12, 20, (41, 52), (5, 5), (2, 2, 2, 2, 1, 2)), (6, 8, 16, (64, 64), (5, 5), (2, 2, 2, 2, 2, 2))])
 @pytest.mark.parametrize("act", ["", "Relu"])
 def test_conv_kxk_tensor_core(n, cin, cout, hw, k, pads, act, rng):
     """k x k stride-1 convolutions large enough for the implicit-GEMM kernel (3 x TF32; kernel columns as shifted copies
     of the input window, kernel rows as descriptor offsets): ragged tiles in both directions, channel counts that are
     not whole 8- or 32-blocks, more than one block of output channels, asymmetric padding, non-square kernels, bias,
-    activation and residual; image widths that are not a multiple of 4 (no tensor map for X and Y: the warps load and
+    activation and residual, strides of 2 (also mixed, and a strided 1x1); image widths that are not a multiple of 4 (no tensor map for X and Y: the warps load and
     store themselves), narrow images (two image rows per operand line).  Against the oracle at the fp32 tolerance, and against a float64 convolution at a bound
     that a single-TF32 product (relative error 5e-4) would break."""
     if os.environ.get("B200ML_CONV_TC", "1") == "0":
         pytest.skip("the tensor-core convolution is switched off")
+    strides = tuple(pads[4:]) or (1, 1)  # a six-entry pads tuple carries the strides behind the four pads
+    pads = tuple(pads[:4])
     x = rng.standard_normal((n, cin) + hw).astype(np.float32)
     w = (rng.standard_normal((cout, cin) + k) * 0.1).astype(np.float32)
     b = (rng.standard_normal(cout) * 3).astype(np.float32)
-    oracle = ops.conv2d(x, w, b, pads=pads)
+    oracle = ops.conv2d(x, w, b, strides=strides, pads=pads)
     res = rng.standard_normal(oracle.shape).astype(np.float32)
     guard = torch.full((oracle.size + 4096, ), 7.0, dtype=torch.float32, device="cuda")
     y = guard[:oracle.size].view(oracle.shape)
     before = L.launch_count()
-    donnx.ONNXFusedConv(X=dev(x), W=dev(w), B=dev(b), Residual=dev(res), Y=y, pads=list(pads), activation=act)
+    donnx.ONNXFusedConv(X=dev(x), W=dev(w), B=dev(b), Residual=dev(res), Y=y, pads=list(pads), strides=list(strides), activation=act)
     assert L.launch_count() - before == 2, "expected the weight split and the implicit-GEMM kernel"
     pt, pl, pb, pr = pads
     xp = torch.nn.functional.pad(torch.from_numpy(x).double(), (pl, pr, pt, pb))
-    pre = torch.nn.functional.conv2d(xp, torch.from_numpy(w).double(), torch.from_numpy(b).double()).numpy()
-    mag = torch.nn.functional.conv2d(xp.abs(), torch.from_numpy(w).double().abs(), torch.from_numpy(b).double().abs()).numpy() + np.abs(res)
+    pre = torch.nn.functional.conv2d(xp, torch.from_numpy(w).double(), torch.from_numpy(b).double(), stride=strides).numpy()
+    mag = torch.nn.functional.conv2d(xp.abs(), torch.from_numpy(w).double().abs(), torch.from_numpy(b).double().abs(), stride=strides).numpy() + np.abs(res)
     post = {"": pre, "Relu": np.maximum(pre, 0)}[act] + res
     err = np.abs(y.double().cpu().numpy() - post)
     assert (err <= 4e-6 * mag + 1e-6).all(), "3 x TF32 accuracy lost: worst error / magnitude %.3g" % float((err / (mag + 1e-9)).max())
