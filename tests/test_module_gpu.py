@@ -282,3 +282,47 @@ def test_batchnorm_inference_modules(dtype):
     with torch.no_grad():
         assert_close(y, net.float()(x.float()), dtype=dtype, what="Conv + BatchNorm + Relu")
     status_ok()
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_resnet_basic_block_module(stride):
+    """A ResNet basic block in eval mode through ``DaceModule``: Conv 3x3 + BatchNorm + ReLU, Conv 3x3 + BatchNorm, the
+    shortcut (identity, or a strided 1x1 Conv + BatchNorm) added, ReLU.  The 3x3 convolutions (and the strided 1x1) take
+    the implicit-GEMM tensor-core kernel; against PyTorch in full fp32."""
+    class BasicBlock(nn.Module):
+        def __init__(self, cin, cout, stride):
+            super().__init__()
+            self.conv1, self.bn1 = nn.Conv2d(cin, cout, 3, stride=stride, padding=1, bias=False), nn.BatchNorm2d(cout)
+            self.conv2, self.bn2 = nn.Conv2d(cout, cout, 3, padding=1, bias=False), nn.BatchNorm2d(cout)
+            self.down = None
+            if stride != 1 or cin != cout:
+                self.down = nn.Sequential(nn.Conv2d(cin, cout, 1, stride=stride, bias=False), nn.BatchNorm2d(cout))
+
+        def forward(self, x):
+            y = torch.relu(self.bn1(self.conv1(x)))
+            y = self.bn2(self.conv2(y))
+            return torch.relu(y + (x if self.down is None else self.down(x)))
+
+    torch.manual_seed(0)
+    net = BasicBlock(64, 64 if stride == 1 else 128, stride).eval()
+    for m in net.modules():
+        if isinstance(m, nn.BatchNorm2d):
+            m.running_mean.normal_(0.0, 0.1), m.running_var.uniform_(0.5, 1.5), m.weight.data.uniform_(0.5, 1.5), m.bias.data.normal_(0.0, 0.1)
+    x = torch.randn(8, 64, 56, 56)
+    module = DaceModule(copy.deepcopy(net).cuda())
+    before = L.launch_count()
+    y = module(x.cuda())
+    torch.cuda.synchronize()
+    names = module.compiled_function.kernel_names()
+    assert names.count("conv2d") == (2 if stride == 1 else 3), names
+    # every convolution of the block ran as weight split + implicit GEMM: two launches each
+    assert L.launch_count() - before >= 2 * names.count("conv2d")
+    was = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        with torch.no_grad():
+            ref = net(x)
+    finally:
+        torch.backends.cudnn.allow_tf32 = was
+    assert_close(y, ref, what="ResNet basic block, stride %d" % stride, rtol=2e-4, atol=2e-4)
+    status_ok()
