@@ -123,7 +123,7 @@ int peer_ctas() {
     static const int n = [] {
         const char* e = getenv("B200ML_PEER_CTAS");
         const int v = e ? atoi(e) : 0;
-        return v > 0 && v <= 1024 ? v : 64;
+        return v > 0 && v <= 1024 ? v : 48;
     }();
     return n;
 }
