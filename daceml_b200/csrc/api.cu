@@ -55,6 +55,8 @@ int transpose(const b200ml_ctx* ctx, int elem_bytes, const void* x, void* y, int
 int cast(const b200ml_ctx* ctx, int src, int dst, const void* x, void* y, int64_t n, cudaStream_t s);
 int cast_any(const b200ml_ctx* ctx, int src, int dst, const void* x, void* y, int64_t n, cudaStream_t s);
 int conv2d(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t s);
+int64_t conv_prepack_bytes(const b200ml_ctx* ctx, const b200ml_conv_params* p);
+int conv_prepack(const b200ml_ctx* ctx, const b200ml_conv_params* p, void* packed, cudaStream_t s);
 int se_gate(const b200ml_ctx* ctx, int dtype, const void* pooled, const void* w1, const void* b1, const void* w2,
             const void* b2, void* gate, int64_t n, int64_t c, int64_t r, cudaStream_t s);
 int attention_f16(const b200ml_ctx* ctx, const b200ml_attention_params* p, cudaStream_t s);
@@ -341,6 +343,17 @@ int b200ml_cast(b200ml_ctx* ctx, int32_t src_dtype, int32_t dst_dtype, const voi
     if (dtype_ok(src_dtype) && dtype_ok(dst_dtype))
         return cast(ctx, src_dtype, dst_dtype, x, y, n, static_cast<cudaStream_t>(stream));
     return cast_any(ctx, src_dtype, dst_dtype, x, y, n, static_cast<cudaStream_t>(stream));
+}
+
+int64_t b200ml_conv_prepack_bytes(b200ml_ctx* ctx, const b200ml_conv_params* p) {
+    if (ctx == nullptr || p == nullptr || p->dtype != B200ML_F32) return 0;
+    return conv_prepack_bytes(ctx, p);
+}
+
+int b200ml_conv_prepack(b200ml_ctx* ctx, const b200ml_conv_params* p, void* packed, b200ml_stream stream) {
+    CTX_CHECK(ctx);
+    B200ML_REQUIRE(p != nullptr, "conv_prepack: null parameter block");
+    return conv_prepack(ctx, p, packed, static_cast<cudaStream_t>(stream));
 }
 
 int b200ml_conv2d(b200ml_ctx* ctx, const b200ml_conv_params* p, b200ml_stream stream) {

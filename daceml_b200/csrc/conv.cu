@@ -17,6 +17,10 @@ bool conv1x1_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_conv_params
 int conv1x1_tensor_core(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t stream);
 bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow);
 int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow, cudaStream_t stream);
+int64_t conv1x1_pack_bytes(const b200ml_conv_params* p);
+int conv1x1_pack(const b200ml_ctx* ctx, const b200ml_conv_params* p, void* dst, cudaStream_t stream);
+int64_t conv_igemm_pack_bytes(const b200ml_conv_params* p, int64_t ow);
+int conv_igemm_pack(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t ow, void* dst, cudaStream_t stream);
 
 namespace {
 
@@ -654,6 +658,37 @@ int conv2d(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t s) {
         return reduce(ctx, p->dtype, B200ML_RED_MEAN, p->y, p->pool_sum, p->n * p->m, oh * ow, 1, s);
     }
     return B200ML_OK;
+}
+
+// Which tensor-core kernel (if any) takes this convolution: 1 = the 1x1 kernel, 2 = the implicit GEMM, 0 = neither.
+static int conv_tensor_core_kind(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t* ow_out) {
+    if (p->group < 1 || p->stride_h < 1 || p->stride_w < 1 || p->dil_h < 1 || p->dil_w < 1 || p->kh < 1 || p->kw < 1) return 0;
+    const int64_t eh = p->h + p->pad_top + p->pad_bottom - p->dil_h * (p->kh - 1) - 1;
+    const int64_t ew = p->w + p->pad_left + p->pad_right - p->dil_w * (p->kw - 1) - 1;
+    if (eh < 0 || ew < 0 || p->n == 0 || p->m == 0) return 0;
+    const int64_t oh = eh / p->stride_h + 1, ow = ew / p->stride_w + 1;
+    *ow_out = ow;
+    // the pointers only enter through their alignment, and prepacking is asked with the tensors the calls will use or none
+    b200ml_conv_params q = *p;
+    if (!q.x) q.x = reinterpret_cast<const void*>(uintptr_t(256));
+    if (!q.y) q.y = reinterpret_cast<void*>(uintptr_t(256));
+    if (conv1x1_tensor_core_applies(ctx, &q)) return 1;
+    if (conv_igemm_applies(ctx, &q, oh, ow)) return 2;
+    return 0;
+}
+
+int64_t conv_prepack_bytes(const b200ml_ctx* ctx, const b200ml_conv_params* p) {
+    int64_t ow = 0;
+    const int kind = conv_tensor_core_kind(ctx, p, &ow);
+    return kind == 1 ? conv1x1_pack_bytes(p) : (kind == 2 ? conv_igemm_pack_bytes(p, ow) : 0);
+}
+
+int conv_prepack(const b200ml_ctx* ctx, const b200ml_conv_params* p, void* packed, cudaStream_t s) {
+    int64_t ow = 0;
+    const int kind = conv_tensor_core_kind(ctx, p, &ow);
+    B200ML_REQUIRE(kind != 0, "conv_prepack: this convolution takes its weights as they are (b200ml_conv_prepack_bytes returns 0)");
+    B200ML_REQUIRE(packed && aligned16(packed) && p->weight, "conv_prepack: the packed buffer must be 16-byte aligned device memory, the weights given");
+    return kind == 1 ? conv1x1_pack(ctx, p, packed, s) : conv_igemm_pack(ctx, p, ow, packed, s);
 }
 
 int se_gate(const b200ml_ctx*, int dtype, const void* pooled, const void* w1, const void* b1, const void* w2,

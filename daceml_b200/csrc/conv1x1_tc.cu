@@ -388,14 +388,30 @@ bool conv1x1_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_conv_params
     return true;
 }
 
+// Bytes of the split weights (hi and lo of the padded [npad][kpad] matrix with the bias column).
+int64_t conv1x1_pack_bytes(const b200ml_conv_params* p) {
+    const int64_t npad = ceil_div(p->m, 16) * 16, kpad = ceil_div(p->c + 1, PW_KB) * PW_KB;
+    return 2 * npad * kpad * 4;
+}
+
+int conv1x1_pack(const b200ml_ctx*, const b200ml_conv_params* p, void* dst, cudaStream_t stream) {
+    const int npad = (int)(ceil_div(p->m, 16) * 16), kpad = (int)(ceil_div(p->c + 1, PW_KB) * PW_KB);
+    pw_split_weights_kernel<<<(unsigned)ceil_div((int64_t)npad * kpad, 256), 256, 0, stream>>>(
+        static_cast<const float*>(p->weight), static_cast<const float*>(p->bias), static_cast<float*>(dst), (int)p->m, (int)p->c, npad, kpad);
+    return check_launch("pw_split_weights");
+}
+
 int conv1x1_tensor_core(const b200ml_ctx* ctx, const b200ml_conv_params* p, cudaStream_t stream) {
     const int64_t hw = p->h * p->w;
     const int npad = (int)(ceil_div(p->m, 16) * 16), kpad = (int)(ceil_div(p->c + 1, PW_KB) * PW_KB);
     float* wsplit = static_cast<float*>(ctx->workspace);
-    pw_split_weights_kernel<<<(unsigned)ceil_div((int64_t)npad * kpad, 256), 256, 0, stream>>>(
-        static_cast<const float*>(p->weight), static_cast<const float*>(p->bias), wsplit, (int)p->m, (int)p->c, npad, kpad);
-    int rc = check_launch("pw_split_weights");
-    if (rc) return rc;
+    if (p->packed_weight) {  // split once by the caller
+        B200ML_REQUIRE(aligned16(p->packed_weight), "conv: the packed weights must be 16-byte aligned");
+        wsplit = const_cast<float*>(static_cast<const float*>(p->packed_weight));
+    } else {
+        int rc = conv1x1_pack(ctx, p, wsplit, stream);
+        if (rc) return rc;
+    }
 
     CUtensorMap tx, tw, ty;
     {

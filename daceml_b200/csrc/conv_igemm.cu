@@ -564,21 +564,34 @@ bool conv_igemm_applies(const b200ml_ctx* ctx, const b200ml_conv_params* p, int6
     return true;
 }
 
+int64_t conv_igemm_pack_bytes(const b200ml_conv_params* p, int64_t ow) {
+    const IgPlan pl = ig_plan(p, ow);
+    return pl.ok ? 2ll * pl.rows * pl.ntot * 4 : 0;
+}
+
+int conv_igemm_pack(const b200ml_ctx*, const b200ml_conv_params* p, int64_t ow, void* dst, cudaStream_t stream) {
+    const IgPlan pl = ig_plan(p, ow);
+    const int64_t total = (int64_t)pl.rows * pl.ntot;
+    const unsigned grid = (unsigned)(ceil_div(total, 256) < 1184 ? ceil_div(total, 256) : 1184);
+    B200ML_CUDA(launch_pdl(ig_split_weights_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const float*>(p->weight),
+                           static_cast<float*>(dst), (int)p->m, (int)p->c, (int)p->kh, (int)p->kw, pl.ntot, pl.rows));
+    return check_launch("ig_split_weights");
+}
+
 int conv_igemm(const b200ml_ctx* ctx, const b200ml_conv_params* p, int64_t oh, int64_t ow, cudaStream_t stream) {
     const IgPlan pl = ig_plan(p, ow);
     float* wsplit = static_cast<float*>(ctx->workspace);
-    {
-        const int64_t total = (int64_t)pl.rows * pl.ntot;
-        const unsigned grid = (unsigned)(ceil_div(total, 256) < 1184 ? ceil_div(total, 256) : 1184);
-        B200ML_CUDA(launch_pdl(ig_split_weights_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const float*>(p->weight),
-                               wsplit, (int)p->m, (int)p->c, (int)p->kh, (int)p->kw, pl.ntot, pl.rows));
-        int rc = check_launch("ig_split_weights");
+    if (p->packed_weight) {  // split once by the caller
+        B200ML_REQUIRE(aligned16(p->packed_weight), "conv: the packed weights must be 16-byte aligned");
+        wsplit = const_cast<float*>(static_cast<const float*>(p->packed_weight));
+    } else {
+        int rc = conv_igemm_pack(ctx, p, ow, wsplit, stream);
         if (rc) return rc;
     }
+    CUtensorMap tx, tw, ty;
     // X and Y go through the TMA unit when their row pitches and bases are multiples of 16 bytes
     // (and tiles of one row of 32 columns per operand line: the bulk stores write [8 channels][32 columns] boxes)
     const bool direct_io = pl.parts != 1 || p->w % 4 != 0 || ow % 4 != 0 || !aligned16(p->x) || !aligned16(p->y);
-    CUtensorMap tx, tw, ty;
     if (!direct_io) {
         const cuuint64_t dims[4] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->c, (cuuint64_t)p->n};
         const cuuint64_t strides[3] = {(cuuint64_t)p->w * 4, (cuuint64_t)p->w * p->h * 4, (cuuint64_t)p->w * p->h * p->c * 4};

@@ -286,27 +286,54 @@ def maxpool2d(x, out, *, kernel, strides=(1, 1), pads=(0, 0, 0, 0)):
     return out
 
 
-def conv2d(x, w, out, *, bias=None, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1, act=0, gate=None,
-           residual=None, pool_mean=None):
-    """ONNX Conv on NCHW tensors; ``pads`` is ONNX order (top, left, bottom, right)."""
-    ctx = _ctx(x)
-    for t in (x, w, out, bias, gate, residual, pool_mean):
-        _contig(t, "conv operand")
+def _conv_params(x_shape, dtype, w, bias, strides, pads, dilations, group, act):
     p = L.ConvParams()
-    p.dtype, p.act = L.dtype_code(x.dtype), act
-    p.n, p.c, p.h, p.w = x.shape
+    p.dtype, p.act = L.dtype_code(dtype), act
+    p.n, p.c, p.h, p.w = x_shape
     p.m, _, p.kh, p.kw = w.shape
     p.stride_h, p.stride_w = strides
     p.pad_top, p.pad_left, p.pad_bottom, p.pad_right = pads
     p.dil_h, p.dil_w = dilations
     p.group = group
-    p.x, p.weight, p.y = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    p.weight = w.data_ptr()
     p.bias = bias.data_ptr() if bias is not None else None
+    return p
+
+
+def conv2d(x, w, out, *, bias=None, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1, act=0, gate=None,
+           residual=None, pool_mean=None, packed_weight=None):
+    """ONNX Conv on NCHW tensors; ``pads`` is ONNX order (top, left, bottom, right).  ``packed_weight``: what
+    :func:`conv_prepack` returned for these weights, bias, shapes and attributes (or None)."""
+    ctx = _ctx(x)
+    for t in (x, w, out, bias, gate, residual, pool_mean):
+        _contig(t, "conv operand")
+    p = _conv_params(x.shape, x.dtype, w, bias, strides, pads, dilations, group, act)
+    p.x, p.y = x.data_ptr(), out.data_ptr()
     p.gate = gate.data_ptr() if gate is not None else None
     p.residual = residual.data_ptr() if residual is not None else None
     p.pool_sum = pool_mean.data_ptr() if pool_mean is not None else None
+    p.packed_weight = packed_weight.data_ptr() if packed_weight is not None else None
     L.check(ctx.lib.b200ml_conv2d(ctx.handle, ctypes.byref(p), _stream(x)))
     return out
+
+
+def conv_prepack(x_shape, w, *, bias=None, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1, gate=False):
+    """Prepares constant convolution weights once (``b200ml_conv_prepack``): returns the packed tensor to pass to
+    :func:`conv2d` as ``packed_weight``, or None when this convolution runs on a kernel that takes the weights as they
+    are.  ``w`` and ``bias`` are device tensors; ``gate`` says whether the calls will carry a squeeze-excite gate."""
+    if not w.is_cuda or w.dtype != torch.float32:
+        return None
+    ctx = _ctx(w)
+    for t in (w, bias):
+        _contig(t, "conv operand")
+    p = _conv_params(x_shape, w.dtype, w, bias, strides, pads, dilations, group, 0)
+    p.gate = 1 if gate else None  # only its presence matters (the implicit-GEMM kernel takes no gate)
+    nbytes = int(ctx.lib.b200ml_conv_prepack_bytes(ctx.handle, ctypes.byref(p)))
+    if nbytes <= 0:
+        return None
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+    L.check(ctx.lib.b200ml_conv_prepack(ctx.handle, ctypes.byref(p), ctypes.c_void_p(packed.data_ptr()), _stream(w)))
+    return packed
 
 
 def se_gate(pooled, w1, b1, w2, b2, out):

@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = [
     "b200ml_cast", "b200ml_conv2d", "b200ml_se_gate", "b200ml_attention_f16", "b200ml_strided_copy", "b200ml_gather",
     "b200ml_where", "b200ml_compare", "b200ml_maxpool2d", "b200ml_wait_probe", "b200ml_strided_copy_parts",
     "b200ml_peer_allgather", "b200ml_ipc_export", "b200ml_ipc_open", "b200ml_ipc_close",
+    "b200ml_conv_prepack_bytes", "b200ml_conv_prepack",
 ]
 
 
@@ -86,6 +87,7 @@ class ConvParams(ctypes.Structure):
         ("dil_h", ctypes.c_int64), ("dil_w", ctypes.c_int64), ("group", ctypes.c_int64),
         ("x", ctypes.c_void_p), ("weight", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("gate", ctypes.c_void_p),
         ("residual", ctypes.c_void_p), ("y", ctypes.c_void_p), ("pool_sum", ctypes.c_void_p),
+        ("packed_weight", ctypes.c_void_p),
     ]
 
 
@@ -141,6 +143,9 @@ def load_library(path=None):
         lib.b200ml_transpose.argtypes = [vp, c_i32, vp, vp, c_i32, i64p, i32p, vp]
         lib.b200ml_cast.argtypes = [vp, c_i32, c_i32, vp, vp, c_i64, vp]
         lib.b200ml_conv2d.argtypes = [vp, ctypes.POINTER(ConvParams), vp]
+        lib.b200ml_conv_prepack_bytes.argtypes = [vp, ctypes.POINTER(ConvParams)]
+        lib.b200ml_conv_prepack_bytes.restype = ctypes.c_int64
+        lib.b200ml_conv_prepack.argtypes = [vp, ctypes.POINTER(ConvParams), vp, vp]
         lib.b200ml_se_gate.argtypes = [vp, c_i32, vp, vp, vp, vp, vp, vp, c_i64, c_i64, c_i64, vp]
         lib.b200ml_attention_f16.argtypes = [vp, ctypes.POINTER(AttentionParams), vp]
         lib.b200ml_strided_copy.argtypes = [vp, c_i32, vp, vp, c_i32, i64p, i64p, i64p, vp]
@@ -156,7 +161,7 @@ def load_library(path=None):
         lib.b200ml_ipc_close.argtypes = [vp, vp, c_i64]
         for name in EXPORTED_SYMBOLS:
             fn = getattr(lib, name)
-            if name not in ("b200ml_last_error", "b200ml_launch_count", "b200ml_ctx_workspace_bytes"):
+            if name not in ("b200ml_last_error", "b200ml_launch_count", "b200ml_ctx_workspace_bytes", "b200ml_conv_prepack_bytes"):
                 fn.restype = ctypes.c_int
         if path is None:
             _lib = lib

@@ -581,6 +581,28 @@ def _conv_can(node, state, sdfg):
     return x.shape[1] % g == 0 and w.shape[0] % g == 0 and w.shape[1] == x.shape[1] // g
 
 
+def _prepacked_conv_weights(node, state, sdfg, x, strides, pads, dil, group, gate):
+    """Weights (and bias) that are constants of the SDFG are prepared for the tensor-core kernels once, here, instead
+    of by a small kernel at every call (``b200ml_conv_prepack``).  Returns the packed tensor or None (no device, the
+    weights arrive at run time, or the convolution runs on a kernel that takes them as they are)."""
+    if not torch.cuda.is_available() or not _b_is_constant(node, state, sdfg, "W"):
+        return None
+    if _has_in(node, state, "B") and not _b_is_constant(node, state, sdfg, "B"):
+        return None
+    dev = torch.device("cuda", torch.cuda.current_device())
+    tensors = {}
+    for conn in ("W", "B"):
+        for e in state.in_edges_by_connector(node, conn):
+            t = sdfg.constants[e.data.data]
+            if not t.is_cuda:  # the compiled SDFG binds the same device copy at its first call
+                t = sdfg.constants[e.data.data] = t.to(dev).contiguous()
+            tensors[conn] = t
+    w = tensors["W"]
+    if w.dtype != torch.float32 or not w.is_contiguous():
+        return None
+    return K.conv_prepack(tuple(x.shape), w, bias=tensors.get("B"), strides=strides, pads=pads, dilations=dil, group=group, gate=gate)
+
+
 @op_implementation(op="Conv", name="b200")
 class B200Conv(ONNXForward):
     """2-D convolution with strides, pads, dilations and groups (the reference's pure Conv rejects all four)."""
@@ -592,10 +614,12 @@ class B200Conv(ONNXForward):
     def forward(node, state, sdfg):
         x, w = in_desc_with_name(node, state, sdfg, "X"), in_desc_with_name(node, state, sdfg, "W")
         strides, dil, pads, group = _conv_geometry(node, x, w)
+        packed = _prepacked_conv_weights(node, state, sdfg, x, strides, pads, dil, group, False)
 
         def run(ins, outs):
-            K.conv2d(ins["X"], ins["W"], outs["Y"], bias=ins.get("B"), strides=strides, pads=pads, dilations=dil,
-                     group=group)
+            xt = ins["X"]
+            K.conv2d(xt, ins["W"], outs["Y"], bias=ins.get("B"), strides=strides, pads=pads, dilations=dil,
+                     group=group, packed_weight=packed if packed is not None and packed.device == xt.device else None)
 
         return KernelTasklet(node.label, run, kernels=("conv2d",))
 
@@ -649,11 +673,13 @@ class B200FusedConv(ONNXForward):
         x, w = in_desc_with_name(node, state, sdfg, "X"), in_desc_with_name(node, state, sdfg, "W")
         strides, dil, pads, group = _conv_geometry(node, x, w)
         act = _ACT[node.activation]
+        packed = _prepacked_conv_weights(node, state, sdfg, x, strides, pads, dil, group, _has_in(node, state, "Gate"))
 
         def run(ins, outs):
-            K.conv2d(ins["X"], ins["W"], outs["Y"], bias=ins.get("B"), strides=strides, pads=pads, dilations=dil,
+            xt = ins["X"]
+            K.conv2d(xt, ins["W"], outs["Y"], bias=ins.get("B"), strides=strides, pads=pads, dilations=dil,
                      group=group, act=act, gate=ins.get("Gate"), residual=ins.get("Residual"),
-                     pool_mean=outs.get("Pool"))
+                     pool_mean=outs.get("Pool"), packed_weight=packed if packed is not None and packed.device == xt.device else None)
 
         return KernelTasklet(node.label, run, kernels=("conv2d",))
 

@@ -319,6 +319,7 @@ typedef struct {
     const void* residual; /* [n, m, oh, ow] or null, added after act */
     void* y;              /* [n, m, oh, ow] */
     float* pool_sum;      /* [n, m] or null: receives the mean of y over (oh, ow) (GlobalAveragePool fused) */
+    const void* packed_weight; /* null, or what b200ml_conv_prepack wrote for these weights, bias and shapes */
 } b200ml_conv_params;
 
 /* ONNX Conv (cross-correlation, NCHW).  Replaces PureConv2D (img_op_implementations.py:164-330)
@@ -328,6 +329,15 @@ typedef struct {
  * and kernels up to 7 x 7 with stride 1 or 2 whose reduction has 64 terms or more as an implicit GEMM; both use
  * the context's scratch for the split weights, so calls sharing a context must not overlap. */
 int b200ml_conv2d(b200ml_ctx* ctx, const b200ml_conv_params* p, b200ml_stream stream);
+/* Weights that do not change between calls can be prepared once (the role cuDNN's filter descriptors and a framework's
+ * weight pre-packing play for the reference's GPU route, cudnn_implementations.py:205-240): the tensor-core kernels
+ * want weight and bias split into their TF32 hi and lo parts and re-ordered, which b200ml_conv2d otherwise does with a
+ * small kernel at every call.  b200ml_conv_prepack_bytes returns the size of the packed form for this convolution (its
+ * tensor pointers are not read), 0 if the convolution runs on a kernel that takes the weights as they are.
+ * b200ml_conv_prepack writes it (16-byte aligned device memory of that size, owned by the caller); later calls pass it
+ * as p->packed_weight together with the same weight, bias, shapes and attributes. */
+int64_t b200ml_conv_prepack_bytes(b200ml_ctx* ctx, const b200ml_conv_params* p);
+int b200ml_conv_prepack(b200ml_ctx* ctx, const b200ml_conv_params* p, void* packed, b200ml_stream stream);
 
 /* gate[n, c] = sigmoid(W2 . swish(W1 . pooled[n, :] + b1) + b2): the two 1x1 convolutions of a
  * squeeze-excite block on a [n, c, 1, 1] tensor.  w1 is [r, c], w2 is [c, r]. */

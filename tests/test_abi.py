@@ -38,7 +38,7 @@ def test_every_declared_symbol_is_exported(library):
 def test_struct_layouts_match_header():
     # field order of the ctypes mirrors follows the header; sizes are what a C compiler produces
     assert ctypes.sizeof(L.GemmParams) == 4 * 4 + 17 * 8 + 4 * 4 + 5 * 8 + 2 * 8 + 2 * 4
-    assert ctypes.sizeof(L.ConvParams) == 2 * 4 + 16 * 8 + 7 * 8
+    assert ctypes.sizeof(L.ConvParams) == 2 * 4 + 16 * 8 + 8 * 8
     assert ctypes.sizeof(L.AttentionParams) == 17 * 8 + 2 * 4 + 5 * 8
 
 

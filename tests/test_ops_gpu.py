@@ -647,3 +647,30 @@ def test_python_implementations_through_the_helper_api(rng):
         donnx.ONNXSoftplus.implementations.pop("composed", None)
         ONNXForward.unregister(LeakyRelu)
         ONNXForward.unregister(ComposedSoftplus)
+
+
+def test_conv_prepacked_weights(rng):
+    """``b200ml_conv_prepack``: weights split once give bit-identical results in one launch instead of two, for the 1x1
+    and the implicit-GEMM kernel; convolutions on the other kernels report that there is nothing to pack."""
+    if os.environ.get("B200ML_CONV_TC", "1") == "0":
+        pytest.skip("the tensor-core convolution is switched off")
+    for (n, cin, cout, hw, k, pads, strides) in ((8, 24, 144, (56, 56), (1, 1), (0, 0, 0, 0), (1, 1)), (8, 32, 48, (28, 28), (3, 3), (1, 1, 1, 1), (1, 1)),
+                                                 (8, 32, 64, (56, 56), (3, 3), (1, 1, 1, 1), (2, 2))):
+        x = dev(rng.standard_normal((n, cin) + hw).astype(np.float32))
+        w = dev((rng.standard_normal((cout, cin) + k) * 0.1).astype(np.float32))
+        b = dev(rng.standard_normal(cout).astype(np.float32))
+        oh = (hw[0] + pads[0] + pads[2] - k[0]) // strides[0] + 1
+        ow = (hw[1] + pads[1] + pads[3] - k[1]) // strides[1] + 1
+        y0, y1 = empty((n, cout, oh, ow), torch.float32), empty((n, cout, oh, ow), torch.float32)
+        K.conv2d(x, w, y0, bias=b, strides=strides, pads=pads, act=L.EPI_RELU)
+        packed = K.conv_prepack(tuple(x.shape), w, bias=b, strides=strides, pads=pads)
+        assert packed is not None and packed.numel() > 0
+        before = L.launch_count()
+        K.conv2d(x, w, y1, bias=b, strides=strides, pads=pads, act=L.EPI_RELU, packed_weight=packed)
+        assert L.launch_count() - before == 1
+        assert torch.equal(y0, y1)
+    wd = dev(rng.standard_normal((16, 1, 3, 3)).astype(np.float32))
+    assert K.conv_prepack((4, 16, 32, 32), wd, pads=(1, 1, 1, 1), group=16) is None            # depthwise
+    ws = dev(rng.standard_normal((16, 3, 3, 3)).astype(np.float32))
+    assert K.conv_prepack((32, 3, 64, 64), ws, strides=(2, 2)) is None                         # 27 terms: the direct kernel
+    status_ok()
