@@ -262,3 +262,28 @@ def test_model_proto_route_needs_onnx():
                               [helper.make_tensor_value_info("y", TensorProto.FLOAT, [4])])
     model = ONNXModel("proto", helper.make_model(graph, opset_imports=[helper.make_opsetid("", 12)]))
     assert [type(n).schema.name for n in model.state.topological_compute_nodes()] == ["Relu"]
+
+
+def test_resnet_basic_block_collapses_to_two_convolutions_and_a_relu():
+    """Conv + BatchNorm (+ ReLU) fold into one convolution each, the shortcut add rides in the second one's epilogue;
+    the down-sampling block has a third convolution (strided 1x1 + BatchNorm) for the shortcut."""
+    class BasicBlock(nn.Module):
+        def __init__(self, cin, cout, stride):
+            super().__init__()
+            self.conv1, self.bn1 = nn.Conv2d(cin, cout, 3, stride=stride, padding=1, bias=False), nn.BatchNorm2d(cout)
+            self.conv2, self.bn2 = nn.Conv2d(cout, cout, 3, padding=1, bias=False), nn.BatchNorm2d(cout)
+            self.down = None
+            if stride != 1 or cin != cout:
+                self.down = nn.Sequential(nn.Conv2d(cin, cout, 1, stride=stride, bias=False), nn.BatchNorm2d(cout))
+
+        def forward(self, x):
+            y = torch.relu(self.bn1(self.conv1(x)))
+            y = self.bn2(self.conv2(y))
+            return torch.relu(y + (x if self.down is None else self.down(x)))
+
+    m = DaceModule(BasicBlock(16, 16, 1).eval(), dummy_inputs=(torch.randn(2, 16, 12, 12), ))
+    assert m.compiled_function.kernel_names() == ["conv2d", "conv2d", "unary"]
+    fused = [n for n, _ in m.sdfg.all_nodes_recursive() if type(n).__name__ == "KernelTasklet"]
+    assert len(fused) == 3
+    m = DaceModule(BasicBlock(16, 32, 2).eval(), dummy_inputs=(torch.randn(2, 16, 12, 12), ))
+    assert sorted(m.compiled_function.kernel_names()) == ["conv2d", "conv2d", "conv2d", "unary"]
