@@ -188,6 +188,19 @@ def main(reference_root):
     m2 = case("gelu_5_mul", "Mul", {"A": m1, "B": np.array(0.5, F)}, {"C": (S, F)})["C"]
     ARRAYS["gelu_chain:x"], ARRAYS["gelu_chain:y"] = g0, m2
 
+    # ---- Conv large enough for the implicit-GEMM tensor-core kernel (64 terms or more, 4096 output pixels): the
+    # reference's stride-1, unpadded loop nest on 4 images; 5x5 on a width the TMA unit can describe, 3x3 on one it
+    # cannot.  These two take about a minute each (the loop nest runs as Python).  Drawn from a generator of their own so
+    # that the cases above keep their values.
+    rng2 = np.random.default_rng(20261)
+    for cin, ksize, filters, hw in [(4, (5, 5), 16, (36, 36)), (8, (3, 3), 16, (34, 34))]:
+        X = rng2.random((4, cin) + hw).astype(F)
+        W = (rng2.random((filters, cin) + ksize).astype(F) - np.float32(0.5))
+        B = rng2.random(filters).astype(F)
+        case("conv_igemm_c%d_k%d_f%d" % (cin, ksize[0], filters), "Conv", {"X": X, "W": W, "B": B},
+             {"Y": ((4, filters, hw[0] + 1 - ksize[0], hw[1] + 1 - ksize[1]), F)},
+             group=1, dilations=None, pads=None, strides=None, auto_pad="NOTSET", kernel_shape=None)
+
     def plain(v):
         if isinstance(v, type):
             return np.dtype(v).name
