@@ -201,6 +201,12 @@ def main(reference_root):
              {"Y": ((4, filters, hw[0] + 1 - ksize[0], hw[1] + 1 - ksize[1]), F)},
              group=1, dilations=None, pads=None, strides=None, auto_pad="NOTSET", kernel_shape=None)
 
+    # ---- and a 1x1 convolution large enough for the 1x1 tensor-core kernel (16384 pixels) ----
+    X = rng2.standard_normal((4, 8, 64, 64)).astype(F)
+    W = (rng2.standard_normal((8, 8, 1, 1)) * 0.3).astype(F)
+    case("conv_pointwise_tc", "Conv", {"X": X, "W": W, "B": rng2.standard_normal(8).astype(F)}, {"Y": ((4, 8, 64, 64), F)},
+         group=1, dilations=[1, 1], pads=[0, 0, 0, 0], strides=[1, 1], auto_pad="NOTSET", kernel_shape=[1, 1])
+
     def plain(v):
         if isinstance(v, type):
             return np.dtype(v).name

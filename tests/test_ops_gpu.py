@@ -593,17 +593,17 @@ def test_kernels_match_reference_source(case):
     status_ok()
 
 
-@pytest.mark.parametrize("name", ["conv_igemm_c4_k5_f16", "conv_igemm_c8_k3_f16"])
-def test_implicit_gemm_convolution_matches_the_reference_loop_nest(name):
-    """The two fixtures produced by the reference's own ``PureConv2D`` loop nest
-    (``img_op_implementations.py:217-288``, executed as Python) at a size the implicit-GEMM kernel takes: the
-    tensor-core path did run (weight split + kernel), and agrees at the fp32 tolerance."""
+@pytest.mark.parametrize("name", ["conv_igemm_c4_k5_f16", "conv_igemm_c8_k3_f16", "conv_pointwise_tc"])
+def test_tensor_core_convolutions_match_the_reference_loop_nest(name):
+    """The fixtures produced by the reference's own ``PureConv2D`` loop nest (``img_op_implementations.py:217-288``,
+    executed as Python) at sizes the implicit-GEMM kernel and the 1x1 kernel take: the tensor-core path did run (weight
+    split + kernel), and agrees at the fp32 tolerance."""
     if os.environ.get("B200ML_CONV_TC", "1") == "0":
         pytest.skip("the tensor-core convolution is switched off")
     case = next(c for c in ref_cases.REF_CASES if c["case"] == name)
     before = L.launch_count()
     results = ref_cases.frontend_outputs(case, ref_cases.ref_arrays(), donnx, torch)
-    assert L.launch_count() - before == 2, "expected the weight split and the implicit-GEMM kernel"
+    assert L.launch_count() - before == 2, "expected the weight split and the tensor-core kernel"
     got, want = results["Y"]
     assert_close(got, want, torch.float32, what=name)
     status_ok()
