@@ -1,5 +1,5 @@
 // fp32 GEMM on the tensor cores with fp32-grade accuracy ("3 x TF32"):
-//     C = act(alpha * A.B^T + bias) + residual,   A [M, K], B [N, K] (the nn.Linear layout), all fp32.
+//     C = act(alpha * A.B^T + bias) + residual,   A [M, K], B [N, K] (the nn.Linear layout) or [K, N] (ONNX MatMul), all fp32.
 // A single TF32 product keeps 11 significant bits of each operand (relative error ~5e-4, outside the 1e-4 the fp32
 // configurations allow).  Each operand is therefore split once, by a small kernel, into hi = the value rounded to
 // TF32 and lo = value - hi (exact in fp32), and the tensor core accumulates
@@ -10,7 +10,7 @@
 // epilogue adds with round-to-nearest: a quarter of the steps per accumulator.  Same structure as the fp16 kernel: TMA producer warp (four tiles per stage), one MMA-issuing
 // thread (tcgen05.mma kind::tf32, 128 x 128 x 8 per instruction), two accumulators in TMEM, eight epilogue warps.
 // The split copies live in the context's workspace; the caller falls back to the FP32-FMA kernel when they do not
-// fit, when a layout is not K-major, or when the product is too small to be worth three kernels.
+// fit, when A is not K-major, or when the product is too small to be worth three kernels.
 #include "gemm_common.cuh"
 
 namespace b200ml {
@@ -38,6 +38,7 @@ struct Tf32Args {
     float alpha, bias_scale, residual_scale;
     int64_t ldc, ldr;
     int32_t vec_ok;  // C (and residual) rows allow 16-byte accesses
+    int32_t b_mn;    // B is [K, N] (N contiguous, the ONNX MatMul layout): the MN-major operand form
     float* c;
     const float* bias;
     const float* residual;
@@ -55,24 +56,37 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 
+// Shared-memory descriptor of an MN-major 32-bit operand: the 128-byte swizzle with 32-byte atoms (layout type 1, the
+// only one tcgen05.mma takes for MN-major tf32); atoms are 128 bytes (32 elements along N) x 4 k-rows, `lbo` apart along
+// N and `sbo` apart along K.
+__device__ __forceinline__ uint64_t make_smem_desc_mn32(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;
+    d |= 1ull << 61;
+    return d;
+}
+
 // hi = x rounded to nearest-even at 10 mantissa bits (TF32), lo = x - hi; rows of `cols` elements, source rows `ld` apart.
 // One launch splits both operands of a product: the first `a_blocks` blocks take A, the others B.
 struct SplitOperand {
     const float* x;
     float* hi;
     float* lo;
-    int64_t rows, ld;
+    int64_t rows, cols, ld;
 };
 
-__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitOperand oa, const SplitOperand ob, int64_t cols, unsigned a_blocks) {
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitOperand oa, const SplitOperand ob, unsigned a_blocks) {
     const bool first = blockIdx.x < a_blocks;
     const SplitOperand& o = first ? oa : ob;
     const float* __restrict__ x = o.x;
     float* __restrict__ hi = o.hi;
     float* __restrict__ lo = o.lo;
     const int64_t ld = o.ld;
-    const int64_t n4 = o.rows * (cols / 4);
-    const int64_t per_row = cols / 4;
+    const int64_t n4 = o.rows * (o.cols / 4);
+    const int64_t per_row = o.cols / 4;
     const int64_t block = first ? blockIdx.x : blockIdx.x - a_blocks;
     const int64_t nblocks = first ? a_blocks : gridDim.x - a_blocks;
     for (int64_t i = block * blockDim.x + threadIdx.x; i < n4; i += nblocks * blockDim.x) {
@@ -153,8 +167,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
                     ptx::mbar_expect_tx(&full_bar[stage], T_STAGE_BYTES);
                     ptx::tma_load_4d(s0, &tmap_ah, &full_bar[stage], kb * TBK, m0, 0, 0);
                     ptx::tma_load_4d(s0 + T_TILE_BYTES, &tmap_al, &full_bar[stage], kb * TBK, m0, 0, 0);
-                    ptx::tma_load_4d(s0 + 2 * T_TILE_BYTES, &tmap_bh, &full_bar[stage], kb * TBK, n0, 0, 0);
-                    ptx::tma_load_4d(s0 + 3 * T_TILE_BYTES, &tmap_bl, &full_bar[stage], kb * TBK, n0, 0, 0);
+                    if (args.b_mn) {
+                        // four boxes of 32 columns x 32 k-rows each: 32 lines of 128 bytes, the MN-major atom layout
+                        for (int j = 0; j < TBN / 32; ++j) {
+                            ptx::tma_load_4d(s0 + 2 * T_TILE_BYTES + j * 4096, &tmap_bh, &full_bar[stage], n0 + 32 * j, kb * TBK, 0, 0);
+                            ptx::tma_load_4d(s0 + 3 * T_TILE_BYTES + j * 4096, &tmap_bl, &full_bar[stage], n0 + 32 * j, kb * TBK, 0, 0);
+                        }
+                    } else {
+                        ptx::tma_load_4d(s0 + 2 * T_TILE_BYTES, &tmap_bh, &full_bar[stage], kb * TBK, n0, 0, 0);
+                        ptx::tma_load_4d(s0 + 3 * T_TILE_BYTES, &tmap_bl, &full_bar[stage], kb * TBK, n0, 0, 0);
+                    }
                     if (++stage == T_STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -190,12 +212,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
                         const uint32_t off = kk * (T_UMMA_K * 4);  // 32 bytes along K inside the 128-byte swizzle row
                         const uint64_t d_ah = ptx::make_smem_desc_sw128(ah + off, 16, 1024);
                         const uint64_t d_al = ptx::make_smem_desc_sw128(al + off, 16, 1024);
-                        const uint64_t d_bh = ptx::make_smem_desc_sw128(bh + off, 16, 1024);
-                        const uint64_t d_bl = ptx::make_smem_desc_sw128(bl + off, 16, 1024);
+                        // B K-major: 32 bytes along the swizzle row per step; B MN-major: 8 k-rows (two 512-byte groups) per
+                        // step, 32-column atoms one box (4 KB) apart
+                        const uint64_t d_bh = args.b_mn ? make_smem_desc_mn32(bh + kk * 1024, 4096, 512) : ptx::make_smem_desc_sw128(bh + off, 16, 1024);
+                        const uint64_t d_bl = args.b_mn ? make_smem_desc_mn32(bl + kk * 1024, 4096, 512) : ptx::make_smem_desc_sw128(bl + off, 16, 1024);
+                        const uint32_t idesc = args.b_mn ? (T_IDESC | (1u << 16)) : T_IDESC;
                         // the two small terms first, the large one last
-                        mma_tf32_ss(d_tmem, d_al, d_bh, T_IDESC, (kb >= T_NACC || kk != 0) ? 1u : 0u);
-                        mma_tf32_ss(d_tmem, d_ah, d_bl, T_IDESC, 1u);
-                        mma_tf32_ss(d_tmem, d_ah, d_bh, T_IDESC, 1u);
+                        mma_tf32_ss(d_tmem, d_al, d_bh, idesc, (kb >= T_NACC || kk != 0) ? 1u : 0u);
+                        mma_tf32_ss(d_tmem, d_ah, d_bl, idesc, 1u);
+                        mma_tf32_ss(d_tmem, d_ah, d_bh, idesc, 1u);
                     }
                     ptx::mma_commit(&empty_bar[stage]);
                     if (++stage == T_STAGES) {
@@ -328,8 +353,9 @@ bool tf32x3_enabled() {
 // Whether the tensor-core path covers this fp32 product (the caller uses the FP32-FMA kernel otherwise).
 bool gemm_f32_tensor_core_applies(const b200ml_ctx* ctx, const b200ml_gemm_params* p) {
     if (!tf32x3_enabled() || p->batch_outer * p->batch_inner != 1) return false;
-    if (p->a_layout != 0 || p->b_layout != 1) return false;                       // both operands K-major
+    if (p->a_layout != 0) return false;                                            // A K-major; B [N, K] or [K, N]
     if (p->k % 4 != 0 || p->lda % 4 != 0 || p->ldb % 4 != 0) return false;         // 16-byte rows for the split and the TMA
+    if (p->b_layout == 0 && p->n % 4 != 0) return false;
     if (!aligned16(p->a) || !aligned16(p->b)) return false;
     if (p->m < 256 || p->n < 32 || p->k < 64) return false;                        // three launches must pay for themselves
     if (p->m * p->n * p->k < (1ll << 26)) return false;
@@ -350,17 +376,29 @@ int gemm_f32_tensor_core(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cud
         return static_cast<unsigned>(b < 1 ? 1 : (b > cap ? cap : b));
     };
     const unsigned ba = blocks(p->m * p->k), bb = blocks(p->n * p->k);
-    const SplitOperand oa{static_cast<const float*>(p->a), a_hi, a_lo, p->m, p->lda};
-    const SplitOperand ob{static_cast<const float*>(p->b), b_hi, b_lo, p->n, p->ldb};
-    split_tf32_kernel<<<ba + bb, 256, 0, stream>>>(oa, ob, p->k, ba);
+    const bool b_mn = p->b_layout == 0;  // B [K, N]: its split copies keep that shape, rows of N
+    const SplitOperand oa{static_cast<const float*>(p->a), a_hi, a_lo, p->m, p->k, p->lda};
+    const SplitOperand ob{static_cast<const float*>(p->b), b_hi, b_lo, b_mn ? p->k : p->n, b_mn ? p->n : p->k, p->ldb};
+    split_tf32_kernel<<<ba + bb, 256, 0, stream>>>(oa, ob, ba);
     int rc = check_launch("split_tf32");
     if (rc) return rc;
 
     CUtensorMap tah, tal, tbh, tbl;
     if ((rc = make_tmap_f32(ctx, &tah, a_hi, p->k, p->m, "A hi"))) return rc;
     if ((rc = make_tmap_f32(ctx, &tal, a_lo, p->k, p->m, "A lo"))) return rc;
-    if ((rc = make_tmap_f32(ctx, &tbh, b_hi, p->k, p->n, "B hi"))) return rc;
-    if ((rc = make_tmap_f32(ctx, &tbl, b_lo, p->k, p->n, "B lo"))) return rc;
+    if (b_mn) {
+        for (int part = 0; part < 2; ++part) {
+            const cuuint64_t dims[4] = {(cuuint64_t)p->n, (cuuint64_t)p->k, 1, 1};
+            const cuuint64_t strides[3] = {(cuuint64_t)p->n * 4, (cuuint64_t)p->n * 4 * (cuuint64_t)p->k, (cuuint64_t)p->n * 4 * (cuuint64_t)p->k};
+            const cuuint32_t box[4] = {32, TBK, 1, 1};
+            CUresult r = encode_tiled_cached(ctx, part ? &tbl : &tbh, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, part ? b_lo : b_hi, dims, strides, box,
+                                             CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+            if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(B [K, N], fp32) failed with CUresult %d", (int)r);
+        }
+    } else {
+        if ((rc = make_tmap_f32(ctx, &tbh, b_hi, p->k, p->n, "B hi"))) return rc;
+        if ((rc = make_tmap_f32(ctx, &tbl, b_lo, p->k, p->n, "B lo"))) return rc;
+    }
 
     Tf32Args args{};
     args.m = (int32_t)p->m;
@@ -379,6 +417,7 @@ int gemm_f32_tensor_core(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cud
     if (p->residual) vec = vec && aligned16(p->residual) && p->ldr % 4 == 0;
     if (p->bias) vec = vec && aligned16(p->bias);
     args.vec_ok = vec ? 1 : 0;
+    args.b_mn = b_mn ? 1 : 0;
     args.c = static_cast<float*>(p->c);
     args.bias = static_cast<const float*>(p->bias);
     args.residual = static_cast<const float*>(p->residual);

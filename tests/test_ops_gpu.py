@@ -128,6 +128,27 @@ def test_gemm_fp32_tensor_core_path(m, n, k, rng):
     status_ok()
 
 
+@pytest.mark.parametrize("m, n, k", [(512, 520, 384), (1024, 256, 260), (4096, 1024, 1024), (777, 132, 1000)])
+def test_matmul_fp32_tensor_core_path_with_b_in_onnx_layout(m, n, k, rng):
+    """fp32 MatMul with B as ONNX gives it ([K, N], N contiguous) on the same three-pass TF32 kernel (B read as the
+    MN-major operand): ragged M, N and K; one split launch and one product."""
+    if os.environ.get("B200ML_TF32X3", "1") == "0":
+        pytest.skip("the fp32 tensor-core GEMM is switched off")
+    a, b = rng.standard_normal((m, k)).astype(np.float32), (rng.standard_normal((k, n)) * 0.1).astype(np.float32)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    guard = torch.full((m * n + 4096, ), 7.0, dtype=torch.float32, device="cuda")
+    y = guard[:m * n].view(m, n)
+    before = L.launch_count()
+    donnx.ONNXMatMul(A=dev(a), B=dev(b), Y=y)
+    assert L.launch_count() - before == 2, "expected the operand split and the tensor-core product"
+    scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    ratio = (np.abs(y.cpu().numpy().astype(np.float64) - ref) / scale).max()
+    assert ratio < 2e-6, f"3xTF32 forward error {ratio:.2e} of sum |a||b|"
+    assert_close(y, ops.matmul(a, b), torch.float32, atol=3e-5, what=f"fp32 matmul {m}x{n}x{k}")
+    assert bool((guard[m * n:] == 7.0).all()), "written past the end of Y"
+    status_ok()
+
+
 def test_gemm_golden_and_rules():
     g = gold("gemm")
     y = empty((7, 5), torch.float32)
