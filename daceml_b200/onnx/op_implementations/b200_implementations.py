@@ -589,14 +589,14 @@ def _prepacked_conv_weights(node, state, sdfg, x, strides, pads, dil, group, gat
         return None
     if _has_in(node, state, "B") and not _b_is_constant(node, state, sdfg, "B"):
         return None
-    dev = torch.device("cuda", torch.cuda.current_device())
+    dev = torch.device("cuda", torch.cuda.current_device())  # calls on another device ignore the packed copy
     tensors = {}
     for conn in ("W", "B"):
         for e in state.in_edges_by_connector(node, conn):
             t = sdfg.constants[e.data.data]
-            if not t.is_cuda:  # the compiled SDFG binds the same device copy at its first call
-                t = sdfg.constants[e.data.data] = t.to(dev).contiguous()
-            tensors[conn] = t
+            if not t.is_cuda:  # a copy for the packing kernel only; the SDFG's own constant moves with its first call
+                t = t.to(dev)
+            tensors[conn] = t.contiguous()
     w = tensors["W"]
     if w.dtype != torch.float32 or not w.is_contiguous():
         return None
