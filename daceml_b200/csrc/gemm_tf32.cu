@@ -27,6 +27,7 @@ constexpr int T_STAGES = 3;
 constexpr int T_SMEM = T_STAGES * T_STAGE_BYTES + 256 + 1024;
 constexpr int T_NACC = 4;                           // partial accumulators per tile
 constexpr uint32_t T_TMEM_COLS = T_NACC * TBN;     // 512: one tile at a time, no overlap of epilogue and main loop
+constexpr int T_PART_LD = TBM + 4;                  // row stride of a parked partial tile (column-major, padded)
 
 // Instruction descriptor for kind::tf32: D = f32 (bits [4,6) = 1), A and B formats = tf32 (2 in [7,10) and [10,13)),
 // both operands K-major, N >> 3 in [17,23), M >> 4 in [24,29).
@@ -107,7 +108,55 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const SplitOperand oa, 
     }
 }
 
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// Finishes NC columns of one output row: alpha, bias, activation, residual, store (16-byte stores when the row allows).
+template <int NC>
+__device__ __forceinline__ void tf32_finish_chunk(const Tf32Args& args, const uint32_t (&r)[NC], bool row_ok, float* c_row, const float* r_row,
+                                                  int col0, bool has_bias, bool has_res, int act) {
+    const bool full = args.vec_ok && col0 + NC <= args.n;
+    if (!row_ok) return;
+#pragma unroll
+    for (int g = 0; g < NC / 4; ++g) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = args.alpha * __uint_as_float(r[g * 4 + j]);
+        if (full) {
+            if (has_bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col0 + g * 4));
+                v[0] = fmaf(args.bias_scale, b.x, v[0]), v[1] = fmaf(args.bias_scale, b.y, v[1]);
+                v[2] = fmaf(args.bias_scale, b.z, v[2]), v[3] = fmaf(args.bias_scale, b.w, v[3]);
+            }
+            if (act) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = apply_act(v[j], act);
+            }
+            if (has_res) {
+                const float4 q = __ldg(reinterpret_cast<const float4*>(r_row + col0 + g * 4));
+                v[0] = fmaf(args.residual_scale, q.x, v[0]), v[1] = fmaf(args.residual_scale, q.y, v[1]);
+                v[2] = fmaf(args.residual_scale, q.z, v[2]), v[3] = fmaf(args.residual_scale, q.w, v[3]);
+            }
+            *reinterpret_cast<float4*>(c_row + col0 + g * 4) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int col = col0 + g * 4 + j;
+                if (col < args.n) {
+                    float o = v[j];
+                    if (has_bias) o = fmaf(args.bias_scale, __ldg(args.bias + col), o);
+                    if (act) o = apply_act(o, act);
+                    if (has_res) o = fmaf(args.residual_scale, __ldg(r_row + col), o);
+                    c_row[col] = o;
+                }
+            }
+        }
+    }
+}
+
+// SPLITK > 1: a cluster of SPLITK CTAs shares one output tile, each CTA takes a contiguous share of the k-blocks; the
+// partial tiles are parked in shared memory and every CTA adds up and finishes its own share of the tile's columns,
+// reading the peers' partial tiles through distributed shared memory.  For products with few output tiles (a tall A against
+// a narrow B), where one CTA per tile would leave most SMs idle and each busy SM bound by what it can take in from L2.
+template <int SPLITK>
+__global__ void __cluster_dims__(SPLITK, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_constant__ CUtensorMap tmap_al,
                    const __grid_constant__ CUtensorMap tmap_bh, const __grid_constant__ CUtensorMap tmap_bl, const Tf32Args args) {
     extern __shared__ uint8_t smem_raw[];
@@ -122,6 +171,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_kb = (args.k + TBK - 1) / TBK;
+    const uint32_t rank = SPLITK > 1 ? ptx::cluster_ctarank() : 0u;
+    const int first_tile = blockIdx.x / SPLITK, tile_step = gridDim.x / SPLITK;  // a cluster = a tile at a time
+    const int kb_per = (num_kb + SPLITK - 1) / SPLITK;
+    const int kb_begin = static_cast<int>(rank) * kb_per;
+    const int kb_end = kb_begin + kb_per < num_kb ? kb_begin + kb_per : num_kb;
+    float* partial = reinterpret_cast<float*>(smem);  // SPLITK > 1: the pipeline stages are idle by the time it is written
 
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_ah);
@@ -155,9 +210,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
+            for (int tile = first_tile; ok && tile < args.num_tiles; tile += tile_step) {
                 const int m0 = (tile % args.tiles_m) * TBM, n0 = (tile / args.tiles_m) * TBN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
                         atomicExch(args.status, DEV_TIMEOUT_PRODUCER);
                         ok = false;
@@ -191,14 +246,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
             uint32_t phase = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < args.num_tiles; tile += gridDim.x) {
+            for (int tile = first_tile; ok && tile < args.num_tiles; tile += tile_step) {
                 if (!ptx::mbar_wait(&tmem_empty_bar[0], acc_phase ^ 1)) {
                     atomicExch(args.status, DEV_TIMEOUT_MMA);
                     break;
                 }
                 ptx::tc_fence_after();
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    const uint32_t d_tmem = tmem_base + (kb % T_NACC) * TBN;  // k-block kb adds into accumulator kb mod 4
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    const int kbl = kb - kb_begin;
+                    const uint32_t d_tmem = tmem_base + (kbl % T_NACC) * TBN;  // this CTA's i-th k-block adds into accumulator i mod 4
                     if (!ptx::mbar_wait(&full_bar[stage], phase)) {
                         atomicExch(args.status, DEV_TIMEOUT_MMA);
                         ok = false;
@@ -218,7 +274,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
                         const uint64_t d_bl = args.b_mn ? make_smem_desc_mn32(bl + kk * 1024, 4096, 512) : ptx::make_smem_desc_sw128(bl + off, 16, 1024);
                         const uint32_t idesc = args.b_mn ? (T_IDESC | (1u << 16)) : T_IDESC;
                         // the two small terms first, the large one last
-                        mma_tf32_ss(d_tmem, d_al, d_bh, idesc, (kb >= T_NACC || kk != 0) ? 1u : 0u);
+                        mma_tf32_ss(d_tmem, d_al, d_bh, idesc, (kbl >= T_NACC || kk != 0) ? 1u : 0u);
                         mma_tf32_ss(d_tmem, d_ah, d_bl, idesc, 1u);
                         mma_tf32_ss(d_tmem, d_ah, d_bh, idesc, 1u);
                     }
@@ -239,11 +295,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
         const int half = (warp - 2) >> 2;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t acc_phase = 0;
-        const int nacc = num_kb < T_NACC ? num_kb : T_NACC;  // accumulators that received a k-block
+        const int nacc = kb_end - kb_begin < T_NACC ? kb_end - kb_begin : T_NACC;  // accumulators that received a k-block
         const bool has_bias = (args.epilogue & B200ML_EPI_BIAS) && args.bias != nullptr;
         const bool has_res = (args.epilogue & B200ML_EPI_RESIDUAL) && args.residual != nullptr;
         const int act = args.epilogue & (B200ML_EPI_RELU | B200ML_EPI_GELU | B200ML_EPI_SWISH);
-        for (int tile = blockIdx.x; tile < args.num_tiles; tile += gridDim.x) {
+        for (int tile = first_tile; tile < args.num_tiles; tile += tile_step) {
             const int row = (tile % args.tiles_m) * TBM + row_in_tile;
             const int n0 = (tile / args.tiles_m) * TBN + half * 64;
             if (!ptx::mbar_wait(&tmem_full_bar[0], acc_phase)) {
@@ -263,6 +319,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
                 __syncwarp();  // the TMEM load is warp-collective: no lane may still be inside the guarded stores below
                 ptx::tmem_ld_32x32b_x32(t_base + c * 32, r);  // every lane loads; only the stores are guarded
                 ptx::tmem_ld_wait();
+                if (nacc == 0) {  // SPLITK: a CTA past the end of K received nothing; its share is zero
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
                 for (int a = 1; a < nacc; ++a) {  // warp-uniform trip count
                     uint32_t q[32];
                     ptx::tmem_ld_32x32b_x32(t_base + a * TBN + c * 32, q);
@@ -270,43 +330,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
                 }
-                const bool full = args.vec_ok && col0 + 32 <= args.n;
-                if (row_ok) {
+                if constexpr (SPLITK == 1) {
+                    tf32_finish_chunk<32>(args, r, row_ok, c_row, r_row, col0, has_bias, has_res, act);
+                } else {
+                    // this CTA's share of K: park the partial sums column-major (a lane = a row: conflict-free) for the reduction
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    float v[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = args.alpha * __uint_as_float(r[g * 4 + j]);
-                    if (full) {
-                        if (has_bias) {
-                            const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col0 + g * 4));
-                            v[0] = fmaf(args.bias_scale, b.x, v[0]), v[1] = fmaf(args.bias_scale, b.y, v[1]);
-                            v[2] = fmaf(args.bias_scale, b.z, v[2]), v[3] = fmaf(args.bias_scale, b.w, v[3]);
-                        }
-                        if (act) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) v[j] = apply_act(v[j], act);
-                        }
-                        if (has_res) {
-                            const float4 q = __ldg(reinterpret_cast<const float4*>(r_row + col0 + g * 4));
-                            v[0] = fmaf(args.residual_scale, q.x, v[0]), v[1] = fmaf(args.residual_scale, q.y, v[1]);
-                            v[2] = fmaf(args.residual_scale, q.z, v[2]), v[3] = fmaf(args.residual_scale, q.w, v[3]);
-                        }
-                        *reinterpret_cast<float4*>(c_row + col0 + g * 4) = make_float4(v[0], v[1], v[2], v[3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int col = col0 + g * 4 + j;
-                            if (col < args.n) {
-                                float o = v[j];
-                                if (has_bias) o = fmaf(args.bias_scale, __ldg(args.bias + col), o);
-                                if (act) o = apply_act(o, act);
-                                if (has_res) o = fmaf(args.residual_scale, __ldg(r_row + col), o);
-                                c_row[col] = o;
-                            }
-                        }
-                    }
-                }
+                    for (int j = 0; j < 32; ++j) partial[(half * 64 + c * 32 + j) * T_PART_LD + row_in_tile] = __uint_as_float(r[j]);
                 }
             }
             ptx::tc_fence_before();
@@ -316,6 +345,38 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_ah, const __grid_con
         }
     }
 
+    if constexpr (SPLITK > 1) {
+        // every thread of the cluster: the partial tiles are parked
+        ptx::cluster_sync_acq_rel();
+        if (warp >= 2 && first_tile < args.num_tiles) {
+            // every rank adds up and finishes its own 128 / SPLITK columns of the tile: a warp takes 32 rows (a lane = a row,
+            // so the loads from a peer's shared memory are 128 contiguous bytes) and half of those columns
+            constexpr int NC = TBN / SPLITK / 2;
+            const int quarter = warp & 3, half = (warp - 2) >> 2, row_in_tile = quarter * 32 + lane;
+            const int tile = first_tile;
+            const int row = (tile % args.tiles_m) * TBM + row_in_tile;
+            const int tc0 = static_cast<int>(rank) * (TBN / SPLITK) + half * NC;  // first column inside the tile
+            const int col0 = (tile / args.tiles_m) * TBN + tc0;
+            const bool has_bias = (args.epilogue & B200ML_EPI_BIAS) && args.bias != nullptr;
+            const bool has_res = (args.epilogue & B200ML_EPI_RESIDUAL) && args.residual != nullptr;
+            const int act = args.epilogue & (B200ML_EPI_RELU | B200ML_EPI_GELU | B200ML_EPI_SWISH);
+            float* c_row = args.c + static_cast<int64_t>(row) * args.ldc;
+            const float* r_row = has_res ? args.residual + static_cast<int64_t>(row) * args.ldr : nullptr;
+            if (col0 < args.n) {  // warp-uniform
+                uint32_t r[NC];
+#pragma unroll
+                for (int j = 0; j < NC; ++j) {
+                    const float* slot = partial + (tc0 + j) * T_PART_LD + row_in_tile;
+                    float v = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < SPLITK; ++q) v += ptx::ld_shared_cluster_f32(slot, q);  // rank order: the same sum on every run
+                    r[j] = __float_as_uint(v);
+                }
+                tf32_finish_chunk<NC>(args, r, row < args.m, c_row, r_row, col0, has_bias, has_res, act);
+            }
+        }
+        ptx::cluster_sync_acq_rel();  // no CTA leaves while a peer may still read its partial tile
+    }
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -338,6 +399,14 @@ int make_tmap_f32(const b200ml_ctx* ctx, CUtensorMap* out, const float* base, in
     CUresult r = encode_tiled_cached(ctx, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box);
     if (r != CUDA_SUCCESS) return fail(B200ML_ERR_CUDA, "cuTensorMapEncodeTiled(%s, fp32) failed with CUresult %d", what, (int)r);
     return B200ML_OK;
+}
+
+bool splitk_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("B200ML_TF32_SPLITK");
+        return !(e && e[0] == '0');
+    }();
+    return on;
 }
 
 bool tf32x3_enabled() {
@@ -425,11 +494,24 @@ int gemm_f32_tensor_core(const b200ml_ctx* ctx, const b200ml_gemm_params* p, cud
 
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        B200ML_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM));
+        B200ML_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM));
+        B200ML_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM));
+        B200ML_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM));
         configured[ctx->device & 63] = true;
     }
-    const int grid = args.num_tiles < ctx->sm_count ? args.num_tiles : ctx->sm_count;
-    B200ML_CUDA(launch_pdl(gemm_tf32x3_kernel, dim3(grid), dim3(GEMM_THREADS), T_SMEM, stream, tah, tal, tbh, tbl, args));
+    // few output tiles: split K over a cluster of 2 or 4 CTAs per tile (one tile per cluster, no persistence)
+    const int num_kb = (int)ceil_div(p->k, TBK);
+    int split = 1;
+    if (splitk_enabled()) {
+        if (args.num_tiles * 4 <= ctx->sm_count && num_kb >= 8) split = 4;
+        else if (args.num_tiles * 2 <= ctx->sm_count && num_kb >= 4) split = 2;
+    }
+    if (split == 4) B200ML_CUDA(launch_pdl(gemm_tf32x3_kernel<4>, dim3(args.num_tiles * 4), dim3(GEMM_THREADS), T_SMEM, stream, tah, tal, tbh, tbl, args));
+    else if (split == 2) B200ML_CUDA(launch_pdl(gemm_tf32x3_kernel<2>, dim3(args.num_tiles * 2), dim3(GEMM_THREADS), T_SMEM, stream, tah, tal, tbh, tbl, args));
+    else {
+        const int grid = args.num_tiles < ctx->sm_count ? args.num_tiles : ctx->sm_count;
+        B200ML_CUDA(launch_pdl(gemm_tf32x3_kernel<1>, dim3(grid), dim3(GEMM_THREADS), T_SMEM, stream, tah, tal, tbh, tbl, args));
+    }
     return check_launch("gemm_tf32x3");
 }
 

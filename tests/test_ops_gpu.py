@@ -107,9 +107,11 @@ def test_matmul_pair_kernel_ragged_rows(m, n, k, rng):
     status_ok()
 
 
-@pytest.mark.parametrize("m, n, k", [(1000, 200, 360), (4096, 120, 784), (300, 256, 1024)])
+@pytest.mark.parametrize("m, n, k", [(1000, 200, 360), (4096, 120, 784), (300, 256, 1024), (2048, 128, 288), (4096, 100, 2048), (640, 128, 4096),
+                                     (8192, 64, 516)])
 def test_gemm_fp32_tensor_core_path(m, n, k, rng):
-    """fp32 Gemm(transB=1) large enough for the three-pass TF32 tensor-core kernel: ragged M, N and K, bias + ReLU.
+    """fp32 Gemm(transB=1) large enough for the three-pass TF32 tensor-core kernel: ragged M, N and K, bias + ReLU;
+    few output tiles (K split over clusters of 2 or 4 CTAs, also with a share of K that is empty) and many.
     The result must meet the fp32 tolerance (rtol 1e-4), which a single TF32 pass would not."""
     a, w, c = (rng.standard_normal((m, k)).astype(np.float32), (rng.standard_normal((n, k)) * 0.1).astype(np.float32),
                rng.standard_normal(n).astype(np.float32))
