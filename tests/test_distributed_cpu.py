@@ -46,6 +46,16 @@ def _worker(rank, world, port, mode, ret):
                 ret[rank] = False
             except Exception:
                 ret[rank] = True
+        elif mode == "peer_unavailable":
+            # without a GPU the peer all-gather cannot be set up: every rank gets the exception (none is left waiting in a
+            # collective), and the NCCL / gloo gather still works afterwards
+            try:
+                D.PeerGather((3, 8), torch.float16, torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu"), r, w)
+                ok = torch.cuda.is_available()
+            except Exception:
+                ok = not torch.cuda.is_available()
+            y = D.gather_outputs(torch.full((2, 4), float(r)))
+            ret[rank] = ok and bool(torch.equal(y, torch.cat([torch.full((2, 4), float(i)) for i in range(w)])))
         dist.barrier() if mode != "rank_raises" else None
     finally:
         if dist.is_initialized() and mode != "rank_raises":
@@ -77,6 +87,10 @@ def test_uneven_batch_is_rejected():
 
 def test_failed_rank_surfaces_as_exception():
     assert _run("rank_raises") == {0: True, 1: True}
+
+
+def test_peer_gather_without_a_gpu_fails_on_every_rank_and_leaves_the_group_usable():
+    assert _run("peer_unavailable") == {0: True, 1: True}
 
 
 def test_single_process_paths():
